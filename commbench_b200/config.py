@@ -1,0 +1,68 @@
+"""Typed configuration with ``CB200_*`` environment overrides.
+
+The reference has no central configuration: every example script parses its own
+argparse flags and environment variables (scripts/generate_eval_one.py:661-753,
+datasets/example080_deepep_jit_dispatch_payload/nv/build_and_run.py:296-303) and the
+kernels' real configuration is compile-time constants
+(datasets/example051_thunderkitten_ag_gemm_easy/nv/empty_thunderkitten_ag_gemm.cu:86-99).
+Here one dataclass holds the per-op tunables; the world size is a run-time value.
+"""
+from __future__ import annotations
+
+import dataclasses
+import os
+from dataclasses import dataclass
+
+
+@dataclass
+class Config:
+    # --- collectives -------------------------------------------------------
+    ar_oneshot_max_bytes: int = 512 * 1024      # at or below: one-shot pull all-reduce
+    ar_nvls_min_bytes: int = 512 * 1024         # at or above (with multicast bound): NVLS
+    coll_max_blocks: int = 64                   # CTAs per collective kernel (<= one wave)
+    # --- fused GEMMs -------------------------------------------------------
+    ag_gemm_comm_ctas: int = 16                 # CTAs reserved for pushing the local A shard
+    gemm_rs_reduce_ctas: int = 0                # 0: reduction runs on all CTAs after their tiles
+    gemm_ar_oneshot_max_m: int = 256            # rows at or below: one-shot AR epilogue
+    # --- MoE ---------------------------------------------------------------
+    moe_expert_alignment: int = 128             # rows per expert padded to a tile multiple
+    # --- runtime -----------------------------------------------------------
+    heap_bytes: int = 1 << 30
+    timeout_s: float = 2.0
+    use_nvls: bool = True
+
+
+_CONFIG: Config | None = None
+
+
+def _coerce(value: str, typ):
+    if typ is bool:
+        return value.strip().lower() not in ("0", "false", "no", "off", "")
+    return typ(value)
+
+
+def get_config() -> Config:
+    """The process-wide configuration (created on first use from the environment)."""
+    global _CONFIG
+    if _CONFIG is None:
+        cfg = Config()
+        for f in dataclasses.fields(Config):
+            env = os.environ.get("CB200_" + f.name.upper())
+            if env is not None:
+                setattr(cfg, f.name, _coerce(env, type(getattr(cfg, f.name))))
+        _CONFIG = cfg
+    return _CONFIG
+
+
+def set_config(**kw) -> Config:
+    cfg = get_config()
+    for k, v in kw.items():
+        if not hasattr(cfg, k):
+            raise KeyError(f"unknown config field {k!r}")
+        setattr(cfg, k, v)
+    return cfg
+
+
+def reset_config():
+    global _CONFIG
+    _CONFIG = None

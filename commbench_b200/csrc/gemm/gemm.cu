@@ -1,0 +1,213 @@
+// Plain (single-GPU) tcgen05 GEMM entry points and the tensor-map helper.
+// C[M,N] = alpha * A[M,K] * B[N,K]^T, bf16 or fp8-e4m3 inputs, bf16 output.
+//
+// This is the local GEMM every fused path is built from, and the kernel that
+// runs when the world size is 1.  The reference has the equivalent as
+// `matmul::kernel` (datasets/example053_thunderkitten_gemm_ar_easy/nv/
+// empty_thunderkitten_gemm_ar.cu:84-191).
+#include "gemm_sm100.cuh"
+
+#include <string>
+
+#include "../symm/driver_api.h"
+#include "tmap_host.h"
+
+namespace cb {
+
+int make_tmap_2d(CUtensorMap* out, const void* base, TmapDtype dt, unsigned long long inner,
+                 unsigned long long outer, unsigned long long row_stride_bytes,
+                 unsigned box_inner, unsigned box_outer, bool swizzle128) {
+  const DriverApi& d = driver_api();
+  if (!d.ok) {
+    set_last_error("tensor map: " + d.why);
+    return -1;
+  }
+  const unsigned esz = dt == TMAP_BF16 ? 2 : (dt == TMAP_U8 ? 1 : 4);
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) {
+    set_last_error("tensor map: base address is not 16-byte aligned");
+    return -1;
+  }
+  if (row_stride_bytes % 16ull != 0) {
+    set_last_error("tensor map: row stride is not a multiple of 16 bytes");
+    return -1;
+  }
+  if ((box_inner * esz) % 16u != 0 || box_inner > 256u || box_outer > 256u) {
+    set_last_error("tensor map: bad box");
+    return -1;
+  }
+  if (swizzle128 && box_inner * esz != 128u) {
+    set_last_error("tensor map: 128-byte swizzle needs a 128-byte inner box");
+    return -1;
+  }
+  const CUtensorMapDataType cdt = dt == TMAP_BF16  ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                  : dt == TMAP_U8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                                  : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = d.cuTensorMapEncodeTiled(
+      out, cdt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error(cu_err("cuTensorMapEncodeTiled", r));
+    return -1;
+  }
+  return 0;
+}
+
+struct PlainParams {
+  CUtensorMap tm_a, tm_b, tm_c;
+  GemmShape g;
+  uint32_t* status;
+  int raster_group;
+};
+
+template <class Cfg>
+struct PlainPolicy {
+  using P = PlainParams;
+  __device__ static int num_tiles(const P& p) { return p.g.num_m_blocks * p.g.num_n_blocks; }
+  __device__ static void tile_coord(const P& p, int tile, int* m, int* n) {
+    raster_tile(tile, p.g.num_m_blocks, p.g.num_n_blocks, p.raster_group, m, n);
+  }
+  __device__ static const CUtensorMap* map_a(const P& p, int) { return &p.tm_a; }
+  __device__ static const CUtensorMap* map_b(const P& p) { return &p.tm_b; }
+  __device__ static int a_row(const P&, int m_blk) { return m_blk * Cfg::BM; }
+  __device__ static bool wait_a_ready(const P&, int, volatile int*) { return true; }
+  __device__ static void store_box(const P& p, int m_blk, int n_blk, int row, int col,
+                                   const void* smem_box) {
+    tma_store_2d(&p.tm_c, smem_box, n_blk * Cfg::BN + col, m_blk * Cfg::BM + row);
+  }
+  __device__ static void tile_done(const P&, int, int, int) {}
+};
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
+    gemm_plain_kernel(const __grid_constant__ PlainParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  gemm_cta_main<Cfg, PlainPolicy<Cfg>>(p, p.g, p.status, blockIdx.x, gridDim.x, smem_raw);
+}
+
+static int g_sm_count = 0;
+static int sm_count() {
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (g_sm_count <= 0) g_sm_count = 148;
+  }
+  return g_sm_count;
+}
+
+template <class Cfg>
+static int launch_plain(const void* a, const void* b, void* c, int M, int N, int K, float alpha,
+                        uint32_t* status, int max_ctas, cudaStream_t st) {
+  PlainParams p;
+  const TmapDtype dt = Cfg::FP8 ? TMAP_U8 : TMAP_BF16;
+  const unsigned esz = Cfg::FP8 ? 1 : 2;
+  if (make_tmap_2d(&p.tm_a, a, dt, K, M, (unsigned long long)K * esz, Cfg::BK, Cfg::BM, true))
+    return -1;
+  if (make_tmap_2d(&p.tm_b, b, dt, K, N, (unsigned long long)K * esz, Cfg::BK, Cfg::BN, true))
+    return -1;
+  if (make_tmap_2d(&p.tm_c, c, TMAP_BF16, N, M, (unsigned long long)N * 2, Cfg::EPI_COLS, 32,
+                   true))
+    return -1;
+  p.g.M = M;
+  p.g.N = N;
+  p.g.K = K;
+  p.g.num_m_blocks = (M + Cfg::BM - 1) / Cfg::BM;
+  p.g.num_n_blocks = (N + Cfg::BN - 1) / Cfg::BN;
+  p.g.num_k_blocks = (K + Cfg::BK - 1) / Cfg::BK;
+  p.g.alpha = alpha;
+  p.status = status;
+  p.raster_group = 8;
+  {
+    cudaError_t e = cudaFuncSetAttribute(gemm_plain_kernel<Cfg>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) {
+      set_last_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+      return -1;
+    }
+  }
+  int tiles = p.g.num_m_blocks * p.g.num_n_blocks;
+  int ctas = sm_count();
+  if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+  if (tiles < ctas) ctas = tiles;
+  if (ctas < 1) return 0;
+  gemm_plain_kernel<Cfg><<<ctas, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error(std::string("gemm launch: ") + cudaGetErrorString(e));
+    return -1;
+  }
+  return 0;
+}
+
+}  // namespace cb
+
+using namespace cb;
+
+extern "C" {
+
+// bf16: A [M,K], B [N,K], C [M,N], all row-major and 16-byte aligned; K % 8 == 0, N % 8 == 0.
+// `bn` picks the tile width (256, 128 or 64; 0 = choose from the shape).
+// `status` may be null.  Returns 0 or -1 (cb_last_error()).
+int cb_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, float alpha, int bn,
+                 int max_ctas, void* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 8) != 0 || (N % 8) != 0) {
+    set_last_error("cb_gemm_bf16: need M,N,K > 0, K % 8 == 0, N % 8 == 0");
+    return -1;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint32_t* s = static_cast<uint32_t*>(status);
+  if (bn == 0) {
+    // Fill the machine: wide tiles when there are plenty, narrow ones for skinny problems.
+    const long long m_blocks = (M + 127) / 128;
+    if (m_blocks * ((N + 255) / 256) >= sm_count()) bn = 256;
+    else if (m_blocks * ((N + 127) / 128) >= sm_count()) bn = 128;
+    else bn = 64;
+  }
+  switch (bn) {
+    case 256:
+      return launch_plain<GemmCfg<256, 4, false>>(a, b, c, M, N, K, alpha, s, max_ctas, st);
+    case 128:
+      return launch_plain<GemmCfg<128, 6, false>>(a, b, c, M, N, K, alpha, s, max_ctas, st);
+    case 64:
+      return launch_plain<GemmCfg<64, 8, false>>(a, b, c, M, N, K, alpha, s, max_ctas, st);
+    default:
+      set_last_error("cb_gemm_bf16: bn must be 0, 64, 128 or 256");
+      return -1;
+  }
+}
+
+// fp8 e4m3 inputs with ONE scale per tensor folded into alpha; K % 16 == 0.
+int cb_gemm_fp8(const void* a, const void* b, void* c, int M, int N, int K, float alpha, int bn,
+                int max_ctas, void* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 16) != 0 || (N % 8) != 0) {
+    set_last_error("cb_gemm_fp8: need M,N,K > 0, K % 16 == 0, N % 8 == 0");
+    return -1;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint32_t* s = static_cast<uint32_t*>(status);
+  if (bn == 0) {
+    const long long m_blocks = (M + 127) / 128;
+    if (m_blocks * ((N + 255) / 256) >= sm_count()) bn = 256;
+    else if (m_blocks * ((N + 127) / 128) >= sm_count()) bn = 128;
+    else bn = 64;
+  }
+  switch (bn) {
+    case 256:
+      return launch_plain<GemmCfg<256, 4, true>>(a, b, c, M, N, K, alpha, s, max_ctas, st);
+    case 128:
+      return launch_plain<GemmCfg<128, 6, true>>(a, b, c, M, N, K, alpha, s, max_ctas, st);
+    case 64:
+      return launch_plain<GemmCfg<64, 8, true>>(a, b, c, M, N, K, alpha, s, max_ctas, st);
+    default:
+      set_last_error("cb_gemm_fp8: bn must be 0, 64, 128 or 256");
+      return -1;
+  }
+}
+
+}  // extern "C"

@@ -1,0 +1,52 @@
+"""Local tcgen05 GEMM: ``C = alpha * A @ B.T`` with A [M,K], B [N,K] (nn.Linear weight layout).
+
+bf16 inputs, or fp8 e4m3 inputs with per-tensor scales folded into ``alpha``;
+fp32 accumulation in tensor memory; bf16 output.  This is the single-GPU
+building block of every fused tensor-parallel op (reference counterpart:
+``matmul::kernel`` in datasets/example053_thunderkitten_gemm_ar_easy/nv/
+empty_thunderkitten_gemm_ar.cu:84-191).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import _native as N
+
+
+class GemmError(RuntimeError):
+    pass
+
+
+def _check(t: torch.Tensor, name: str):
+    if not (t.is_cuda and t.is_contiguous() and t.dim() == 2 and t.data_ptr() % 16 == 0):
+        raise GemmError(f"{name} must be a contiguous, 16-byte aligned 2-D CUDA tensor")
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, alpha: float = 1.0,
+         bn: int = 0, max_ctas: int = 0, status_ptr: int = 0, stream=None) -> torch.Tensor:
+    """``out[M,N] = alpha * a[M,K] @ b[N,K].T`` on the tcgen05 kernel (no library GEMM)."""
+    lib = N.load()
+    _check(a, "a")
+    _check(b, "b")
+    M, K = a.shape
+    Nn, K2 = b.shape
+    if K != K2:
+        raise GemmError(f"inner dimensions differ: {K} vs {K2}")
+    if out is None:
+        out = torch.empty((M, Nn), dtype=torch.bfloat16, device=a.device)
+    _check(out, "out")
+    if out.dtype != torch.bfloat16 or tuple(out.shape) != (M, Nn):
+        raise GemmError("out must be bf16 [M, N]")
+    if a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16:
+        fn = lib.cb_gemm_bf16
+    elif a.dtype == torch.float8_e4m3fn and b.dtype == torch.float8_e4m3fn:
+        fn = lib.cb_gemm_fp8
+    else:
+        raise GemmError(f"unsupported dtypes {a.dtype} x {b.dtype}")
+    rc = fn(N.ptr(a), N.ptr(b), N.ptr(out), M, Nn, K, C.c_float(alpha), bn, max_ctas,
+            C.c_void_p(status_ptr), N.stream_ptr(stream))
+    if rc != 0:
+        raise GemmError(f"gemm launch failed: {N.last_error()}")
+    return out

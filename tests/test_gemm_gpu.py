@@ -1,0 +1,66 @@
+"""tcgen05 GEMM vs a plain PyTorch fp32 reference of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, alpha=1.0):
+    return alpha * (a.float() @ b.float().t())
+
+
+def _check(out, ref, tol):
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err / scale < tol, f"max abs err {err} vs scale {scale}"
+
+
+@pytest.mark.parametrize("bn", [256, 128, 64])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (384, 768, 1024),
+                                   (1000, 1304, 520), (16, 8192, 1024)])
+def test_gemm_bf16_matches_fp32_reference(native_lib, shape, bn):
+    from commbench_b200.ops.gemm import gemm
+
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(1234 + M + N + K)
+    a = torch.randn(M, K, device="cuda", generator=g).mul_(0.5).bfloat16()
+    b = torch.randn(N, K, device="cuda", generator=g).mul_(0.5).bfloat16()
+    out = gemm(a, b, bn=bn)
+    torch.cuda.synchronize()
+    _check(out, _ref(a, b), 1e-2)
+
+
+def test_gemm_bf16_full_tensor_exact_on_small_ints(native_lib):
+    """Integer-valued inputs make the fp32 accumulation exact: every element must match."""
+    from commbench_b200.ops.gemm import gemm
+
+    M, N, K = 256, 512, 192
+    g = torch.Generator(device="cuda").manual_seed(7)
+    a = torch.randint(-3, 4, (M, K), device="cuda", generator=g).bfloat16()
+    b = torch.randint(-3, 4, (N, K), device="cuda", generator=g).bfloat16()
+    out = gemm(a, b, bn=128)
+    ref = _ref(a, b)
+    assert torch.equal(out.float(), ref.bfloat16().float())
+
+
+def test_gemm_bf16_large_auto_tile(native_lib):
+    from commbench_b200.ops.gemm import gemm
+
+    M, N, K = 4096, 4096, 2048
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = torch.randn(M, K, device="cuda", generator=g).mul_(0.1).bfloat16()
+    b = torch.randn(N, K, device="cuda", generator=g).mul_(0.1).bfloat16()
+    out = gemm(a, b, alpha=0.5)
+    _check(out, _ref(a, b, 0.5), 1e-2)
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 128), (512, 1024, 512), (300, 520, 1024)])
+def test_gemm_fp8_matches_fp32_reference(native_lib, shape):
+    from commbench_b200.ops.gemm import gemm
+
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(99)
+    a = torch.randn(M, K, device="cuda", generator=g).to(torch.float8_e4m3fn)
+    b = torch.randn(N, K, device="cuda", generator=g).to(torch.float8_e4m3fn)
+    out = gemm(a, b, alpha=0.25, bn=128)
+    _check(out, _ref(a, b, 0.25), 1e-2)

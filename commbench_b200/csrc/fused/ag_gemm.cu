@@ -1,0 +1,388 @@
+// Fused all-gather -> GEMM:  C[M, N_local] = allgather_rows(A_local)[M, K] * B[N_local, K]^T
+//
+// ONE kernel per rank.  A few CTAs ("comm CTAs") push this rank's A rows into
+// every peer's gathered buffer with TMA bulk copies and raise a per-row-block
+// flag on the peer; the other CTAs run the tcgen05 GEMM, doing the tiles of
+// their own rows first (straight from A_local) and then, in arrival order, the
+// tiles of remote rows as soon as the row block's flag is up.  Transfer and
+// math overlap row block by row block.
+//
+// The reference has the same split -- comm SMs storing A chunks through the
+// multicast address plus per-row-block barriers, compute SMs waiting on them
+// (datasets/example051_thunderkitten_ag_gemm_easy/nv/empty_thunderkitten_ag_gemm.cu:118-238)
+// -- with NUM_DEVICES fixed at 8 and a separate clean-up kernel; here the world
+// size is a run-time value, buffers/flags are double-buffered by call parity so
+// no clean-up launch and no cross-GPU barrier is needed, and operand loads are
+// never cluster-multicast.
+#include "fused_common.cuh"
+
+#include <string>
+
+#include "../gemm/tmap_host.h"
+#include "../symm/driver_api.h"
+
+namespace cb {
+
+static constexpr int kAgMaxRowBlocks = 1024;  // flags per parity
+static constexpr int kCommWorkers = 3;        // worker warps per comm CTA
+static constexpr int kCommBufs = 4;           // staging buffers per worker
+static constexpr int kCommChunk = 16384;      // bytes per bulk copy
+static constexpr int kCommPrefetch = 2;
+
+struct AgGemmParams {
+  CUtensorMap tm_a_local;
+  CUtensorMap tm_a_full[2];
+  CUtensorMap tm_b;
+  CUtensorMap tm_c;
+  GemmShape g;
+  int rank, world;
+  int blocks_per_rank;  // 128-row blocks of A owned by each rank
+  int parts;            // independent pieces a row block is pushed in
+  int num_comm_ctas;
+  int raster_group;
+  unsigned long long row_block_bytes;
+  const uint8_t* a_local;
+  uint8_t* a_full_peer[2][CB_MAX_RANKS];
+  uint8_t* a_full_mc[2];
+  uint32_t* flags_peer[CB_MAX_RANKS];  // [2][kAgMaxRowBlocks] on each rank
+  uint32_t* flags_mc;
+  uint32_t* flags_local;
+  FusedSeq seq;
+  uint32_t* status;
+  unsigned long long timeout_ns;
+};
+
+struct AgRt {
+  const AgGemmParams* p;
+  uint32_t parity;
+};
+
+template <class Cfg>
+struct AgPolicy {
+  __device__ static int num_tiles(const AgRt& r) {
+    return r.p->g.num_m_blocks * r.p->g.num_n_blocks;
+  }
+  // Position in the processing order -> global row block: own blocks first, then
+  // row block 0 of every peer, row block 1 of every peer, ... (the order they arrive in).
+  __device__ static int seq_to_mblk(const AgGemmParams& p, int i) {
+    const int bpr = p.blocks_per_rank;
+    if (i < bpr) return p.rank * bpr + i;
+    const int j = i - bpr;
+    const int rb = j / (p.world - 1);
+    const int peer = (p.rank + 1 + j % (p.world - 1)) % p.world;
+    return peer * bpr + rb;
+  }
+  __device__ static void tile_coord(const AgRt& r, int tile, int* m, int* n) {
+    int i;
+    raster_tile(tile, r.p->g.num_m_blocks, r.p->g.num_n_blocks, r.p->raster_group, &i, n);
+    *m = seq_to_mblk(*r.p, i);
+  }
+  __device__ static bool is_local(const AgGemmParams& p, int m_blk) {
+    return m_blk / p.blocks_per_rank == p.rank;
+  }
+  __device__ static const CUtensorMap* map_a(const AgRt& r, int m_blk) {
+    return is_local(*r.p, m_blk) ? &r.p->tm_a_local : &r.p->tm_a_full[r.parity];
+  }
+  __device__ static const CUtensorMap* map_b(const AgRt& r) { return &r.p->tm_b; }
+  __device__ static int a_row(const AgRt& r, int m_blk) {
+    return is_local(*r.p, m_blk) ? (m_blk - r.p->rank * r.p->blocks_per_rank) * Cfg::BM
+                                 : m_blk * Cfg::BM;
+  }
+  __device__ static bool wait_a_ready(const AgRt& r, int m_blk, volatile int* abort_flag) {
+    const AgGemmParams& p = *r.p;
+    if (is_local(p, m_blk)) return true;
+    const uint32_t* f = p.flags_local + r.parity * kAgMaxRowBlocks + m_blk;
+    if (!wait_flag_ge_sys(f, static_cast<uint32_t>(p.parts), p.timeout_ns, p.status, PH_AG_ROWS,
+                          m_blk)) {
+      *abort_flag = 1;
+      return false;
+    }
+    // The rows were written by a peer's bulk copies; our TMA load must see them.
+    fence_proxy_async();
+    return true;
+  }
+  __device__ static void store_box(const AgRt& r, int m_blk, int n_blk, int row, int col,
+                                   const void* smem_box) {
+    tma_store_2d(&r.p->tm_c, smem_box, n_blk * Cfg::BN + col, m_blk * Cfg::BM + row);
+  }
+  __device__ static void tile_done(const AgRt&, int, int, int) {}
+};
+
+// Comm CTA: worker warps (lane 0 each) stream pieces of the local A rows
+// global -> shared -> every peer, then bump the row block's flag on the peers.
+__device__ __forceinline__ void ag_comm_cta(const AgGemmParams& p, uint32_t parity, int comm_cta,
+                                            uint8_t* smem) {
+  __shared__ uint64_t bars[kCommWorkers][kCommBufs];
+  const int warp = threadIdx.x >> 5;
+  if (warp >= kCommWorkers || (threadIdx.x & 31) != 0) return;
+  uint8_t* bufs = smem + warp * (kCommBufs * kCommChunk);
+  for (int b = 0; b < kCommBufs; ++b) mbar_init(&bars[warp][b], 1);
+  fence_mbar_init();
+  const int worker = comm_cta * kCommWorkers + warp;
+  const int nworkers = p.num_comm_ctas * kCommWorkers;
+  const unsigned long long piece = p.row_block_bytes / p.parts;
+  const int nchunks = static_cast<int>((piece + kCommChunk - 1) / kCommChunk);
+  uint32_t gi = 0;  // running chunk counter: buffer = gi % kCommBufs, parity = (gi / kCommBufs) & 1
+  bool ok = true;
+  for (int item = worker; ok && item < p.blocks_per_rank * p.parts; item += nworkers) {
+    const int rb = item / p.parts;
+    const int part = item % p.parts;
+    const uint8_t* src = p.a_local + rb * p.row_block_bytes + part * piece;
+    const unsigned long long dst_off =
+        static_cast<unsigned long long>(p.rank * p.blocks_per_rank + rb) * p.row_block_bytes +
+        part * piece;
+    auto chunk_bytes = [&](int i) -> uint32_t {
+      const unsigned long long left = piece - static_cast<unsigned long long>(i) * kCommChunk;
+      return static_cast<uint32_t>(left < kCommChunk ? left : kCommChunk);
+    };
+    auto issue_load = [&](int i) {
+      const uint32_t b = (gi + i) % kCommBufs;
+      mbar_arrive_expect_tx(&bars[warp][b], chunk_bytes(i));
+      bulk_load_1d(bufs + b * kCommChunk, src + static_cast<unsigned long long>(i) * kCommChunk,
+                   chunk_bytes(i), &bars[warp][b]);
+    };
+    for (int i = 0; i < kCommPrefetch && i < nchunks; ++i) issue_load(i);
+    for (int i = 0; i < nchunks; ++i) {
+      const uint32_t b = (gi + i) % kCommBufs;
+      const uint32_t par = ((gi + i) / kCommBufs) & 1u;
+      if (!mbar_wait(&bars[warp][b], par, nullptr, p.status, 0x500 + b)) {
+        ok = false;
+        break;
+      }
+      const unsigned long long off = dst_off + static_cast<unsigned long long>(i) * kCommChunk;
+      if (p.a_full_mc[parity] != nullptr) {
+        bulk_store_1d(p.a_full_mc[parity] + off, bufs + b * kCommChunk, chunk_bytes(i));
+      } else {
+        for (int d = 1; d < p.world; ++d) {
+          const int peer = (p.rank + d) % p.world;
+          bulk_store_1d(p.a_full_peer[parity][peer] + off, bufs + b * kCommChunk, chunk_bytes(i));
+        }
+      }
+      bulk_commit();
+      if (i + kCommPrefetch < nchunks) {
+        // The buffer about to be refilled was read by the stores of chunk i+prefetch-bufs.
+        if (gi + i + kCommPrefetch >= static_cast<uint32_t>(kCommBufs))
+          bulk_wait_read<kCommBufs - kCommPrefetch>();
+        issue_load(i + kCommPrefetch);
+      }
+    }
+    // All stores of this piece are performed before the flag goes up.
+    bulk_wait_all<0>();
+    gi += nchunks;
+    if (!ok) break;
+    fence_proxy_async();
+    __threadfence_system();
+    const int m_blk = p.rank * p.blocks_per_rank + rb;
+    if (p.a_full_mc[parity] != nullptr && p.flags_mc != nullptr) {
+      mm_red_add_u32(p.flags_mc + parity * kAgMaxRowBlocks + m_blk, 1u);
+    } else {
+      for (int d = 1; d < p.world; ++d) {
+        const int peer = (p.rank + d) % p.world;
+        red_release_sys_add(p.flags_peer[peer] + parity * kAgMaxRowBlocks + m_blk, 1u);
+      }
+    }
+  }
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
+    ag_gemm_kernel(const __grid_constant__ AgGemmParams p0, const AgGemmParams* emu,
+                   int ctas_per_rank) {
+  extern __shared__ uint8_t smem_raw[];
+  const int vrank = emu != nullptr ? blockIdx.x / ctas_per_rank : 0;
+  const AgGemmParams& p = emu != nullptr ? emu[vrank] : p0;
+  const int cta = blockIdx.x - vrank * ctas_per_rank;
+  const uint32_t parity = fused_begin(p.seq);
+  const int ncomp = ctas_per_rank - p.num_comm_ctas;
+  if (cta >= ncomp) {
+    ag_comm_cta(p, parity, cta - ncomp, gemm_smem_base<Cfg>(smem_raw));
+  } else {
+    AgRt rt{&p, parity};
+    gemm_cta_main<Cfg, AgPolicy<Cfg>>(rt, p.g, p.status, cta, ncomp, smem_raw);
+  }
+  __syncthreads();
+  // Last CTA out zeroes this parity's flags (all waits of this call are over by then).
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t prev = atomicAdd(p.seq.done_ctas, 1u);
+    if (prev == static_cast<uint32_t>(ctas_per_rank) - 1u) {
+      for (int m = 0; m < p.g.num_m_blocks; ++m)
+        p.flags_local[parity * kAgMaxRowBlocks + m] = 0u;
+      *p.seq.done_ctas = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(p.seq.seq) = ld_volatile(p.seq.seq) + 1u;
+    }
+  }
+}
+
+template <class Cfg>
+static int launch_ag(const AgGemmParams& p, const AgGemmParams* emu, int emu_world,
+                     int ctas_per_rank, cudaStream_t st) {
+  cudaError_t e = cudaFuncSetAttribute(ag_gemm_kernel<Cfg>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       Cfg::SMEM_BYTES);
+  if (e != cudaSuccess) {
+    set_last_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+    return -1;
+  }
+  if (emu != nullptr) {
+    void* params[] = {const_cast<AgGemmParams*>(&p), &emu, &ctas_per_rank};
+    e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(ag_gemm_kernel<Cfg>),
+                                    dim3(ctas_per_rank * emu_world), dim3(Cfg::THREADS), params,
+                                    Cfg::SMEM_BYTES, st);
+  } else {
+    ag_gemm_kernel<Cfg><<<ctas_per_rank, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(p, nullptr,
+                                                                              ctas_per_rank);
+    e = cudaGetLastError();
+  }
+  if (e != cudaSuccess) {
+    set_last_error(std::string("ag_gemm launch: ") + cudaGetErrorString(e));
+    return -1;
+  }
+  return 0;
+}
+
+}  // namespace cb
+
+using namespace cb;
+
+extern "C" {
+
+// Host-side description of one rank's call; pointers are device addresses.
+struct CbAgGemmDesc {
+  int rank, world;
+  int M, N, K;            // M = rows of the gathered A (all ranks), N = local columns
+  int fp8;                // 0 bf16, 1 fp8 e4m3 (inputs); output is bf16
+  float alpha;
+  int bn;                 // 256 or 128
+  int num_comm_ctas;      // 0 when world == 1
+  int parts;              // pieces per 128-row block (divides 128)
+  int ctas_per_rank;      // CTAs this rank's launch (or grid slice) uses
+  const void* a_local;    // [M/world, K]
+  const void* b;          // [N, K]
+  void* c;                // [M, N] bf16
+  void* a_full_peer[2][CB_MAX_RANKS];  // gathered buffers [M, K], per parity and rank
+  void* a_full_mc[2];
+  void* flags_peer[CB_MAX_RANKS];      // uint32 [2][1024] per rank
+  void* flags_mc;
+  void* seq;              // uint32 [2] local: {call counter, done CTAs}
+  void* status;
+  unsigned long long timeout_ns;
+};
+
+static int build_ag_params(const CbAgGemmDesc& d, AgGemmParams* p) {
+  const int esz = d.fp8 ? 1 : 2;
+  const int BK = d.fp8 ? 128 : 64;
+  const TmapDtype dt = d.fp8 ? TMAP_U8 : TMAP_BF16;
+  if (d.world < 1 || d.M % (d.world * 128) != 0) {
+    set_last_error("ag_gemm: M must be a multiple of world * 128");
+    return -1;
+  }
+  if (d.K % 16 != 0 || d.N % 8 != 0) {
+    set_last_error("ag_gemm: K % 16 == 0 and N % 8 == 0 required");
+    return -1;
+  }
+  if (d.M / 128 > kAgMaxRowBlocks) {
+    set_last_error("ag_gemm: too many row blocks");
+    return -1;
+  }
+  if (d.parts < 1 || 128 % d.parts != 0) {
+    set_last_error("ag_gemm: parts must divide 128");
+    return -1;
+  }
+  const int Ml = d.M / d.world;
+  if (make_tmap_2d(&p->tm_a_local, d.a_local, dt, d.K, Ml, (unsigned long long)d.K * esz, BK, 128,
+                   true))
+    return -1;
+  for (int par = 0; par < 2; ++par) {
+    const void* base = d.a_full_peer[par][d.rank];
+    if (d.world > 1) {
+      if (make_tmap_2d(&p->tm_a_full[par], base, dt, d.K, d.M, (unsigned long long)d.K * esz, BK,
+                       128, true))
+        return -1;
+    } else {
+      p->tm_a_full[par] = p->tm_a_local;
+    }
+  }
+  if (make_tmap_2d(&p->tm_b, d.b, dt, d.K, d.N, (unsigned long long)d.K * esz, BK, d.bn, true))
+    return -1;
+  if (make_tmap_2d(&p->tm_c, d.c, TMAP_BF16, d.N, d.M, (unsigned long long)d.N * 2, 64, 32, true))
+    return -1;
+  p->g.M = d.M;
+  p->g.N = d.N;
+  p->g.K = d.K;
+  p->g.num_m_blocks = d.M / 128;
+  p->g.num_n_blocks = (d.N + d.bn - 1) / d.bn;
+  p->g.num_k_blocks = (d.K + BK - 1) / BK;
+  p->g.alpha = d.alpha;
+  p->rank = d.rank;
+  p->world = d.world;
+  p->blocks_per_rank = Ml / 128;
+  p->parts = d.parts;
+  p->num_comm_ctas = d.world > 1 ? d.num_comm_ctas : 0;
+  p->raster_group = p->blocks_per_rank < 8 ? p->blocks_per_rank : 8;
+  p->row_block_bytes = 128ull * d.K * esz;
+  p->a_local = static_cast<const uint8_t*>(d.a_local);
+  for (int par = 0; par < 2; ++par) {
+    for (int r = 0; r < CB_MAX_RANKS; ++r)
+      p->a_full_peer[par][r] = static_cast<uint8_t*>(d.a_full_peer[par][r]);
+    p->a_full_mc[par] = static_cast<uint8_t*>(d.a_full_mc[par]);
+  }
+  for (int r = 0; r < CB_MAX_RANKS; ++r) p->flags_peer[r] = static_cast<uint32_t*>(d.flags_peer[r]);
+  p->flags_mc = static_cast<uint32_t*>(d.flags_mc);
+  p->flags_local = static_cast<uint32_t*>(d.flags_peer[d.rank]);
+  p->seq.seq = static_cast<uint32_t*>(d.seq);
+  p->seq.done_ctas = static_cast<uint32_t*>(d.seq) + 1;
+  p->status = static_cast<uint32_t*>(d.status);
+  p->timeout_ns = d.timeout_ns;
+  if (d.world > 1 && p->num_comm_ctas < 1) {
+    set_last_error("ag_gemm: world > 1 needs at least one comm CTA");
+    return -1;
+  }
+  if (d.ctas_per_rank - p->num_comm_ctas < 1) {
+    set_last_error("ag_gemm: no compute CTAs left");
+    return -1;
+  }
+  return 0;
+}
+
+int cb_sizeof_ag_gemm_params() { return static_cast<int>(sizeof(AgGemmParams)); }
+
+// descs: `n` descriptors; n == 1 is a real rank, n > 1 emulates n ranks in one
+// cooperative launch on the current device (`emu_table` = device buffer of
+// n * cb_sizeof_ag_gemm_params() bytes that the call fills).
+int cb_ag_gemm(const CbAgGemmDesc* descs, int n, void* emu_table, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n < 1 || n > CB_MAX_RANKS) return -1;
+  AgGemmParams hp[CB_MAX_RANKS];
+  for (int i = 0; i < n; ++i)
+    if (build_ag_params(descs[i], &hp[i]) != 0) return -1;
+  const AgGemmParams* emu = nullptr;
+  if (n > 1) {
+    if (emu_table == nullptr) {
+      set_last_error("ag_gemm: emulation needs a device table");
+      return -1;
+    }
+    cudaError_t e = cudaMemcpyAsync(emu_table, hp, sizeof(AgGemmParams) * n,
+                                    cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) {
+      set_last_error(std::string("ag_gemm: table copy: ") + cudaGetErrorString(e));
+      return -1;
+    }
+    // hp lives on this stack frame: make sure the copy has read it.
+    cudaStreamSynchronize(st);
+    emu = static_cast<const AgGemmParams*>(emu_table);
+  }
+  const CbAgGemmDesc& d = descs[0];
+  if (d.fp8) {
+    if (d.bn == 256) return launch_ag<GemmCfg<256, 4, true>>(hp[0], emu, n, d.ctas_per_rank, st);
+    if (d.bn == 128) return launch_ag<GemmCfg<128, 6, true>>(hp[0], emu, n, d.ctas_per_rank, st);
+  } else {
+    if (d.bn == 256) return launch_ag<GemmCfg<256, 4, false>>(hp[0], emu, n, d.ctas_per_rank, st);
+    if (d.bn == 128) return launch_ag<GemmCfg<128, 6, false>>(hp[0], emu, n, d.ctas_per_rank, st);
+  }
+  set_last_error("ag_gemm: bn must be 128 or 256");
+  return -1;
+}
+
+}  // extern "C"

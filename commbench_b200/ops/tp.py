@@ -1,0 +1,320 @@
+"""Tensor-parallel fused GEMM + collective ops (one kernel each):
+
+* :class:`AgGemm`  - all-gather(A rows) -> GEMM       (column-parallel linear)
+* :class:`GemmRs`  - GEMM -> reduce-scatter(rows)      (row-parallel linear)
+* :class:`GemmAr`  - GEMM -> all-reduce                (row-parallel linear, decode shapes)
+
+Each object owns its symmetric staging buffers and flags (allocated once,
+collectively), so a call is a single launch with no host synchronisation.
+Weights follow the ``nn.Linear`` layout ``[out_features, in_features]``.
+
+Reference counterparts: AllGatherMatmul / matmul_reduce_scatter / GEMM+AR of
+datasets/example051_thunderkitten_ag_gemm_easy/nv/empty_thunderkitten_ag_gemm.cu:479-511,
+datasets/example054_thunderkitten_gemm_rs_easy/nv/empty_thunderkitten_gemm_rs.cu:450-487,
+datasets/example053_thunderkitten_gemm_ar_easy/nv/empty_thunderkitten_gemm_ar.cu:491-536.
+
+Every class also accepts an :class:`~commbench_b200.runtime.context.EmuContext`; tensors are
+then lists (one per virtual rank) and the call is one cooperative launch on one GPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import _native as N
+from ..config import get_config
+from ..runtime.context import CommContext, CommError, EmuContext
+
+_P8 = C.c_void_p * N.MAX_RANKS
+
+
+class _AgDesc(C.Structure):
+    _fields_ = [
+        ("rank", C.c_int), ("world", C.c_int), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
+        ("fp8", C.c_int), ("alpha", C.c_float), ("bn", C.c_int), ("num_comm_ctas", C.c_int),
+        ("parts", C.c_int), ("ctas_per_rank", C.c_int),
+        ("a_local", C.c_void_p), ("b", C.c_void_p), ("c", C.c_void_p),
+        ("a_full_peer", _P8 * 2), ("a_full_mc", C.c_void_p * 2),
+        ("flags_peer", _P8), ("flags_mc", C.c_void_p),
+        ("seq", C.c_void_p), ("status", C.c_void_p), ("timeout_ns", C.c_ulonglong),
+    ]
+
+
+class _RsDesc(C.Structure):
+    _fields_ = [
+        ("rank", C.c_int), ("world", C.c_int), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
+        ("fp8", C.c_int), ("alpha", C.c_float), ("bn", C.c_int), ("ctas_per_rank", C.c_int),
+        ("a", C.c_void_p), ("b", C.c_void_p), ("out", C.c_void_p),
+        ("stage_peer", _P8 * 2), ("flags_peer", _P8),
+        ("seq", C.c_void_p), ("status", C.c_void_p), ("timeout_ns", C.c_ulonglong),
+    ]
+
+
+class _ArDesc(C.Structure):
+    _fields_ = [
+        ("rank", C.c_int), ("world", C.c_int), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
+        ("fp8", C.c_int), ("alpha", C.c_float), ("bn", C.c_int), ("oneshot", C.c_int),
+        ("slots", C.c_int), ("ctas_per_rank", C.c_int),
+        ("a", C.c_void_p), ("b", C.c_void_p), ("out", C.c_void_p),
+        ("stage_peer", _P8 * 2), ("result_peer", _P8 * 2), ("result_mc", C.c_void_p * 2),
+        ("flags_peer", _P8), ("seq", C.c_void_p), ("status", C.c_void_p),
+        ("timeout_ns", C.c_ulonglong),
+    ]
+
+
+def _esz(dtype) -> int:
+    return 1 if dtype == torch.float8_e4m3fn else 2
+
+
+class _Sym:
+    """A symmetric buffer seen uniformly for real and emulated contexts."""
+
+    def __init__(self, ctx, nbytes: int, zero: bool = False):
+        self.nbytes = nbytes
+        if isinstance(ctx, EmuContext):
+            self.tensors = ctx.alloc(nbytes)
+            self.ptrs = [t.data_ptr() for t in self.tensors]
+            self.mc = 0
+        else:
+            blk = ctx.alloc(nbytes)
+            self.tensors = [blk.local]
+            self.ptrs = blk.peer_ptrs
+            self.mc = blk.mc_ptr
+            if zero:
+                blk.local.zero_()
+
+    def local(self, ctx, r: int = 0) -> torch.Tensor:
+        return self.tensors[r] if isinstance(ctx, EmuContext) else self.tensors[0]
+
+
+def _fill_p8(arr, ptrs):
+    for r in range(N.MAX_RANKS):
+        arr[r] = ptrs[r] if r < len(ptrs) else 0
+
+
+def _sm_count(device) -> int:
+    return torch.cuda.get_device_properties(device).multi_processor_count
+
+
+class _FusedBase:
+    def __init__(self, ctx):
+        self.ctx = ctx
+        self.lib = ctx.lib
+        self.emu = isinstance(ctx, EmuContext)
+        self.world = ctx.world
+        self.nseq = ctx.world if self.emu else 1
+        # {call counter, done CTAs} per (virtual) rank, local memory
+        self.seq = [torch.zeros(4, dtype=torch.int32, device=ctx.device) for _ in range(self.nseq)]
+        self.calls = 0
+        self._table = None
+
+    def _status_ptr(self, r: int) -> int:
+        return self.ctx.comms[r].status if self.emu else self.ctx.comm.status
+
+    def _ctas(self) -> int:
+        sms = _sm_count(self.ctx.device)
+        return sms // self.world if self.emu else sms
+
+    def _sync_init(self):
+        torch.cuda.synchronize(self.ctx.device)
+        if not self.emu:
+            self.ctx.host_barrier()
+
+    def _emu_table(self, nbytes: int):
+        if self._table is None or self._table.numel() < nbytes:
+            self._table = torch.empty(nbytes, dtype=torch.uint8, device=self.ctx.device)
+        return C.c_void_p(self._table.data_ptr())
+
+
+class AgGemm(_FusedBase):
+    """``C[M, N_local] = all_gather_rows(A_local)[M, K] @ B[N_local, K].T`` in one kernel."""
+
+    def __init__(self, ctx, max_m: int, k: int, dtype=torch.bfloat16):
+        super().__init__(ctx)
+        self.max_m, self.k, self.dtype = max_m, k, dtype
+        nbytes = max_m * k * _esz(dtype)
+        self.a_full = [_Sym(ctx, nbytes), _Sym(ctx, nbytes)]
+        self.flags = _Sym(ctx, 2 * 1024 * 4, zero=True)
+        self._sync_init()
+
+    def _desc(self, r, a_local, b, c, M, Nn, K, alpha, bn, comm_ctas, parts) -> _AgDesc:
+        d = _AgDesc()
+        d.rank, d.world, d.M, d.N, d.K = r, self.world, M, Nn, K
+        d.fp8 = int(self.dtype == torch.float8_e4m3fn)
+        d.alpha, d.bn = alpha, bn
+        d.num_comm_ctas, d.parts, d.ctas_per_rank = comm_ctas, parts, self._ctas()
+        d.a_local, d.b, d.c = a_local.data_ptr(), b.data_ptr(), c.data_ptr()
+        for par in range(2):
+            _fill_p8(d.a_full_peer[par], self.a_full[par].ptrs)
+            d.a_full_mc[par] = self.a_full[par].mc
+        _fill_p8(d.flags_peer, self.flags.ptrs)
+        d.flags_mc = self.flags.mc
+        d.seq = self.seq[r if self.emu else 0].data_ptr()
+        d.status = self._status_ptr(r)
+        d.timeout_ns = self.ctx.timeout_ns
+        return d
+
+    def __call__(self, a_local, b, out=None, alpha: float = 1.0, bn: int = 256,
+                 comm_ctas: int | None = None, parts: int = 8, stream=None):
+        cfg = get_config()
+        if comm_ctas is None:
+            comm_ctas = cfg.ag_gemm_comm_ctas if self.world > 1 else 0
+        if self.emu:
+            comm_ctas = min(comm_ctas, 4) if self.world > 1 else 0
+            a0, b0 = a_local[0], b[0]
+        else:
+            a0, b0 = a_local, b
+        Ml, K = a0.shape
+        Nn = b0.shape[0]
+        M = Ml * self.world
+        if M > self.max_m or K != self.k:
+            raise CommError(f"AgGemm built for M<={self.max_m}, K={self.k}; got M={M}, K={K}")
+        if self.emu:
+            outs = out or [torch.empty((M, Nn), dtype=torch.bfloat16, device=a0.device)
+                           for _ in range(self.world)]
+            descs = (_AgDesc * self.world)(*[
+                self._desc(r, a_local[r], b[r], outs[r], M, Nn, K, alpha, bn, comm_ctas, parts)
+                for r in range(self.world)])
+            table = self._emu_table(self.lib.cb_sizeof_ag_gemm_params() * self.world)
+            rc = self.lib.cb_ag_gemm(descs, self.world, table, N.stream_ptr(stream))
+            result = outs
+        else:
+            if out is None:
+                out = torch.empty((M, Nn), dtype=torch.bfloat16, device=a0.device)
+            descs = (_AgDesc * 1)(self._desc(self.ctx.rank, a_local, b, out, M, Nn, K, alpha, bn,
+                                             comm_ctas, parts))
+            rc = self.lib.cb_ag_gemm(descs, 1, None, N.stream_ptr(stream))
+            result = out
+        if rc != 0:
+            raise CommError(f"ag_gemm failed: {N.last_error()}")
+        self.calls += 1
+        return result
+
+
+class GemmRs(_FusedBase):
+    """``out[M/W, N] = reduce_scatter_rows(A[M, K_local] @ B[N, K_local].T)`` in one kernel."""
+
+    def __init__(self, ctx, max_m: int, max_n: int):
+        super().__init__(ctx)
+        self.max_m, self.max_n = max_m, max_n
+        nbytes = max_m * max_n * 2  # W sources x M/W rows x N bf16
+        self.stage = [_Sym(ctx, nbytes), _Sym(ctx, nbytes)]
+        self.flags = _Sym(ctx, 2 * 8192 * 4, zero=True)
+        self._sync_init()
+
+    def _desc(self, r, a, b, out, M, Nn, K, alpha, bn, fp8) -> _RsDesc:
+        d = _RsDesc()
+        d.rank, d.world, d.M, d.N, d.K = r, self.world, M, Nn, K
+        d.fp8, d.alpha, d.bn, d.ctas_per_rank = int(fp8), alpha, bn, self._ctas()
+        d.a, d.b, d.out = a.data_ptr(), b.data_ptr(), out.data_ptr()
+        for par in range(2):
+            _fill_p8(d.stage_peer[par], self.stage[par].ptrs)
+        _fill_p8(d.flags_peer, self.flags.ptrs)
+        d.seq = self.seq[r if self.emu else 0].data_ptr()
+        d.status = self._status_ptr(r)
+        d.timeout_ns = self.ctx.timeout_ns
+        return d
+
+    def __call__(self, a, b, out=None, alpha: float = 1.0, bn: int = 256, stream=None):
+        a0, b0 = (a[0], b[0]) if self.emu else (a, b)
+        M, K = a0.shape
+        Nn = b0.shape[0]
+        if M > self.max_m or Nn > self.max_n:
+            raise CommError(f"GemmRs built for M<={self.max_m}, N<={self.max_n}")
+        fp8 = a0.dtype == torch.float8_e4m3fn
+        Ml = M // self.world
+        if self.emu:
+            outs = out or [torch.empty((Ml, Nn), dtype=torch.bfloat16, device=a0.device)
+                           for _ in range(self.world)]
+            descs = (_RsDesc * self.world)(*[
+                self._desc(r, a[r], b[r], outs[r], M, Nn, K, alpha, bn, fp8)
+                for r in range(self.world)])
+            table = self._emu_table(self.lib.cb_sizeof_gemm_rs_params() * self.world)
+            rc = self.lib.cb_gemm_rs(descs, self.world, table, N.stream_ptr(stream))
+            result = outs
+        else:
+            if out is None:
+                out = torch.empty((Ml, Nn), dtype=torch.bfloat16, device=a0.device)
+            descs = (_RsDesc * 1)(self._desc(self.ctx.rank, a, b, out, M, Nn, K, alpha, bn, fp8))
+            rc = self.lib.cb_gemm_rs(descs, 1, None, N.stream_ptr(stream))
+            result = out
+        if rc != 0:
+            raise CommError(f"gemm_rs failed: {N.last_error()}")
+        self.calls += 1
+        return result
+
+
+class GemmAr(_FusedBase):
+    """``out[M, N] = all_reduce(A[M, K_local] @ B[N, K_local].T)`` in one kernel."""
+
+    def __init__(self, ctx, max_m: int, max_n: int):
+        super().__init__(ctx)
+        self.max_m, self.max_n = max_m, max_n
+        # Worst case: one-shot, 64-wide tiles: every tile has a slot for every source.
+        self.max_tiles = ((max_m + 127) // 128) * ((max_n + 63) // 64)
+        self.stage_bytes = self.world * self.max_tiles * 128 * 64 * 2
+        self.stage = [_Sym(ctx, self.stage_bytes), _Sym(ctx, self.stage_bytes)]
+        self.result = [_Sym(ctx, max_m * max_n * 2), _Sym(ctx, max_m * max_n * 2)]
+        self.flags = _Sym(ctx, self.lib.cb_gemm_ar_flag_words() * 4, zero=True)
+        self._sync_init()
+
+    def _desc(self, r, a, b, out, M, Nn, K, alpha, bn, fp8, oneshot) -> _ArDesc:
+        d = _ArDesc()
+        d.rank, d.world, d.M, d.N, d.K = r, self.world, M, Nn, K
+        d.fp8, d.alpha, d.bn, d.oneshot = int(fp8), alpha, bn, int(oneshot)
+        d.slots = self.stage_bytes // (self.world * 128 * bn * 2)
+        d.ctas_per_rank = self._ctas()
+        d.a, d.b = a.data_ptr(), b.data_ptr()
+        d.out = out.data_ptr() if out is not None else 0
+        for par in range(2):
+            _fill_p8(d.stage_peer[par], self.stage[par].ptrs)
+            _fill_p8(d.result_peer[par], self.result[par].ptrs)
+            d.result_mc[par] = self.result[par].mc
+        _fill_p8(d.flags_peer, self.flags.ptrs)
+        d.seq = self.seq[r if self.emu else 0].data_ptr()
+        d.status = self._status_ptr(r)
+        d.timeout_ns = self.ctx.timeout_ns
+        return d
+
+    @staticmethod
+    def pick_bn(M: int, Nn: int, sms: int) -> int:
+        mb = (M + 127) // 128
+        for bn in (256, 128):
+            if mb * ((Nn + bn - 1) // bn) >= 2 * sms:
+                return bn
+        return 64
+
+    def __call__(self, a, b, out=None, alpha: float = 1.0, bn: int | None = None,
+                 oneshot: bool | None = None, stream=None):
+        a0, b0 = (a[0], b[0]) if self.emu else (a, b)
+        M, K = a0.shape
+        Nn = b0.shape[0]
+        if M > self.max_m or Nn > self.max_n:
+            raise CommError(f"GemmAr built for M<={self.max_m}, N<={self.max_n}")
+        fp8 = a0.dtype == torch.float8_e4m3fn
+        cfg = get_config()
+        if oneshot is None:
+            oneshot = M <= cfg.gemm_ar_oneshot_max_m
+        if bn is None:
+            bn = self.pick_bn(M, Nn, self._ctas())
+        if self.emu:
+            outs = out or [torch.empty((M, Nn), dtype=torch.bfloat16, device=a0.device)
+                           for _ in range(self.world)]
+            descs = (_ArDesc * self.world)(*[
+                self._desc(r, a[r], b[r], outs[r], M, Nn, K, alpha, bn, fp8, oneshot)
+                for r in range(self.world)])
+            table = self._emu_table(self.lib.cb_sizeof_gemm_ar_params() * self.world)
+            rc = self.lib.cb_gemm_ar(descs, self.world, table, N.stream_ptr(stream))
+            result = outs
+        else:
+            if out is None:
+                out = torch.empty((M, Nn), dtype=torch.bfloat16, device=a0.device)
+            descs = (_ArDesc * 1)(self._desc(self.ctx.rank, a, b, out, M, Nn, K, alpha, bn, fp8,
+                                             oneshot))
+            rc = self.lib.cb_gemm_ar(descs, 1, None, N.stream_ptr(stream))
+            result = out
+        if rc != 0:
+            raise CommError(f"gemm_ar failed: {N.last_error()}")
+        self.calls += 1
+        return result

@@ -1,0 +1,77 @@
+"""Fused GEMM+collective kernels with virtual ranks on ONE GPU (one cooperative launch),
+against plain PyTorch fp32 references."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(shape, seed, scale=0.25):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, device="cuda", generator=g) * scale).bfloat16()
+
+
+def _close(out, ref, tol=1.5e-2):
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item() + 1e-6
+    assert err / scale < tol, f"max abs err {err} vs scale {scale}"
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("bn", [256, 128])
+def test_emu_ag_gemm(native_lib, world, bn):
+    from commbench_b200.ops.tp import AgGemm
+    from commbench_b200.runtime.context import EmuContext
+
+    Ml, K, Nn = 256, 512, 384
+    ctx = EmuContext(world)
+    op = AgGemm(ctx, max_m=Ml * world, k=K)
+    a = [_rand((Ml, K), 10 + r) for r in range(world)]
+    b = [_rand((Nn, K), 50 + r) for r in range(world)]
+    full = torch.cat(a, dim=0).float()
+    for it in range(3):   # three calls: both buffer parities and the flag reset are exercised
+        outs = op(a, b, bn=bn)
+        ctx.check_status()
+        for r in range(world):
+            _close(outs[r], full @ b[r].float().t())
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_emu_gemm_rs(native_lib, world):
+    from commbench_b200.ops.tp import GemmRs
+    from commbench_b200.runtime.context import EmuContext
+
+    M, K, Nn = 256 * world, 256, 384
+    ctx = EmuContext(world)
+    op = GemmRs(ctx, max_m=M, max_n=Nn)
+    a = [_rand((M, K), 100 + r) for r in range(world)]
+    b = [_rand((Nn, K), 200 + r) for r in range(world)]
+    total = sum(a[r].float() @ b[r].float().t() for r in range(world))
+    Ml = M // world
+    for it in range(3):
+        outs = op(a, b, bn=128 if it == 1 else 256)
+        ctx.check_status()
+        for r in range(world):
+            _close(outs[r], total[r * Ml:(r + 1) * Ml])
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("oneshot", [True, False])
+@pytest.mark.parametrize("M", [16, 200, 512])
+def test_emu_gemm_ar(native_lib, world, oneshot, M):
+    from commbench_b200.ops.tp import GemmAr
+    from commbench_b200.runtime.context import EmuContext
+
+    K, Nn = 256, 1024
+    ctx = EmuContext(world)
+    op = GemmAr(ctx, max_m=512, max_n=Nn)
+    a = [_rand((M, K), 300 + r) for r in range(world)]
+    b = [_rand((Nn, K), 400 + r) for r in range(world)]
+    total = sum(a[r].float() @ b[r].float().t() for r in range(world))
+    for it in range(3):
+        outs = op(a, b, oneshot=oneshot, bn=64 if it < 2 else 128)
+        ctx.check_status()
+        for r in range(world):
+            _close(outs[r], total)
+        for r in range(1, world):
+            assert torch.equal(outs[r], outs[0])

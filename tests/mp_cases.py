@@ -1,0 +1,206 @@
+"""Multi-process checks run under torch.distributed.run (one rank per GPU).
+
+Prints one JSON line per check from rank 0 ("check", "ok", "detail") and exits non-zero
+if any check failed on any rank.  Usage: torchrun ... tests/mp_cases.py [--quick]
+"""
+import json
+import os
+import sys
+import traceback
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+RESULTS = []
+
+
+def report(name, ok, detail=""):
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    ok_all = bool(flag.item())
+    RESULTS.append(ok_all)
+    if dist.get_rank() == 0:
+        print(json.dumps({"check": name, "ok": ok_all, "detail": str(detail)[:300]}), flush=True)
+
+
+def guarded(name):
+    def deco(fn):
+        def run(*a, **k):
+            try:
+                fn(*a, **k)
+            except Exception as e:  # noqa: BLE001
+                traceback.print_exc()
+                report(name, False, repr(e))
+        return run
+    return deco
+
+
+def uniform(shape, seed, dtype=torch.bfloat16):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.rand(shape, device="cuda", generator=g) * 2 - 1).to(dtype)
+
+
+def gather_all(x):
+    outs = [torch.empty_like(x) for _ in range(dist.get_world_size())]
+    dist.all_gather(outs, x)
+    return outs
+
+
+def main():
+    dist.init_process_group("nccl")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    from commbench_b200.ops import collectives as coll
+    from commbench_b200.ops.tp import AgGemm, GemmAr, GemmRs
+    from commbench_b200.runtime.context import CommContext
+
+    ctx = CommContext(heap_bytes=1 << 30)
+    report("context", True, f"mode={ctx.mode} multicast={ctx.has_multicast}")
+
+    @guarded("all_reduce")
+    def t_all_reduce():
+        algos = ["oneshot", "twoshot"] + (["nvls"] if ctx.has_multicast else [])
+        for numel in (8, 2048, 1 << 16, (1 << 20) + 8, 1 << 24):
+            x = uniform((numel,), rank)
+            ref = sum(t.float() for t in gather_all(x))
+            for algo in algos:
+                y = coll.all_reduce(ctx, x.clone(), algo=algo)
+                ctx.check_status()
+                ok = torch.allclose(y.float(), ref, atol=5e-2, rtol=5e-2)
+                report(f"all_reduce/{algo}/{numel}", ok, (y.float() - ref).abs().max().item())
+        # symmetric, zero-copy, in place
+        t, _ = ctx.empty((1 << 20,), torch.bfloat16)
+        for algo in algos[1:]:
+            t.copy_(uniform((1 << 20,), 100 + rank))
+            ref = sum(u.float() for u in gather_all(t.clone()))
+            torch.cuda.synchronize(); dist.barrier()
+            coll.all_reduce(ctx, t, algo=algo)
+            ctx.check_status()
+            report(f"all_reduce/symmetric/{algo}", torch.allclose(t.float(), ref, atol=5e-2, rtol=5e-2))
+        xf = uniform((4099,), 7 + rank, torch.float32)
+        ref = sum(t.double() for t in gather_all(xf))
+        y = coll.all_reduce(ctx, xf.clone(), algo="auto")
+        ctx.check_status()
+        report("all_reduce/fp32", torch.allclose(y.double(), ref, atol=1e-5, rtol=1e-5))
+
+    @guarded("all_gather")
+    def t_all_gather():
+        x = uniform((300, 72), 20 + rank)
+        ref = torch.cat(gather_all(x), dim=0)
+        y = coll.all_gather(ctx, x)
+        ctx.check_status()
+        report("all_gather/pull", torch.equal(y, ref))
+        out, _ = ctx.empty((300 * world, 72), torch.bfloat16)
+        coll.all_gather(ctx, x, out=out)
+        ctx.check_status()
+        report("all_gather/push", torch.equal(out, ref))
+
+    @guarded("reduce_scatter")
+    def t_reduce_scatter():
+        x = uniform((world * 128, 256), 30 + rank)
+        total = sum(t.float() for t in gather_all(x))
+        ref = total[rank * 128:(rank + 1) * 128]
+        y = coll.reduce_scatter(ctx, x, use_nvls=False)
+        ctx.check_status()
+        report("reduce_scatter/pull", torch.allclose(y.float(), ref, atol=5e-2, rtol=5e-2))
+        if ctx.has_multicast:
+            y = coll.reduce_scatter(ctx, x, use_nvls=True)
+            ctx.check_status()
+            report("reduce_scatter/nvls", torch.allclose(y.float(), ref, atol=5e-2, rtol=5e-2))
+
+    @guarded("all_to_all")
+    def t_all_to_all():
+        x = uniform((world * 64, 128), 40 + rank)
+        ref = torch.empty_like(x)
+        dist.all_to_all_single(ref, x)
+        y = coll.all_to_all(ctx, x)
+        ctx.check_status()
+        report("all_to_all/flat", torch.equal(y, ref))
+        B, Sl, H, D = 1, 96, 8 * world, 128
+        q = uniform((B, Sl, H, D), 50 + rank)
+        full = torch.cat(gather_all(q), dim=1)
+        Hl = H // world
+        y = coll.all_to_all_4d(ctx, q, to_heads=True)
+        ctx.check_status()
+        report("all_to_all/4d_fwd", torch.equal(y, full[:, :, rank * Hl:(rank + 1) * Hl].contiguous()))
+        z = coll.all_to_all_4d(ctx, y, to_heads=False)
+        ctx.check_status()
+        report("all_to_all/4d_roundtrip", torch.equal(z, q))
+
+    @guarded("broadcast")
+    def t_broadcast():
+        for root in (0, world - 1):
+            x = uniform((5000,), 60 + rank, torch.float32)
+            ref = x.clone()
+            dist.broadcast(ref, src=root)
+            coll.broadcast(ctx, x, root=root)
+            ctx.check_status()
+            report(f"broadcast/root{root}", torch.equal(x, ref))
+        coll.barrier(ctx, iters=5)
+        ctx.check_status()
+        if ctx.has_multicast:
+            coll.barrier(ctx, iters=5, use_nvls=True)
+            ctx.check_status()
+        report("barrier", True)
+
+    def rnd(shape, seed, scale=0.25):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        return (torch.randn(shape, device="cuda", generator=g) * scale).bfloat16()
+
+    def close(out, ref, tol=1.5e-2):
+        return ((out.float() - ref).abs().max() / (ref.abs().max() + 1e-6)).item() < tol
+
+    @guarded("ag_gemm")
+    def t_ag_gemm():
+        Ml, K, Nn = 512, 1024, 768
+        op = AgGemm(ctx, max_m=Ml * world, k=K)
+        a, b = rnd((Ml, K), 70 + rank), rnd((Nn, K), 80 + rank)
+        ref = torch.cat(gather_all(a), dim=0).float() @ b.float().t()
+        for it in range(4):
+            c = op(a, b, bn=256 if it % 2 == 0 else 128)
+            ctx.check_status()
+            report(f"ag_gemm/{it}", close(c, ref))
+
+    @guarded("gemm_rs")
+    def t_gemm_rs():
+        M, K, Nn = 256 * world, 512, 768
+        op = GemmRs(ctx, max_m=M, max_n=Nn)
+        a, b = rnd((M, K), 90 + rank), rnd((Nn, K), 95 + rank)
+        part = (a.float() @ b.float().t())
+        dist.all_reduce(part)
+        Ml = M // world
+        for it in range(4):
+            o = op(a, b)
+            ctx.check_status()
+            report(f"gemm_rs/{it}", close(o, part[rank * Ml:(rank + 1) * Ml]))
+
+    @guarded("gemm_ar")
+    def t_gemm_ar():
+        K, Nn = 512, 2048
+        op = GemmAr(ctx, max_m=1024, max_n=Nn)
+        for M in (16, 128, 1024):
+            a, b = rnd((M, K), 110 + rank), rnd((Nn, K), 120 + rank)
+            part = (a.float() @ b.float().t())
+            dist.all_reduce(part)
+            for oneshot in (True, False):
+                for it in range(3):
+                    o = op(a, b, oneshot=oneshot)
+                    ctx.check_status()
+                    report(f"gemm_ar/M{M}/oneshot{int(oneshot)}/{it}", close(o, part))
+
+    t_all_reduce(); t_all_gather(); t_reduce_scatter(); t_all_to_all(); t_broadcast()
+    t_ag_gemm(); t_gemm_rs(); t_gemm_ar()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ctx.close()
+    ok = all(RESULTS)
+    if rank == 0:
+        print(json.dumps({"summary": "PASS" if ok else "FAIL", "checks": len(RESULTS)}), flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if ok else 2)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,104 @@
+"""Tensor-parallel MLP block built from the fused kernels (the flagship step of ``bench.py``).
+
+Sequence-parallel in, sequence-parallel out (Megatron "SP + TP" layout):
+
+    x_local [T/W, H]  --AG->GEMM-->  h [T, I/W]  --GEMM->RS-->  y_local [T/W, H]
+
+with ``W1`` column-sharded ``[I/W, H]`` and ``W2`` row-sharded ``[H, I/W]``.  The shapes of
+the headline configuration (T=8192 tokens, H=8192, I=28672) are the ones the reference's
+fused examples sweep towards (datasets/example051_thunderkitten_ag_gemm_easy/nv/
+empty_thunderkitten_ag_gemm.cu:539-543 and datasets/example054_thunderkitten_gemm_rs_easy/nv/
+empty_thunderkitten_gemm_rs.cu:514), which stop at one GEMM each; chaining the two gives a
+complete transformer MLP without any standalone collective.
+
+``forward``          fused path (2 kernel launches of this library; 2 plain tcgen05 GEMMs at W=1)
+``forward_unfused``  the baseline: NCCL all-gather + cuBLAS matmul + cuBLAS matmul + NCCL
+                     reduce-scatter on the same tensors
+``forward_host``     end-to-end call: pinned host tokens in, scalar metric out
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops.gemm import gemm
+from ..ops.tp import AgGemm, GemmRs
+
+
+class TPMLP:
+    def __init__(self, ctx, hidden: int, intermediate: int, max_tokens: int, seed: int = 0,
+                 activation: str | None = None):
+        self.ctx = ctx
+        self.world = ctx.world
+        self.rank = ctx.rank
+        self.hidden, self.intermediate, self.max_tokens = hidden, intermediate, max_tokens
+        if intermediate % self.world or max_tokens % (128 * self.world):
+            raise ValueError("intermediate must divide by world and tokens by 128*world")
+        self.i_local = intermediate // self.world
+        dev = ctx.device
+        g = torch.Generator(device=dev).manual_seed(seed * 1000 + self.rank)
+        # random-init weights N(0, 0.02): this rank's shards only
+        self.w1 = (torch.randn(self.i_local, hidden, device=dev, generator=g) * 0.02).bfloat16()
+        self.w2 = (torch.randn(hidden, self.i_local, device=dev, generator=g) * 0.02).bfloat16()
+        self.activation = activation
+        if self.world > 1:
+            self.ag = AgGemm(ctx, max_m=max_tokens, k=hidden)
+            self.rs = GemmRs(ctx, max_m=max_tokens, max_n=hidden)
+        self.h = torch.empty(max_tokens, self.i_local, dtype=torch.bfloat16, device=dev)
+        self.y = torch.empty(max_tokens // self.world, hidden, dtype=torch.bfloat16, device=dev)
+        self._x_dev = torch.empty(max_tokens // self.world, hidden, dtype=torch.bfloat16, device=dev)
+        self._metric_host = torch.empty(1, dtype=torch.float32).pin_memory() \
+            if torch.cuda.is_available() else torch.empty(1)
+        self.launches_per_step = 2
+
+    # ---------------------------------------------------------------- fused path
+    def forward(self, x_local: torch.Tensor) -> torch.Tensor:
+        T = x_local.shape[0] * self.world
+        h = self.h[:T]
+        y = self.y[:x_local.shape[0]]
+        if self.world == 1:
+            gemm(x_local, self.w1, out=h)
+            if self.activation == "silu":
+                torch.nn.functional.silu(h, inplace=True)
+            gemm(h, self.w2, out=y)
+            return y
+        self.ag(x_local, self.w1, out=h)
+        if self.activation == "silu":
+            torch.nn.functional.silu(h, inplace=True)
+        self.rs(h, self.w2, out=y)
+        return y
+
+    # ------------------------------------------------------------ unfused baseline
+    def forward_unfused(self, x_local: torch.Tensor) -> torch.Tensor:
+        import torch.distributed as dist
+
+        if self.world == 1:
+            h = torch.matmul(x_local, self.w1.t())
+            if self.activation == "silu":
+                torch.nn.functional.silu(h, inplace=True)
+            return torch.matmul(h, self.w2.t())
+        x_full = torch.empty(x_local.shape[0] * self.world, self.hidden, dtype=x_local.dtype,
+                             device=x_local.device)
+        dist.all_gather_into_tensor(x_full, x_local)
+        h = torch.matmul(x_full, self.w1.t())
+        if self.activation == "silu":
+            torch.nn.functional.silu(h, inplace=True)
+        part = torch.matmul(h, self.w2.t())
+        y = torch.empty(x_local.shape[0], self.hidden, dtype=x_local.dtype, device=x_local.device)
+        dist.reduce_scatter_tensor(y, part)
+        return y
+
+    # ---------------------------------------------------------------- end to end
+    def forward_host(self, x_host_pinned: torch.Tensor, fused: bool = True) -> float:
+        """Tokens arrive in pinned host memory; returns mean(|y|) read back to the host."""
+        n = x_host_pinned.shape[0]
+        xd = self._x_dev[:n]
+        xd.copy_(x_host_pinned, non_blocking=True)
+        y = self.forward(xd) if fused else self.forward_unfused(xd)
+        m = y.float().abs().mean()
+        self._metric_host.copy_(m.reshape(1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return float(self._metric_host[0])
+
+    def flops(self, tokens: int) -> float:
+        """FLOPs of one step over the WHOLE job (all ranks)."""
+        return 2.0 * 2.0 * tokens * self.hidden * self.intermediate

@@ -43,7 +43,7 @@ def reference_arm() -> int:
 class ClockSampler:
     """Samples SM clocks and throttle reasons of the local GPU with NVML (read-only)."""
 
-    def __init__(self, index: int, period_s: float = 0.05):
+    def __init__(self, index: int, period_s: float = 0.02):
         self.index, self.period = index, period_s
         self.samples, self.reasons = [], set()
         self.max_mhz = None

@@ -1,8 +1,8 @@
 // Fused all-gather -> GEMM:  C[M, N_local] = allgather_rows(A_local)[M, K] * B[N_local, K]^T
 //
 // ONE kernel per rank.  A few CTAs ("comm CTAs") push this rank's A rows into
-// every peer's gathered buffer with TMA bulk copies and raise a per-row-block
-// flag on the peer; the other CTAs run the tcgen05 GEMM, doing the tiles of
+// every peer's gathered buffer (16-byte stores over NVLink, or one multimem.st
+// per vector through the switch) and raise a per-row-block flag on the peer; the other CTAs run the tcgen05 GEMM, doing the tiles of
 // their own rows first (straight from A_local) and then, in arrival order, the
 // tiles of remote rows as soon as the row block's flag is up.  Transfer and
 // math overlap row block by row block.
@@ -24,10 +24,6 @@
 namespace cb {
 
 static constexpr int kAgMaxRowBlocks = 1024;  // flags per parity
-static constexpr int kCommWorkers = 3;        // worker warps per comm CTA
-static constexpr int kCommBufs = 4;           // staging buffers per worker
-static constexpr int kCommChunk = 16384;      // bytes per bulk copy
-static constexpr int kCommPrefetch = 2;
 
 struct AgGemmParams {
   CUtensorMap tm_a_local;
@@ -101,6 +97,7 @@ struct AgPolicy {
     fence_proxy_async();
     return true;
   }
+  static constexpr bool kDirect = false;  // C is local: TMA-store epilogue
   __device__ static void store_box(const AgRt& r, int m_blk, int n_blk, int row, int col,
                                    const void* smem_box) {
     tma_store_2d(&r.p->tm_c, smem_box, n_blk * Cfg::BN + col, m_blk * Cfg::BM + row);
@@ -108,77 +105,64 @@ struct AgPolicy {
   __device__ static void tile_done(const AgRt&, int, int, int) {}
 };
 
-// Comm CTA: worker warps (lane 0 each) stream pieces of the local A rows
-// global -> shared -> every peer, then bump the row block's flag on the peers.
-__device__ __forceinline__ void ag_comm_cta(const AgGemmParams& p, uint32_t parity, int comm_cta,
-                                            uint8_t* smem) {
-  __shared__ uint64_t bars[kCommWorkers][kCommBufs];
-  const int warp = threadIdx.x >> 5;
-  if (warp >= kCommWorkers || (threadIdx.x & 31) != 0) return;
-  uint8_t* bufs = smem + warp * (kCommBufs * kCommChunk);
-  for (int b = 0; b < kCommBufs; ++b) mbar_init(&bars[warp][b], 1);
-  fence_mbar_init();
-  const int worker = comm_cta * kCommWorkers + warp;
-  const int nworkers = p.num_comm_ctas * kCommWorkers;
+// Comm CTA: all threads stream pieces of the local A rows to every peer with
+// 16-byte loads and stores (one multimem.st per vector when a multicast object is
+// bound, W-1 plain peer stores otherwise), then bump the row block's flag on the
+// peers.  Load/store traffic from a handful of CTAs saturates NVLink here, which
+// bulk (TMA) copies issued from the same number of SMs did not.
+__device__ __forceinline__ void ag_comm_cta(const AgGemmParams& p, uint32_t parity, int comm_cta) {
   const unsigned long long piece = p.row_block_bytes / p.parts;
-  const int nchunks = static_cast<int>((piece + kCommChunk - 1) / kCommChunk);
-  uint32_t gi = 0;  // running chunk counter: buffer = gi % kCommBufs, parity = (gi / kCommBufs) & 1
-  bool ok = true;
-  for (int item = worker; ok && item < p.blocks_per_rank * p.parts; item += nworkers) {
+  const unsigned long long piece_vecs = piece / 16ull;
+  const bool use_mc = p.a_full_mc[parity] != nullptr && p.flags_mc != nullptr;
+  for (int item = comm_cta; item < p.blocks_per_rank * p.parts; item += p.num_comm_ctas) {
     const int rb = item / p.parts;
     const int part = item % p.parts;
-    const uint8_t* src = p.a_local + rb * p.row_block_bytes + part * piece;
-    const unsigned long long dst_off =
-        static_cast<unsigned long long>(p.rank * p.blocks_per_rank + rb) * p.row_block_bytes +
-        part * piece;
-    auto chunk_bytes = [&](int i) -> uint32_t {
-      const unsigned long long left = piece - static_cast<unsigned long long>(i) * kCommChunk;
-      return static_cast<uint32_t>(left < kCommChunk ? left : kCommChunk);
-    };
-    auto issue_load = [&](int i) {
-      const uint32_t b = (gi + i) % kCommBufs;
-      mbar_arrive_expect_tx(&bars[warp][b], chunk_bytes(i));
-      bulk_load_1d(bufs + b * kCommChunk, src + static_cast<unsigned long long>(i) * kCommChunk,
-                   chunk_bytes(i), &bars[warp][b]);
-    };
-    for (int i = 0; i < kCommPrefetch && i < nchunks; ++i) issue_load(i);
-    for (int i = 0; i < nchunks; ++i) {
-      const uint32_t b = (gi + i) % kCommBufs;
-      const uint32_t par = ((gi + i) / kCommBufs) & 1u;
-      if (!mbar_wait(&bars[warp][b], par, nullptr, p.status, 0x500 + b)) {
-        ok = false;
-        break;
+    const uint4* src =
+        reinterpret_cast<const uint4*>(p.a_local + rb * p.row_block_bytes + part * piece);
+    const unsigned long long dst_vec =
+        (static_cast<unsigned long long>(p.rank * p.blocks_per_rank + rb) * p.row_block_bytes +
+         part * piece) / 16ull;
+    const unsigned long long T = blockDim.x;
+    unsigned long long i = threadIdx.x;
+    if (use_mc) {
+      uint4* mc = reinterpret_cast<uint4*>(p.a_full_mc[parity]) + dst_vec;
+      for (; i + 3ull * T < piece_vecs; i += 4ull * T) {
+        const uint4 v0 = ld_nc_v4(src + i), v1 = ld_nc_v4(src + i + T),
+                    v2 = ld_nc_v4(src + i + 2ull * T), v3 = ld_nc_v4(src + i + 3ull * T);
+        mm_st_v4(mc + i, v0);
+        mm_st_v4(mc + i + T, v1);
+        mm_st_v4(mc + i + 2ull * T, v2);
+        mm_st_v4(mc + i + 3ull * T, v3);
       }
-      const unsigned long long off = dst_off + static_cast<unsigned long long>(i) * kCommChunk;
-      if (p.a_full_mc[parity] != nullptr) {
-        bulk_store_1d(p.a_full_mc[parity] + off, bufs + b * kCommChunk, chunk_bytes(i));
-      } else {
+      for (; i < piece_vecs; i += T) mm_st_v4(mc + i, ld_nc_v4(src + i));
+    } else {
+      for (; i + 1ull * T < piece_vecs; i += 2ull * T) {
+        const uint4 v0 = ld_nc_v4(src + i), v1 = ld_nc_v4(src + i + T);
         for (int d = 1; d < p.world; ++d) {
-          const int peer = (p.rank + d) % p.world;
-          bulk_store_1d(p.a_full_peer[parity][peer] + off, bufs + b * kCommChunk, chunk_bytes(i));
+          uint4* dst =
+              reinterpret_cast<uint4*>(p.a_full_peer[parity][(p.rank + d) % p.world]) + dst_vec;
+          st_sys_v4(dst + i, v0);
+          st_sys_v4(dst + i + T, v1);
         }
       }
-      bulk_commit();
-      if (i + kCommPrefetch < nchunks) {
-        // The buffer about to be refilled was read by the stores of chunk i+prefetch-bufs.
-        if (gi + i + kCommPrefetch >= static_cast<uint32_t>(kCommBufs))
-          bulk_wait_read<kCommBufs - kCommPrefetch>();
-        issue_load(i + kCommPrefetch);
+      for (; i < piece_vecs; i += T) {
+        const uint4 v = ld_nc_v4(src + i);
+        for (int d = 1; d < p.world; ++d)
+          st_sys_v4(reinterpret_cast<uint4*>(p.a_full_peer[parity][(p.rank + d) % p.world]) +
+                        dst_vec + i, v);
       }
     }
-    // All stores of this piece are performed before the flag goes up.
-    bulk_wait_all<0>();
-    gi += nchunks;
-    if (!ok) break;
-    fence_proxy_async();
+    // Every thread's stores are visible system-wide before the flag goes up.
     __threadfence_system();
-    const int m_blk = p.rank * p.blocks_per_rank + rb;
-    if (p.a_full_mc[parity] != nullptr && p.flags_mc != nullptr) {
-      mm_red_add_u32(p.flags_mc + parity * kAgMaxRowBlocks + m_blk, 1u);
-    } else {
-      for (int d = 1; d < p.world; ++d) {
-        const int peer = (p.rank + d) % p.world;
-        red_release_sys_add(p.flags_peer[peer] + parity * kAgMaxRowBlocks + m_blk, 1u);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int m_blk = p.rank * p.blocks_per_rank + rb;
+      if (use_mc) {
+        mm_red_add_u32(p.flags_mc + parity * kAgMaxRowBlocks + m_blk, 1u);
+      } else {
+        for (int d = 1; d < p.world; ++d)
+          red_release_sys_add(
+              p.flags_peer[(p.rank + d) % p.world] + parity * kAgMaxRowBlocks + m_blk, 1u);
       }
     }
   }
@@ -195,7 +179,7 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1)
   const uint32_t parity = fused_begin(p.seq);
   const int ncomp = ctas_per_rank - p.num_comm_ctas;
   if (cta >= ncomp) {
-    ag_comm_cta(p, parity, cta - ncomp, gemm_smem_base<Cfg>(smem_raw));
+    ag_comm_cta(p, parity, cta - ncomp);
   } else {
     AgRt rt{&p, parity};
     gemm_cta_main<Cfg, AgPolicy<Cfg>>(rt, p.g, p.status, cta, ncomp, smem_raw);

@@ -3,7 +3,7 @@
 //
 // ONE kernel per rank, two variants chosen by the host from the row count:
 //  * two-shot (default): output tile t is owned by rank t % W.  The GEMM
-//    epilogue TMA-stores each bf16 partial tile into the owner's staging slot
+//    epilogue writes each bf16 partial tile into the owner's staging slot
 //    and bumps an arrival counter there; the owner adds the W partials in fp32
 //    and writes the reduced tile into EVERY rank's symmetric result buffer (one
 //    multimem.st per vector when a multicast object is bound, W plain stores
@@ -30,9 +30,7 @@ static constexpr int kArMaxTiles = 8192;  // flags per parity
 struct GemmArParams {
   CUtensorMap tm_a;
   CUtensorMap tm_b;
-  // [parity][dest]: dest's staging, rows = (src*slots + slot)*128 .. , BN columns; already
-  // offset to THIS source rank's region.
-  CUtensorMap tm_stage[2][CB_MAX_RANKS];
+  uint8_t* stage_peer[2][CB_MAX_RANKS];  // [parity][dest]: dest's staging [W][slots][128][BN]
   GemmShape g;
   int rank, world;
   int oneshot;
@@ -74,28 +72,31 @@ struct ArPolicy {
   __device__ static const CUtensorMap* map_b(const ArRt& r) { return &r.p->tm_b; }
   __device__ static int a_row(const ArRt&, int m_blk) { return m_blk * Cfg::BM; }
   __device__ static bool wait_a_ready(const ArRt&, int, volatile int*) { return true; }
-  __device__ static void store_box(const ArRt& r, int m_blk, int n_blk, int row, int col,
-                                   const void* smem_box) {
+  static constexpr bool kDirect = true;
+  __device__ static void direct_targets(const ArRt& r, int m_blk, int n_blk, DirectTargets* t) {
     const GemmArParams& p = *r.p;
-    const int t = m_blk * p.g.num_n_blocks + n_blk;
-    // Boxes entirely below the last row carry nothing (decode-sized M): keep them off NVLink.
-    if (m_blk * Cfg::BM + row >= p.g.M) return;
+    const int tl = m_blk * p.g.num_n_blocks + n_blk;
+    const long long tile_bytes = static_cast<long long>(Cfg::BM) * Cfg::BN * 2;
+    t->ld_bytes = static_cast<long long>(Cfg::BN) * 2;
+    const int rows_left = p.g.M - m_blk * Cfg::BM;
+    t->rows = rows_left < Cfg::BM ? rows_left : Cfg::BM;  // rows past M carry nothing
+    t->cols = Cfg::BN;
     if (p.oneshot) {
+      t->n = p.world;
       for (int d = 0; d < p.world; ++d) {
         const int dest = (p.rank + d) % p.world;
-        tma_store_2d(&p.tm_stage[r.parity][dest], smem_box, col, t * Cfg::BM + row);
+        t->base[d] = p.stage_peer[r.parity][dest] +
+                     (static_cast<long long>(p.rank) * p.slots + tl) * tile_bytes;
       }
     } else {
-      const int owner = t % p.world;
-      tma_store_2d(&p.tm_stage[r.parity][owner], smem_box, col, (t / p.world) * Cfg::BM + row);
+      t->n = 1;
+      t->base[0] = p.stage_peer[r.parity][tl % p.world] +
+                   (static_cast<long long>(p.rank) * p.slots + tl / p.world) * tile_bytes;
     }
   }
   __device__ static void tile_done(const ArRt& r, int m_blk, int n_blk, int) {
     const GemmArParams& p = *r.p;
     const int t = m_blk * p.g.num_n_blocks + n_blk;
-    bulk_wait_all<0>();
-    fence_proxy_async();
-    __threadfence_system();
     if (p.oneshot) {
       for (int d = 0; d < p.world; ++d) {
         const int dest = (p.rank + d) % p.world;
@@ -284,15 +285,9 @@ static int build_ar_params(const CbGemmArDesc& d, GemmArParams* p) {
     return -1;
   if (make_tmap_2d(&p->tm_b, d.b, dt, d.K, d.N, (unsigned long long)d.K * esz, BK, d.bn, true))
     return -1;
-  const unsigned long long src_bytes = (unsigned long long)d.slots * 128ull * d.bn * 2ull;
   for (int par = 0; par < 2; ++par) {
-    for (int o = 0; o < d.world; ++o) {
-      const uint8_t* base = static_cast<const uint8_t*>(d.stage_peer[par][o]) + src_bytes * d.rank;
-      if (make_tmap_2d(&p->tm_stage[par][o], base, TMAP_BF16, d.bn,
-                       (unsigned long long)d.slots * 128ull, (unsigned long long)d.bn * 2, 64, 32,
-                       true))
-        return -1;
-    }
+    for (int o = 0; o < CB_MAX_RANKS; ++o)
+      p->stage_peer[par][o] = static_cast<uint8_t*>(d.stage_peer[par][o]);
     p->stage_local[par] = static_cast<const uint8_t*>(d.stage_peer[par][d.rank]);
     for (int r = 0; r < CB_MAX_RANKS; ++r)
       p->result_peer[par][r] = static_cast<uint8_t*>(d.result_peer[par][r]);

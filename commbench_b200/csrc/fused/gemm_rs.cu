@@ -3,9 +3,9 @@
 //
 // ONE kernel per rank.  The tcgen05 GEMM walks the output row blocks owner by
 // owner, starting with the next rank (so at any moment the W ranks write to W
-// different owners); the epilogue TMA-stores each bf16 partial tile straight
-// into the OWNER's staging slot for this source rank and bumps a per-tile
-// arrival counter there.  When a CTA has finished its GEMM tiles it turns to the
+// different owners); the epilogue writes each bf16 partial tile straight into
+// the OWNER's staging slot for this source rank (row-contiguous 16-byte stores
+// over NVLink) and bumps a per-tile arrival counter there.  When a CTA has finished its GEMM tiles it turns to the
 // reduction of this rank's own output tiles: wait until all W partials of a
 // tile arrived, add them in fp32, write bf16.  The transfer of tile i overlaps
 // the math of tile i+1; the result is deterministic (fixed summation order).
@@ -30,7 +30,7 @@ static constexpr int kRsMaxTiles = 8192;  // flags per parity
 struct GemmRsParams {
   CUtensorMap tm_a;
   CUtensorMap tm_b;
-  CUtensorMap tm_stage[2][CB_MAX_RANKS];  // [parity][owner]: owner's slot for THIS source rank
+  uint8_t* stage_peer[2][CB_MAX_RANKS];  // [parity][owner]: owner's staging (all source slots)
   GemmShape g;
   int rank, world;
   int blocks_per_rank;  // 128-row blocks of the output owned by each rank
@@ -70,22 +70,26 @@ struct RsPolicy {
   __device__ static const CUtensorMap* map_b(const RsRt& r) { return &r.p->tm_b; }
   __device__ static int a_row(const RsRt&, int m_blk) { return m_blk * Cfg::BM; }
   __device__ static bool wait_a_ready(const RsRt&, int, volatile int*) { return true; }
-  __device__ static void store_box(const RsRt& r, int m_blk, int n_blk, int row, int col,
-                                   const void* smem_box) {
+  static constexpr bool kDirect = true;
+  __device__ static void direct_targets(const RsRt& r, int m_blk, int n_blk, DirectTargets* t) {
     const GemmRsParams& p = *r.p;
     const int owner = m_blk / p.blocks_per_rank;
     const int lm = m_blk - owner * p.blocks_per_rank;
-    tma_store_2d(&p.tm_stage[r.parity][owner], smem_box, n_blk * Cfg::BN + col,
-                 lm * Cfg::BM + row);
+    const long long Ml = p.g.M / p.world;
+    t->n = 1;
+    t->ld_bytes = static_cast<long long>(p.g.N) * 2;
+    t->base[0] = p.stage_peer[r.parity][owner] +
+                 ((static_cast<long long>(p.rank) * Ml + lm * Cfg::BM) * p.g.N +
+                  static_cast<long long>(n_blk) * Cfg::BN) * 2;
+    t->rows = Cfg::BM;
+    const int left = p.g.N - n_blk * Cfg::BN;
+    t->cols = left < Cfg::BN ? left : Cfg::BN;
   }
-  // One lane per epilogue warp: its boxes of this tile are in the owner's memory -> count up.
+  // One lane per epilogue warp, after its rows of the tile are visible at the owner.
   __device__ static void tile_done(const RsRt& r, int m_blk, int n_blk, int) {
     const GemmRsParams& p = *r.p;
     const int owner = m_blk / p.blocks_per_rank;
     const int lm = m_blk - owner * p.blocks_per_rank;
-    bulk_wait_all<0>();
-    fence_proxy_async();
-    __threadfence_system();
     red_release_sys_add(
         p.flags_peer[owner] + r.parity * kRsMaxTiles + lm * p.g.num_n_blocks + n_blk, 1u);
   }
@@ -212,14 +216,9 @@ static int build_rs_params(const CbGemmRsDesc& d, GemmRsParams* p) {
     return -1;
   if (make_tmap_2d(&p->tm_b, d.b, dt, d.K, d.N, (unsigned long long)d.K * esz, BK, d.bn, true))
     return -1;
-  const unsigned long long slot_bytes = (unsigned long long)Ml * d.N * 2ull;
   for (int par = 0; par < 2; ++par) {
-    for (int o = 0; o < d.world; ++o) {
-      const uint8_t* base = static_cast<const uint8_t*>(d.stage_peer[par][o]) + slot_bytes * d.rank;
-      if (make_tmap_2d(&p->tm_stage[par][o], base, TMAP_BF16, d.N, Ml, (unsigned long long)d.N * 2,
-                       64, 32, true))
-        return -1;
-    }
+    for (int o = 0; o < CB_MAX_RANKS; ++o)
+      p->stage_peer[par][o] = static_cast<uint8_t*>(d.stage_peer[par][o]);
     p->stage_local[par] = static_cast<const uint8_t*>(d.stage_peer[par][d.rank]);
   }
   p->g.M = d.M;

@@ -67,6 +67,7 @@ struct PlainParams {
 template <class Cfg>
 struct PlainPolicy {
   using P = PlainParams;
+  static constexpr bool kDirect = false;
   __device__ static int num_tiles(const P& p) { return p.g.num_m_blocks * p.g.num_n_blocks; }
   __device__ static void tile_coord(const P& p, int tile, int* m, int* n) {
     raster_tile(tile, p.g.num_m_blocks, p.g.num_n_blocks, p.raster_group, m, n);

@@ -93,9 +93,12 @@ struct GemmCtl {
 //   const CUtensorMap* map_a(const P&, int m_blk), map_b(const P&)
 //   int  a_row(const P&, int m_blk)            row coordinate of the A tile in map_a
 //   bool wait_a_ready(const P&, int m_blk, volatile int* abort)   (producer thread only)
+//   static constexpr bool kDirect            false: TMA-store epilogue (store_box);
+//                                              true: load/store epilogue (direct_targets)
 //   void store_box(const P&, int m_blk, int n_blk, int row_in_tile, int col_in_tile,
 //                  const void* smem_box)       issued by one lane; must issue exactly one
 //                                              bulk-group worth of stores (commit is done here)
+//   void direct_targets(const P&, int m_blk, int n_blk, DirectTargets*)
 //   void tile_done(const P&, int m_blk, int n_blk, int quadrant)  after the quadrant's boxes
 //                                              were issued (one lane)
 template <class Cfg, class Policy, class P>
@@ -189,11 +192,111 @@ __device__ __forceinline__ void epi_write_row_swizzled(uint8_t* buf, uint32_t la
   }
 }
 
+// Where a "direct" policy wants a finished tile: up to 8 destinations (peer or
+// local global memory) that all receive the same data with plain 16-byte stores.
+struct DirectTargets {
+  uint8_t* base[8];    // address of (tile row 0, tile column 0) at each destination
+  int n;               // destinations
+  long long ld_bytes;  // row pitch at the destination
+  int rows, cols;      // valid rows / columns of this tile (columns a multiple of 8)
+};
+
+// fp32 accumulator row (64 columns) -> bf16 into a [32 rows][256 B] buffer; chunk
+// index (0..15) XOR row%8 keeps both the row-wise writes and the row-contiguous
+// reads below free of bank conflicts.
+__device__ __forceinline__ void epi_write_row_256(uint8_t* buf, uint32_t lane, int half_chunk,
+                                                  const uint32_t (&r0)[32],
+                                                  const uint32_t (&r1)[32], float alpha) {
+  uint8_t* row = buf + lane * 256u;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int col = c * 8 + j * 2;
+      const float x = __uint_as_float(col < 32 ? r0[col] : r1[col - 32]) * alpha;
+      const float y = __uint_as_float(col + 1 < 32 ? r0[col + 1] : r1[col + 1 - 32]) * alpha;
+      __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+      w[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    const uint32_t idx = static_cast<uint32_t>(half_chunk * 8 + c);
+    const uint32_t phys = (idx ^ (lane & 7u)) * 16u;
+    *reinterpret_cast<uint4*>(row + phys) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+// Epilogue for policies with `kDirect`: accumulator -> bf16 -> shared memory
+// (transposition) -> row-contiguous 16-byte global stores, 256 bytes per row and
+// half-warp.  Used where the destination is another GPU: load/store traffic
+// keeps NVLink busy with few SMs, and no TMA store sits between data and flag.
 template <class Cfg, class Policy, class P>
-__device__ __forceinline__ void gemm_epilogue(const P& p, const GemmShape& g, uint8_t* epi_smem,
-                                              GemmCtl<Cfg::STAGES>* ctl, uint32_t* status,
-                                              int cta, int num_ctas, uint32_t tmem_base,
-                                              uint32_t warp, uint32_t lane) {
+__device__ __forceinline__ void gemm_epilogue_direct(const P& p, const GemmShape& g,
+                                                     uint8_t* epi_smem,
+                                                     GemmCtl<Cfg::STAGES>* ctl, uint32_t* status,
+                                                     int cta, int num_ctas, uint32_t tmem_base,
+                                                     uint32_t warp, uint32_t lane) {
+  const uint32_t q = warp & 3u;
+  uint8_t* buf = epi_smem + q * (2 * Cfg::EPI_BUF_BYTES);  // 8 KB: 32 rows x 256 B
+  uint32_t acc = 0, acc_phase = 0;
+  const int ntiles = Policy::num_tiles(p);
+  constexpr int HALVES = (Cfg::BN + 127) / 128;
+  for (int tile = cta; tile < ntiles; tile += num_ctas) {
+    int m_blk, n_blk;
+    Policy::tile_coord(p, tile, &m_blk, &n_blk);
+    DirectTargets tg;
+    Policy::direct_targets(p, m_blk, n_blk, &tg);
+    if (!mbar_wait(&ctl->tmem_full[acc], acc_phase, &ctl->abort_flag, status, 0x400 + acc)) return;
+    tc_fence_after_sync();
+#pragma unroll 1
+    for (int h = 0; h < HALVES; ++h) {
+      constexpr int CH = Cfg::BN >= 128 ? 2 : 1;  // 64-column chunks per half
+#pragma unroll
+      for (int cc = 0; cc < CH; ++cc) {
+        const uint32_t taddr =
+            tmem_base + ((q * 32u) << 16) + acc * Cfg::BN + (h * CH + cc) * Cfg::EPI_COLS;
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(taddr, r0);
+        tmem_ld_32x32(taddr + 32u, r1);
+        tmem_wait_ld();
+        if (h == HALVES - 1 && cc == CH - 1) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctl->tmem_empty[acc]);
+        }
+        epi_write_row_256(buf, lane, cc, r0, r1, g.alpha);
+      }
+      __syncwarp();
+      // Half-warp per row: 16 lanes x 16 B = 256 B (128 bf16 columns; 64 when BN == 64).
+      const uint32_t idx = lane & 15u;
+      const int col = h * 128 + static_cast<int>(idx) * 8;
+      const bool col_ok = (static_cast<int>(idx) < CH * 8) && col < tg.cols;
+#pragma unroll 4
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t r = 2u * i + (lane >> 4);
+        const int row = static_cast<int>(q * 32u + r);
+        const uint4 v = *reinterpret_cast<const uint4*>(buf + r * 256u + ((idx ^ (r & 7u)) * 16u));
+        if (col_ok && row < tg.rows) {
+          const long long off = row * tg.ld_bytes + col * 2ll;
+          for (int d = 0; d < tg.n; ++d) st_sys_v4(tg.base[d] + off, v);
+        }
+      }
+      __syncwarp();
+    }
+    // Every lane's stores must be visible system-wide before the flag goes up.
+    __threadfence_system();
+    __syncwarp();
+    if (lane == 0) Policy::tile_done(p, m_blk, n_blk, static_cast<int>(q));
+    acc ^= 1u;
+    if (acc == 0u) acc_phase ^= 1u;
+  }
+}
+
+template <class Cfg, class Policy, class P>
+__device__ __forceinline__ void gemm_epilogue_tma(const P& p, const GemmShape& g,
+                                                  uint8_t* epi_smem, GemmCtl<Cfg::STAGES>* ctl,
+                                                  uint32_t* status, int cta, int num_ctas,
+                                                  uint32_t tmem_base, uint32_t warp,
+                                                  uint32_t lane) {
   const uint32_t q = warp & 3u;  // TMEM lane quadrant this warp may read
   uint8_t* bufs = epi_smem + q * (2 * Cfg::EPI_BUF_BYTES);
   uint32_t acc = 0, acc_phase = 0, buf = 0;
@@ -234,6 +337,20 @@ __device__ __forceinline__ void gemm_epilogue(const P& p, const GemmShape& g, ui
     if (acc == 0u) acc_phase ^= 1u;
   }
   if (lane == 0) bulk_wait_all<0>();
+}
+
+template <class Cfg, class Policy, class P>
+__device__ __forceinline__ void gemm_epilogue(const P& p, const GemmShape& g, uint8_t* epi_smem,
+                                              GemmCtl<Cfg::STAGES>* ctl, uint32_t* status,
+                                              int cta, int num_ctas, uint32_t tmem_base,
+                                              uint32_t warp, uint32_t lane) {
+  if constexpr (Policy::kDirect) {
+    gemm_epilogue_direct<Cfg, Policy>(p, g, epi_smem, ctl, status, cta, num_ctas, tmem_base, warp,
+                                      lane);
+  } else {
+    gemm_epilogue_tma<Cfg, Policy>(p, g, epi_smem, ctl, status, cta, num_ctas, tmem_base, warp,
+                                   lane);
+  }
 }
 
 // Common prologue / epilogue of every kernel built on this core.

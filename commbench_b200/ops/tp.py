@@ -138,7 +138,7 @@ class AgGemm(_FusedBase):
         self.flags = _Sym(ctx, 2 * 1024 * 4, zero=True)
         self._sync_init()
 
-    def _desc(self, r, a_local, b, c, M, Nn, K, alpha, bn, comm_ctas, parts) -> _AgDesc:
+    def _desc(self, r, a_local, b, c, M, Nn, K, alpha, bn, comm_ctas, parts, use_mc=True) -> _AgDesc:
         d = _AgDesc()
         d.rank, d.world, d.M, d.N, d.K = r, self.world, M, Nn, K
         d.fp8 = int(self.dtype == torch.float8_e4m3fn)
@@ -147,16 +147,16 @@ class AgGemm(_FusedBase):
         d.a_local, d.b, d.c = a_local.data_ptr(), b.data_ptr(), c.data_ptr()
         for par in range(2):
             _fill_p8(d.a_full_peer[par], self.a_full[par].ptrs)
-            d.a_full_mc[par] = self.a_full[par].mc
+            d.a_full_mc[par] = self.a_full[par].mc if use_mc else 0
         _fill_p8(d.flags_peer, self.flags.ptrs)
-        d.flags_mc = self.flags.mc
+        d.flags_mc = self.flags.mc if use_mc else 0
         d.seq = self.seq[r if self.emu else 0].data_ptr()
         d.status = self._status_ptr(r)
         d.timeout_ns = self.ctx.timeout_ns
         return d
 
     def __call__(self, a_local, b, out=None, alpha: float = 1.0, bn: int = 256,
-                 comm_ctas: int | None = None, parts: int = 8, stream=None):
+                 comm_ctas: int | None = None, parts: int = 8, use_mc: bool = True, stream=None):
         cfg = get_config()
         if comm_ctas is None:
             comm_ctas = cfg.ag_gemm_comm_ctas if self.world > 1 else 0
@@ -183,7 +183,7 @@ class AgGemm(_FusedBase):
             if out is None:
                 out = torch.empty((M, Nn), dtype=torch.bfloat16, device=a0.device)
             descs = (_AgDesc * 1)(self._desc(self.ctx.rank, a_local, b, out, M, Nn, K, alpha, bn,
-                                             comm_ctas, parts))
+                                             comm_ctas, parts, use_mc))
             rc = self.lib.cb_ag_gemm(descs, 1, None, N.stream_ptr(stream))
             result = out
         if rc != 0:

@@ -152,10 +152,11 @@ __device__ __forceinline__ void ag_comm_cta(const AgGemmParams& p, uint32_t pari
                         dst_vec + i, v);
       }
     }
-    // Every thread's stores are visible system-wide before the flag goes up.
-    __threadfence_system();
+    // One thread fences for the CTA (the barrier makes the others' stores precede it);
+    // the other warps go straight on to the next piece while that fence drains.
     __syncthreads();
     if (threadIdx.x == 0) {
+      __threadfence_system();
       const int m_blk = p.rank * p.blocks_per_rank + rb;
       if (use_mc) {
         mm_red_add_u32(p.flags_mc + parity * kAgMaxRowBlocks + m_blk, 1u);

@@ -126,7 +126,7 @@ __device__ __forceinline__ void ar_reduce_phase(const GemmArParams& p, uint32_t 
     uint32_t* flag = p.flags_local + parity * kArMaxTiles + slot;
     bool ok = true;
     if (threadIdx.x == 0)
-      ok = wait_flag_ge_sys(flag, 4u * static_cast<uint32_t>(p.world), p.timeout_ns, p.status,
+      ok = wait_flag_ge_sys(flag, static_cast<uint32_t>(p.world), p.timeout_ns, p.status,
                             PH_AR_TILE, t);
     if (__syncthreads_and(ok ? 1 : 0) == 0) return;
     for (int v = threadIdx.x; v < TILE_VECS; v += blockDim.x) {

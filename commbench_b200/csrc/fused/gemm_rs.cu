@@ -111,7 +111,7 @@ __device__ __forceinline__ void rs_reduce_phase(const GemmRsParams& p, uint32_t 
     uint32_t* flag = p.flags_local + parity * kRsMaxTiles + t;
     bool ok = true;
     if (threadIdx.x == 0)
-      ok = wait_flag_ge_sys(flag, 4u * static_cast<uint32_t>(p.world), p.timeout_ns, p.status,
+      ok = wait_flag_ge_sys(flag, static_cast<uint32_t>(p.world), p.timeout_ns, p.status,
                             PH_RS_TILE, t);
     if (__syncthreads_and(ok ? 1 : 0) == 0) return;
     for (int v = threadIdx.x; v < Cfg::BM * VPR; v += blockDim.x) {

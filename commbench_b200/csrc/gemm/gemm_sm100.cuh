@@ -12,6 +12,7 @@
 //                 tiles into a STAGES-deep shared-memory ring (128-byte swizzle);
 //   warp 1      : allocates TMEM; one elected thread issues tcgen05.mma (M=128, N=BN,
 //                 K=32 bytes per instruction) and commits completion to mbarriers;
+//   warp 6      : signal warp (fused kernels only): system-scope fence + flag per tile;
 //   warps 2..5  : epilogue: tcgen05.ld the accumulator (warp w owns TMEM lanes
 //                 32*(w%4)...), scale, convert to bf16, stage in swizzled shared memory,
 //                 TMA-store 32-row x 64-column boxes.
@@ -48,7 +49,7 @@ struct GemmCfg {
   static constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024;
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int THREADS = 192;
+  static constexpr int THREADS = 224;  // producer, MMA, 4 epilogue warps, signal warp
   static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN in {64,128,192,256}");
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS >= 32 && TMEM_COLS <= 512,
                 "TMEM columns must be a power of two");
@@ -81,6 +82,8 @@ struct GemmCtl {
   uint64_t empty[STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t sig_full[4];   // epilogue warps -> signal warp: a tile's stores were issued
+  uint64_t sig_empty[4];  // signal warp -> epilogue warps: slot may be reused
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -237,7 +240,7 @@ __device__ __forceinline__ void gemm_epilogue_direct(const P& p, const GemmShape
                                                      uint32_t warp, uint32_t lane) {
   const uint32_t q = warp & 3u;
   uint8_t* buf = epi_smem + q * (2 * Cfg::EPI_BUF_BYTES);  // 8 KB: 32 rows x 256 B
-  uint32_t acc = 0, acc_phase = 0;
+  uint32_t acc = 0, acc_phase = 0, seq = 0;
   const int ntiles = Policy::num_tiles(p);
   constexpr int HALVES = (Cfg::BN + 127) / 128;
   for (int tile = cta; tile < ntiles; tile += num_ctas) {
@@ -282,12 +285,40 @@ __device__ __forceinline__ void gemm_epilogue_direct(const P& p, const GemmShape
       }
       __syncwarp();
     }
-    // Every lane's stores must be visible system-wide before the flag goes up.
-    __threadfence_system();
+    // Hand the tile to the signal warp: it runs the (slow, ~20 us under store traffic)
+    // system-scope fence and raises the flag while these warps go on with the next tile.
     __syncwarp();
-    if (lane == 0) Policy::tile_done(p, m_blk, n_blk, static_cast<int>(q));
+    if (lane == 0) {
+      const uint32_t slot = seq & 3u;
+      if (!mbar_wait(&ctl->sig_empty[slot], ((seq >> 2) & 1u) ^ 1u, &ctl->abort_flag, status,
+                     0x800 + slot))
+        return;
+      mbar_arrive(&ctl->sig_full[slot]);
+    }
+    ++seq;
     acc ^= 1u;
     if (acc == 0u) acc_phase ^= 1u;
+  }
+}
+
+// Signal warp of a direct policy: for every tile of this CTA, wait until the four
+// epilogue warps have issued its stores, make them visible system-wide, signal.
+// One fence per tile by one thread; cumulativity covers the other warps' stores
+// (their lanes synchronised with the arriving lane, which synchronised with us).
+template <class Cfg, class Policy, class P>
+__device__ __forceinline__ void gemm_signal(const P& p, GemmCtl<Cfg::STAGES>* ctl,
+                                            uint32_t* status, int cta, int num_ctas) {
+  uint32_t seq = 0;
+  const int ntiles = Policy::num_tiles(p);
+  for (int tile = cta; tile < ntiles; tile += num_ctas, ++seq) {
+    int m_blk, n_blk;
+    Policy::tile_coord(p, tile, &m_blk, &n_blk);
+    const uint32_t slot = seq & 3u;
+    if (!mbar_wait(&ctl->sig_full[slot], (seq >> 2) & 1u, &ctl->abort_flag, status, 0x900 + slot))
+      return;
+    mbar_arrive(&ctl->sig_empty[slot]);
+    __threadfence_system();
+    Policy::tile_done(p, m_blk, n_blk, 0);
   }
 }
 
@@ -370,6 +401,10 @@ __device__ __forceinline__ uint32_t gemm_setup(GemmCtl<Cfg::STAGES>* ctl, uint32
       mbar_init(&ctl->tmem_full[a], 1);
       mbar_init(&ctl->tmem_empty[a], 4);  // one arrival per epilogue warp
     }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&ctl->sig_full[i], 4);
+      mbar_init(&ctl->sig_empty[i], 1);
+    }
     ctl->abort_flag = 0;
     fence_mbar_init();
   }
@@ -422,8 +457,12 @@ __device__ __forceinline__ void gemm_cta_main(const P& p, const GemmShape& g, ui
     if (lane == 0) gemm_producer<Cfg, Policy>(p, g, ring, &ctl, status, cta, num_ctas);
   } else if (warp == 1) {
     if (lane == 0) gemm_mma<Cfg, Policy>(p, g, ring, &ctl, status, cta, num_ctas, tmem_base);
-  } else {
+  } else if (warp < 6) {
     gemm_epilogue<Cfg, Policy>(p, g, epi, &ctl, status, cta, num_ctas, tmem_base, warp, lane);
+  } else {
+    if constexpr (Policy::kDirect) {
+      if (lane == 0) gemm_signal<Cfg, Policy>(p, &ctl, status, cta, num_ctas);
+    }
   }
   __syncwarp();
   gemm_teardown<Cfg>(&ctl, warp, tmem_base);

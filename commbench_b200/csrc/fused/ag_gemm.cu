@@ -58,20 +58,23 @@ struct AgPolicy {
   __device__ static int num_tiles(const AgRt& r) {
     return r.p->g.num_m_blocks * r.p->g.num_n_blocks;
   }
-  // Position in the processing order -> global row block: own blocks first, then
-  // row block 0 of every peer, row block 1 of every peer, ... (the order they arrive in).
-  __device__ static int seq_to_mblk(const AgGemmParams& p, int i) {
-    const int bpr = p.blocks_per_rank;
-    if (i < bpr) return p.rank * bpr + i;
-    const int j = i - bpr;
-    const int rb = j / (p.world - 1);
-    const int peer = (p.rank + 1 + j % (p.world - 1)) % p.world;
-    return peer * bpr + rb;
-  }
+  // Processing order: this rank's own row blocks first (all column blocks), then, for
+  // rb = 0, 1, ..., row block rb of every peer (the order the pushes arrive in).  The
+  // remote part is rasterised in panels of W-1 row blocks, i.e. one arrival wave each.
   __device__ static void tile_coord(const AgRt& r, int tile, int* m, int* n) {
+    const AgGemmParams& p = *r.p;
+    const int bpr = p.blocks_per_rank;
+    const int local_tiles = bpr * p.g.num_n_blocks;
     int i;
-    raster_tile(tile, r.p->g.num_m_blocks, r.p->g.num_n_blocks, r.p->raster_group, &i, n);
-    *m = seq_to_mblk(*r.p, i);
+    if (tile < local_tiles) {
+      raster_tile(tile, bpr, p.g.num_n_blocks, bpr, &i, n);
+      *m = p.rank * bpr + i;
+    } else {
+      raster_tile(tile - local_tiles, (p.world - 1) * bpr, p.g.num_n_blocks, p.world - 1, &i, n);
+      const int rb = i / (p.world - 1);
+      const int peer = (p.rank + 1 + i % (p.world - 1)) % p.world;
+      *m = peer * bpr + rb;
+    }
   }
   __device__ static bool is_local(const AgGemmParams& p, int m_blk) {
     return m_blk / p.blocks_per_rank == p.rank;
@@ -126,13 +129,12 @@ __device__ __forceinline__ void ag_comm_cta(const AgGemmParams& p, uint32_t pari
     unsigned long long i = threadIdx.x;
     if (use_mc) {
       uint4* mc = reinterpret_cast<uint4*>(p.a_full_mc[parity]) + dst_vec;
-      for (; i + 3ull * T < piece_vecs; i += 4ull * T) {
-        const uint4 v0 = ld_nc_v4(src + i), v1 = ld_nc_v4(src + i + T),
-                    v2 = ld_nc_v4(src + i + 2ull * T), v3 = ld_nc_v4(src + i + 3ull * T);
-        mm_st_v4(mc + i, v0);
-        mm_st_v4(mc + i + T, v1);
-        mm_st_v4(mc + i + 2ull * T, v2);
-        mm_st_v4(mc + i + 3ull * T, v3);
+      for (; i + 7ull * T < piece_vecs; i += 8ull * T) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = ld_nc_v4(src + i + u * T);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) mm_st_v4(mc + i + u * T, v[u]);
       }
       for (; i < piece_vecs; i += T) mm_st_v4(mc + i, ld_nc_v4(src + i));
     } else {

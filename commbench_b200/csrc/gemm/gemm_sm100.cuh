@@ -82,8 +82,8 @@ struct GemmCtl {
   uint64_t empty[STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
-  uint64_t sig_full[4];   // epilogue warps -> signal warp: a tile's stores were issued
-  uint64_t sig_empty[4];  // signal warp -> epilogue warps: slot may be reused
+  uint64_t sig_full[8];   // epilogue warps -> signal warp: a tile's stores were issued
+  uint64_t sig_empty[8];  // signal warp -> epilogue warps: slot may be reused
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -289,8 +289,8 @@ __device__ __forceinline__ void gemm_epilogue_direct(const P& p, const GemmShape
     // system-scope fence and raises the flag while these warps go on with the next tile.
     __syncwarp();
     if (lane == 0) {
-      const uint32_t slot = seq & 3u;
-      if (!mbar_wait(&ctl->sig_empty[slot], ((seq >> 2) & 1u) ^ 1u, &ctl->abort_flag, status,
+      const uint32_t slot = seq & 7u;
+      if (!mbar_wait(&ctl->sig_empty[slot], ((seq >> 3) & 1u) ^ 1u, &ctl->abort_flag, status,
                      0x800 + slot))
         return;
       mbar_arrive(&ctl->sig_full[slot]);
@@ -301,24 +301,42 @@ __device__ __forceinline__ void gemm_epilogue_direct(const P& p, const GemmShape
   }
 }
 
-// Signal warp of a direct policy: for every tile of this CTA, wait until the four
-// epilogue warps have issued its stores, make them visible system-wide, signal.
-// One fence per tile by one thread; cumulativity covers the other warps' stores
-// (their lanes synchronised with the arriving lane, which synchronised with us).
+// Signal warp of a direct policy: for the tiles of this CTA, wait until the four
+// epilogue warps have issued a tile's stores, make them visible system-wide,
+// signal.  A system-scope fence under store traffic costs tens of microseconds,
+// so it runs here, off the epilogue's path, and one fence covers every tile that
+// became ready while the previous fence was draining (up to 4).  Cumulativity
+// covers the epilogue warps' stores: their lanes synchronised with the arriving
+// lane, which synchronised with this thread through the mbarrier.
 template <class Cfg, class Policy, class P>
 __device__ __forceinline__ void gemm_signal(const P& p, GemmCtl<Cfg::STAGES>* ctl,
                                             uint32_t* status, int cta, int num_ctas) {
   uint32_t seq = 0;
   const int ntiles = Policy::num_tiles(p);
-  for (int tile = cta; tile < ntiles; tile += num_ctas, ++seq) {
-    int m_blk, n_blk;
-    Policy::tile_coord(p, tile, &m_blk, &n_blk);
-    const uint32_t slot = seq & 3u;
-    if (!mbar_wait(&ctl->sig_full[slot], (seq >> 2) & 1u, &ctl->abort_flag, status, 0x900 + slot))
-      return;
-    mbar_arrive(&ctl->sig_empty[slot]);
+  int pend_m[4], pend_n[4];
+  int npend = 0;
+  int tile = cta;
+  while (tile < ntiles || npend > 0) {
+    if (tile < ntiles && npend < 4) {
+      const uint32_t slot = seq & 7u;
+      const uint32_t par = (seq >> 3) & 1u;
+      bool ready = mbar_try_wait(&ctl->sig_full[slot], par);
+      if (!ready && npend == 0) {
+        if (!mbar_wait(&ctl->sig_full[slot], par, &ctl->abort_flag, status, 0x900 + slot)) return;
+        ready = true;
+      }
+      if (ready) {
+        mbar_arrive(&ctl->sig_empty[slot]);
+        Policy::tile_coord(p, tile, &pend_m[npend], &pend_n[npend]);
+        ++npend;
+        tile += num_ctas;
+        ++seq;
+        continue;
+      }
+    }
     __threadfence_system();
-    Policy::tile_done(p, m_blk, n_blk, 0);
+    for (int i = 0; i < npend; ++i) Policy::tile_done(p, pend_m[i], pend_n[i], 0);
+    npend = 0;
   }
 }
 
@@ -401,7 +419,7 @@ __device__ __forceinline__ uint32_t gemm_setup(GemmCtl<Cfg::STAGES>* ctl, uint32
       mbar_init(&ctl->tmem_full[a], 1);
       mbar_init(&ctl->tmem_empty[a], 4);  // one arrival per epilogue warp
     }
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 8; ++i) {
       mbar_init(&ctl->sig_full[i], 4);
       mbar_init(&ctl->sig_empty[i], 1);
     }

@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(kCollThreads)
     }
     for (; i < c0 + s1; i += blockDim.x) mm_st_v4(mc + i, Vec16<DT>::mm_reduce(mc + i));
     // multimem.st results must be visible on every rank before anyone reads them.
-    __threadfence_system();
+    fence_acq_rel_sys();
     ok = rank_barrier_block(c, ch, e + 2, PH_BARRIER_END);
   }
   if (ok && a.copy_out) copy_bytes_slice(a.out, a.sym[c.rank], a.nbytes, v0, v1, false);
@@ -334,7 +334,7 @@ __global__ void __launch_bounds__(kCollThreads)
         }
       }
     }
-    __threadfence_system();
+    fence_acq_rel_sys();
     ok = rank_barrier_block(c, ch, e + 2, PH_BARRIER_END);
   }
   end_epoch(c, ch, e + 2);
@@ -521,7 +521,7 @@ __global__ void __launch_bounds__(kCollThreads)
         }
         mm_st_v4(mc + i, v);
       }
-      __threadfence_system();
+      fence_acq_rel_sys();
     }
     if (ok) ok = rank_barrier_block(c, ch, e + 2, PH_BARRIER_END);
     if (ok && a.copy_out) copy_bytes_slice(a.out, a.sym[c.rank], a.nbytes, v0, v1, false);

@@ -158,13 +158,13 @@ __device__ __forceinline__ void ag_comm_cta(const AgGemmParams& p, uint32_t pari
     // the other warps go straight on to the next piece while that fence drains.
     __syncthreads();
     if (threadIdx.x == 0) {
-      __threadfence_system();
+      fence_acq_rel_sys();
       const int m_blk = p.rank * p.blocks_per_rank + rb;
       if (use_mc) {
-        mm_red_add_u32(p.flags_mc + parity * kAgMaxRowBlocks + m_blk, 1u);
+        mm_red_add_relaxed_u32(p.flags_mc + parity * kAgMaxRowBlocks + m_blk, 1u);
       } else {
         for (int d = 1; d < p.world; ++d)
-          red_release_sys_add(
+          red_relaxed_sys_add(
               p.flags_peer[(p.rank + d) % p.world] + parity * kAgMaxRowBlocks + m_blk, 1u);
       }
     }

@@ -68,4 +68,53 @@ __device__ __forceinline__ uint4 sum_bf16x8(const uint4* v, int nsrc) {
   return r;
 }
 
+template <int W>
+__device__ __forceinline__ uint4 sum_bf16x8_t(const uint4 (&v)[W]) {
+  float acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+#pragma unroll
+  for (int s = 0; s < W; ++s) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v[s]);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 t = __bfloat1622float2(h[k]);
+      acc[2 * k] += t.x;
+      acc[2 * k + 1] += t.y;
+    }
+  }
+  uint4 r;
+  __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) o[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+  return r;
+}
+
+// Sum of W staged copies of one [ROWS x VPR vectors] tile, many loads in flight
+// per thread (L2-coherent loads: the copies were written by peers).
+//   src(s, v)  -> address of vector v of copy s          (callable)
+//   dst(v, x)  -> consumes the reduced vector            (callable)
+//   valid(v)   -> false for vectors outside the tensor   (callable)
+template <int W, int NVEC, class Src, class Dst, class Valid>
+__device__ __forceinline__ void reduce_tile_copies(Src src, Dst dst, Valid valid) {
+  constexpr int U = W >= 8 ? 2 : (W >= 4 ? 4 : 8);
+  for (int v0 = threadIdx.x; v0 < NVEC; v0 += blockDim.x * U) {
+    uint4 parts[U][W];
+    bool ok[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * static_cast<int>(blockDim.x);
+      ok[u] = v < NVEC && valid(v);
+      if (ok[u]) {
+#pragma unroll
+        for (int s = 0; s < W; ++s) parts[u][s] = __ldcg(src(s, v));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (ok[u]) dst(v0 + u * static_cast<int>(blockDim.x), sum_bf16x8_t<W>(parts[u]));
+    }
+  }
+}
+
 }  // namespace cb

@@ -100,10 +100,10 @@ struct ArPolicy {
     if (p.oneshot) {
       for (int d = 0; d < p.world; ++d) {
         const int dest = (p.rank + d) % p.world;
-        red_release_sys_add(p.flags_peer[dest] + r.parity * kArMaxTiles + t, 1u);
+        red_relaxed_sys_add(p.flags_peer[dest] + r.parity * kArMaxTiles + t, 1u);
       }
     } else {
-      red_release_sys_add(p.flags_peer[t % p.world] + r.parity * kArMaxTiles + t / p.world, 1u);
+      red_relaxed_sys_add(p.flags_peer[t % p.world] + r.parity * kArMaxTiles + t / p.world, 1u);
     }
   }
 };
@@ -129,16 +129,17 @@ __device__ __forceinline__ void ar_reduce_phase(const GemmArParams& p, uint32_t 
       ok = wait_flag_ge_sys(flag, static_cast<uint32_t>(p.world), p.timeout_ns, p.status,
                             PH_AR_TILE, t);
     if (__syncthreads_and(ok ? 1 : 0) == 0) return;
-    for (int v = threadIdx.x; v < TILE_VECS; v += blockDim.x) {
-      const int row = m_blk * Cfg::BM + v / VPR;
-      const int cv = n_blk * VPR + v % VPR;
-      if (row >= p.g.M || static_cast<unsigned long long>(cv) >= row_vecs) continue;
-      uint4 parts[CB_MAX_RANKS];
-      for (int s = 0; s < p.world; ++s)
-        parts[s] = ld_sys_v4(stage + (static_cast<unsigned long long>(s) * p.slots + slot) *
-                                         TILE_VECS + v);
-      const uint4 sum = sum_bf16x8(parts, p.world);
-      const unsigned long long o = static_cast<unsigned long long>(row) * row_vecs + cv;
+    auto src = [&](int s, int v) -> const uint4* {
+      return stage + (static_cast<unsigned long long>(s) * p.slots + slot) * TILE_VECS + v;
+    };
+    auto valid = [&](int v) -> bool {
+      return m_blk * Cfg::BM + v / VPR < p.g.M &&
+             static_cast<unsigned long long>(n_blk * VPR + v % VPR) < row_vecs;
+    };
+    auto dst = [&](int v, uint4 sum) {
+      const unsigned long long o =
+          static_cast<unsigned long long>(m_blk * Cfg::BM + v / VPR) * row_vecs + n_blk * VPR +
+          v % VPR;
       if (p.oneshot) {
         static_cast<uint4*>(p.out)[o] = sum;
       } else if (p.result_mc[parity] != nullptr) {
@@ -149,15 +150,21 @@ __device__ __forceinline__ void ar_reduce_phase(const GemmArParams& p, uint32_t 
           st_sys_v4(reinterpret_cast<uint4*>(p.result_peer[parity][dest]) + o, sum);
         }
       }
+    };
+    switch (p.world) {
+      case 1: reduce_tile_copies<1, TILE_VECS>(src, dst, valid); break;
+      case 2: reduce_tile_copies<2, TILE_VECS>(src, dst, valid); break;
+      case 4: reduce_tile_copies<4, TILE_VECS>(src, dst, valid); break;
+      default: reduce_tile_copies<8, TILE_VECS>(src, dst, valid); break;
     }
-    __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
       *flag = 0u;
       if (!p.oneshot) {
+        fence_acq_rel_sys();  // release for the whole CTA's stores (ordered by the barrier)
         for (int d = 0; d < p.world; ++d) {
           const int dest = (p.rank + d) % p.world;
-          red_release_sys_add(p.flags_peer[dest] + ar_done_index(parity), 1u);
+          red_relaxed_sys_add(p.flags_peer[dest] + ar_done_index(parity), 1u);
         }
       }
     }

@@ -85,12 +85,12 @@ struct RsPolicy {
     const int left = p.g.N - n_blk * Cfg::BN;
     t->cols = left < Cfg::BN ? left : Cfg::BN;
   }
-  // One lane per epilogue warp, after its rows of the tile are visible at the owner.
+  // Signal thread, after its release fence covered the tile's stores.
   __device__ static void tile_done(const RsRt& r, int m_blk, int n_blk, int) {
     const GemmRsParams& p = *r.p;
     const int owner = m_blk / p.blocks_per_rank;
     const int lm = m_blk - owner * p.blocks_per_rank;
-    red_release_sys_add(
+    red_relaxed_sys_add(
         p.flags_peer[owner] + r.parity * kRsMaxTiles + lm * p.g.num_n_blocks + n_blk, 1u);
   }
 };
@@ -114,14 +114,23 @@ __device__ __forceinline__ void rs_reduce_phase(const GemmRsParams& p, uint32_t 
       ok = wait_flag_ge_sys(flag, static_cast<uint32_t>(p.world), p.timeout_ns, p.status,
                             PH_RS_TILE, t);
     if (__syncthreads_and(ok ? 1 : 0) == 0) return;
-    for (int v = threadIdx.x; v < Cfg::BM * VPR; v += blockDim.x) {
-      const int row = lm * Cfg::BM + v / VPR;
-      const int cv = n_blk * VPR + v % VPR;
-      if (row >= Ml || static_cast<unsigned long long>(cv) >= row_vecs) continue;
-      uint4 parts[CB_MAX_RANKS];
-      for (int s = 0; s < p.world; ++s)
-        parts[s] = ld_sys_v4(stage + (static_cast<unsigned long long>(s) * Ml + row) * row_vecs + cv);
-      out[static_cast<unsigned long long>(row) * row_vecs + cv] = sum_bf16x8(parts, p.world);
+    auto src = [&](int s, int v) -> const uint4* {
+      const unsigned long long row = static_cast<unsigned long long>(lm) * Cfg::BM + v / VPR;
+      return stage + (static_cast<unsigned long long>(s) * Ml + row) * row_vecs + n_blk * VPR +
+             v % VPR;
+    };
+    auto dst = [&](int v, uint4 x) {
+      const unsigned long long row = static_cast<unsigned long long>(lm) * Cfg::BM + v / VPR;
+      out[row * row_vecs + n_blk * VPR + v % VPR] = x;
+    };
+    auto valid = [&](int v) -> bool {
+      return static_cast<unsigned long long>(n_blk * VPR + v % VPR) < row_vecs;
+    };
+    switch (p.world) {
+      case 1: reduce_tile_copies<1, Cfg::BM * VPR>(src, dst, valid); break;
+      case 2: reduce_tile_copies<2, Cfg::BM * VPR>(src, dst, valid); break;
+      case 4: reduce_tile_copies<4, Cfg::BM * VPR>(src, dst, valid); break;
+      default: reduce_tile_copies<8, Cfg::BM * VPR>(src, dst, valid); break;
     }
     __syncthreads();
     if (threadIdx.x == 0) *flag = 0u;  // ready for the call after next

@@ -334,7 +334,7 @@ __device__ __forceinline__ void gemm_signal(const P& p, GemmCtl<Cfg::STAGES>* ct
         continue;
       }
     }
-    __threadfence_system();
+    fence_acq_rel_sys();  // release; a sequentially-consistent fence costs far more here
     for (int i = 0; i < npend; ++i) Policy::tile_done(p, pend_m[i], pend_n[i], 0);
     npend = 0;
   }

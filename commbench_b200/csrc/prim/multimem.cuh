@@ -44,6 +44,10 @@ __device__ __forceinline__ void mm_st_v4(void* mc_ptr, uint4 v) {
                "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");
 }
+__device__ __forceinline__ void mm_red_add_relaxed_u32(uint32_t* mc_ptr, uint32_t v) {
+  asm volatile("multimem.red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(mc_ptr), "r"(v)
+               : "memory");
+}
 __device__ __forceinline__ void mm_red_add_u32(uint32_t* mc_ptr, uint32_t v) {
   asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc_ptr), "r"(v)
                : "memory");

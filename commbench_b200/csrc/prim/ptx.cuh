@@ -159,7 +159,7 @@ __device__ __forceinline__ void report_status(uint32_t* status, uint32_t code, u
                                               uint32_t detail) {
   if (status != nullptr) {
     atomicCAS(status, 0u, (code << 24) | ((phase & 0xffu) << 16) | (detail & 0xffffu));
-    __threadfence_system();
+    fence_acq_rel_sys();
   }
 }
 

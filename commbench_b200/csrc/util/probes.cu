@@ -37,10 +37,11 @@ __global__ void copy_width_kernel(V* __restrict__ dst, const V* __restrict__ src
 
 // ------------------------------------------------------- remote-store patterns
 // Each warp owns a contiguous slice and writes it 512 bytes per instruction.
-// mode 0: st.global.v4 (weak)   1: st.relaxed.sys.v4   2: multimem.st.v4
-// After every `fence_every` instructions (0 = only at the end) the warp runs
-// __threadfence_system() and lane 0 adds 1 to `flag` with red.release.sys: the
-// cost of "data, then flag" at that granularity.
+// mode & 15 = 0: st.global.v4 (weak)   1: st.relaxed.sys.v4   2: multimem.st.v4
+// After every `fence_every` instructions (0 = only at the end) the warp runs a
+// system-scope fence (sequentially consistent = __threadfence_system() by default,
+// fence.acq_rel.sys when mode & 16) and lane 0 adds 1 to `flag`: the cost of
+// "data, then flag" at that granularity.
 __global__ void store_pattern_kernel(uint4* dst, const uint4* __restrict__ src, size_t nvec,
                                      int mode, int fence_every, uint32_t* flag) {
   const size_t warps = static_cast<size_t>(gridDim.x) * (blockDim.x >> 5);
@@ -50,6 +51,8 @@ __global__ void store_pattern_kernel(uint4* dst, const uint4* __restrict__ src, 
   if (e > nvec) e = nvec;
   const uint32_t lane = threadIdx.x & 31u;
   int since = 0;
+  const bool acq_rel = (mode & 16) != 0;
+  mode &= 15;
   for (size_t i = b + lane; i < e; i += 32) {
     const uint4 v = src[i];
     if (mode == 0) {
@@ -61,9 +64,9 @@ __global__ void store_pattern_kernel(uint4* dst, const uint4* __restrict__ src, 
     }
     if (fence_every > 0 && ++since == fence_every) {
       since = 0;
-      __threadfence_system();
+      if (acq_rel) fence_acq_rel_sys(); else __threadfence_system();
       __syncwarp();
-      if (lane == 0 && flag != nullptr) red_release_sys_add(flag, 1u);
+      if (lane == 0 && flag != nullptr) red_relaxed_sys_add(flag, 1u);
     }
   }
   __threadfence_system();

@@ -21,7 +21,7 @@ class Config:
     ar_nvls_min_bytes: int = 512 * 1024         # at or above (with multicast bound): NVLS
     coll_max_blocks: int = 64                   # CTAs per collective kernel (<= one wave)
     # --- fused GEMMs -------------------------------------------------------
-    ag_gemm_comm_ctas: int = 16                 # CTAs reserved for pushing the local A shard
+    ag_gemm_comm_ctas: int = 8                  # CTAs reserved for pushing the local A shard
     gemm_rs_reduce_ctas: int = 0                # 0: reduction runs on all CTAs after their tiles
     gemm_ar_oneshot_max_m: int = 256            # rows at or below: one-shot AR epilogue
     # --- MoE ---------------------------------------------------------------

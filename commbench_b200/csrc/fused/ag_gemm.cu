@@ -114,17 +114,22 @@ struct AgPolicy {
 // peers.  Load/store traffic from a handful of CTAs saturates NVLink here, which
 // bulk (TMA) copies issued from the same number of SMs did not.
 __device__ __forceinline__ void ag_comm_cta(const AgGemmParams& p, uint32_t parity, int comm_cta) {
-  const unsigned long long piece = p.row_block_bytes / p.parts;
-  const unsigned long long piece_vecs = piece / 16ull;
+  // A row block (a multiple of 16 bytes) is cut into `parts` nearly equal runs of 16-byte
+  // vectors; with parts == number of comm CTAs all of them work on the same row block, so
+  // row blocks complete one after the other, in the order the compute CTAs want them.
+  const unsigned long long rb_vecs = p.row_block_bytes / 16ull;
+  const unsigned long long per_part = (rb_vecs + p.parts - 1) / p.parts;
   const bool use_mc = p.a_full_mc[parity] != nullptr && p.flags_mc != nullptr;
   for (int item = comm_cta; item < p.blocks_per_rank * p.parts; item += p.num_comm_ctas) {
     const int rb = item / p.parts;
     const int part = item % p.parts;
-    const uint4* src =
-        reinterpret_cast<const uint4*>(p.a_local + rb * p.row_block_bytes + part * piece);
+    unsigned long long v_begin = per_part * part, v_end = v_begin + per_part;
+    if (v_begin > rb_vecs) v_begin = rb_vecs;
+    if (v_end > rb_vecs) v_end = rb_vecs;
+    const unsigned long long piece_vecs = v_end - v_begin;
+    const uint4* src = reinterpret_cast<const uint4*>(p.a_local + rb * p.row_block_bytes) + v_begin;
     const unsigned long long dst_vec =
-        (static_cast<unsigned long long>(p.rank * p.blocks_per_rank + rb) * p.row_block_bytes +
-         part * piece) / 16ull;
+        static_cast<unsigned long long>(p.rank * p.blocks_per_rank + rb) * rb_vecs + v_begin;
     const unsigned long long T = blockDim.x;
     unsigned long long i = threadIdx.x;
     if (use_mc) {
@@ -243,7 +248,7 @@ struct CbAgGemmDesc {
   float alpha;
   int bn;                 // 256 or 128
   int num_comm_ctas;      // 0 when world == 1
-  int parts;              // pieces per 128-row block (divides 128)
+  int parts;              // pieces a 128-row block is pushed in (0 < parts <= 1024)
   int ctas_per_rank;      // CTAs this rank's launch (or grid slice) uses
   const void* a_local;    // [M/world, K]
   const void* b;          // [N, K]
@@ -273,8 +278,8 @@ static int build_ag_params(const CbAgGemmDesc& d, AgGemmParams* p) {
     set_last_error("ag_gemm: too many row blocks");
     return -1;
   }
-  if (d.parts < 1 || 128 % d.parts != 0) {
-    set_last_error("ag_gemm: parts must divide 128");
+  if (d.parts < 1 || d.parts > 1024) {
+    set_last_error("ag_gemm: parts must be in [1, 1024]");
     return -1;
   }
   const int Ml = d.M / d.world;

@@ -156,12 +156,16 @@ class AgGemm(_FusedBase):
         return d
 
     def __call__(self, a_local, b, out=None, alpha: float = 1.0, bn: int = 256,
-                 comm_ctas: int | None = None, parts: int = 8, use_mc: bool = True, stream=None):
+                 comm_ctas: int | None = None, parts: int | None = None, use_mc: bool = True,
+                 stream=None):
         cfg = get_config()
         if comm_ctas is None:
             comm_ctas = cfg.ag_gemm_comm_ctas if self.world > 1 else 0
         if self.emu:
             comm_ctas = min(comm_ctas, 4) if self.world > 1 else 0
+        if parts is None:
+            parts = max(comm_ctas, 1)   # every comm CTA works on the same row block
+        if self.emu:
             a0, b0 = a_local[0], b[0]
         else:
             a0, b0 = a_local, b

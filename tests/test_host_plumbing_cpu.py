@@ -1,0 +1,160 @@
+"""CPU-only tests of the host plumbing: broker (fd exchange, barrier, all-gather over shared
+memory), shared-memory object broadcast, gloo all-reduce correctness, launcher clean-up."""
+import ctypes as C
+import multiprocessing as mp
+import os
+import sys
+import uuid
+
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.dirname(HERE))
+
+
+def _broker_worker(name, rank, world, q):
+    from commbench_b200 import _native as N
+
+    lib = N.load()
+    b = C.c_void_p(0)
+    assert lib.cb_broker_create(name.encode(), rank, world, 120000, C.byref(b)) == 0, N.last_error()
+    # each rank contributes a memfd holding its rank number
+    fd = os.memfd_create(f"r{rank}")
+    os.write(fd, bytes([rank + 65]) * 8)
+    fds = (C.c_int * 8)()
+    for rnd in range(3):    # several rounds: out-of-order arrivals are stashed per round
+        assert lib.cb_broker_exchange_fds(b, fd, fds, 120000) == 0, N.last_error()
+        got = []
+        for r in range(world):
+            os.lseek(fds[r], 0, os.SEEK_SET)
+            got.append(os.read(fds[r], 8))
+            os.close(fds[r])
+        assert got == [bytes([r + 65]) * 8 for r in range(world)]
+    assert lib.cb_broker_barrier(b, 120000) == 0
+    mine = (C.c_ubyte * 16)(*([rank] * 16))
+    allb = (C.c_ubyte * (16 * world))()
+    assert lib.cb_broker_allgather(b, mine, 16, allb, 120000) == 0
+    assert list(allb) == [r for r in range(world) for _ in range(16)]
+    out = C.c_int(-1)
+    assert lib.cb_broker_broadcast_fd(b, 1, fd, C.byref(out), 120000) == 0
+    os.lseek(out.value, 0, os.SEEK_SET)
+    assert os.read(out.value, 8) == bytes([1 + 65]) * 8
+    os.close(out.value)
+    lib.cb_broker_destroy(b)
+    q.put((rank, "ok"))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_broker_fd_exchange_barrier_allgather(native_lib, world):
+    name = "cbt-" + uuid.uuid4().hex[:10]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_broker_worker, args=(name, r, world, q)) for r in range(world)]
+    for p in ps:
+        p.start()
+    for p in ps:
+        p.join(300)
+        assert p.exitcode == 0
+    assert sorted(q.get(timeout=5)[0] for _ in range(world)) == list(range(world))
+
+
+def test_broker_barrier_times_out_when_a_rank_never_joins(native_lib):
+    """Failure made on the host: rank 1 never arrives; rank 0 must get an error, not hang."""
+    from commbench_b200 import _native as N
+
+    lib = N.load()
+    b = C.c_void_p(0)
+    name = "cbt-" + uuid.uuid4().hex[:10]
+    assert lib.cb_broker_create(name.encode(), 0, 2, 5000, C.byref(b)) == 0
+    assert lib.cb_broker_barrier(b, 200) == -2
+    assert "timed out" in N.last_error()
+    lib.cb_broker_destroy(b)
+
+
+def _shm_reader(name, idx, n_msgs, q):
+    from commbench_b200.ops.util import ShmBroadcast
+
+    r = ShmBroadcast(name, n_readers=2, reader_index=idx)
+    out = [r.dequeue(timeout_ms=120000) for _ in range(n_msgs)]
+    r.close()
+    q.put((idx, out))
+
+
+def test_shm_broadcast_objects_small_and_multi_slot(native_lib):
+    from commbench_b200.ops.util import ShmBroadcast
+
+    name = "cbq-" + uuid.uuid4().hex[:10]
+    w = ShmBroadcast(name, n_readers=2, nslots=4, slot_bytes=4096)
+    msgs = [{"step": i, "blob": bytes([i % 251]) * (100 + 3000 * i)} for i in range(12)]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=_shm_reader, args=(name, i, len(msgs), q)) for i in range(2)]
+    for p in ps:
+        p.start()
+    for m in msgs:
+        w.broadcast_object(m, timeout_ms=120000)
+    res = dict(q.get(timeout=300) for _ in range(2))
+    for p in ps:
+        p.join(30)
+    w.close()
+    assert res[0] == msgs and res[1] == msgs
+
+
+def test_shm_dequeue_times_out(native_lib):
+    from commbench_b200.ops.util import ShmBroadcast
+
+    name = "cbq-" + uuid.uuid4().hex[:10]
+    w = ShmBroadcast(name, n_readers=1)
+    r = ShmBroadcast(name, n_readers=1, reader_index=0)
+    with pytest.raises(TimeoutError):
+        r.dequeue(timeout_ms=100)
+    r.close()
+    w.close()
+
+
+def _gloo_allreduce(rank, world, port, q):
+    import torch.distributed as dist
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    g = torch.Generator().manual_seed(rank)
+    x = torch.randn(1_048_576, generator=g, dtype=torch.float32)
+    ref = torch.zeros(1_048_576, dtype=torch.float64)
+    for r in range(world):
+        ref += torch.randn(1_048_576, generator=torch.Generator().manual_seed(r),
+                           dtype=torch.float32).double()
+    dist.all_reduce(x)
+    ok = torch.allclose(x.double(), ref, rtol=1e-5, atol=1e-5)
+    dist.destroy_process_group()
+    q.put((rank, bool(ok)))
+
+
+def test_gloo_sum_all_reduce_matches_fp64(native_lib):
+    """world_size=2 on CPU: fp32 N(0,1) tensors of 1,048,576 elements seeded by rank, checked
+    against an fp64 sum with rtol 1e-5."""
+    from commbench_b200.runtime.launcher import free_port
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    ps = [ctx.Process(target=_gloo_allreduce, args=(r, 2, port, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    res = dict(q.get(timeout=120) for _ in range(2))
+    for p in ps:
+        p.join(30)
+    assert res == {0: True, 1: True}
+
+
+def test_launcher_kills_session_on_timeout(tmp_path):
+    from commbench_b200.runtime.launcher import run_in_new_session
+
+    script = tmp_path / "sleeper.py"
+    script.write_text("import time, subprocess, sys\n"
+                      "subprocess.Popen([sys.executable, '-c', 'import time; time.sleep(60)'])\n"
+                      "time.sleep(60)\n")
+    r = run_in_new_session([sys.executable, str(script)], timeout=1.0)
+    assert r.timed_out
+    assert r.seconds < 10

@@ -1,0 +1,79 @@
+"""FIFOs and probes on one GPU."""
+import time
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_d2h_fifo_all_triggers_arrive_once(native_lib):
+    from commbench_b200.ops.util import D2HFifo
+
+    f = D2HFifo(size=512)
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    f.start_proxy()
+    blocks, threads, per = 4, 256, 16
+    f.push_test(blocks, threads, per, status=st)
+    torch.cuda.synchronize()
+    n = blocks * threads * per
+    t0 = time.time()
+    while f.popped() < n and time.time() - t0 < 10:
+        time.sleep(0.001)
+    popped, checksum, span_ns = f.stop_proxy()
+    f.close()
+    assert int(st.item()) == 0
+    assert popped == n
+    assert checksum == n * (n + 1) // 2      # every id 1..n exactly once
+
+
+def test_d2h_fifo_push_times_out_without_consumer(native_lib):
+    """Nothing pops: once the ring is full a push must give up and leave a status word."""
+    from commbench_b200.ops.util import D2HFifo
+
+    f = D2HFifo(size=8)
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    f.push_test(1, 32, 1, timeout_s=0.05, status=st)
+    torch.cuda.synchronize()
+    assert (int(st.item()) >> 24) & 0xFF == 6     # CB_TIMEOUT_HOST_FLAG
+    f.close()
+
+
+def test_h2d_fifo_items_in_order(native_lib):
+    from commbench_b200.ops.util import H2DFifo
+
+    f = H2DFifo(size=16)
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    n = 100
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        res = f.launch_consumer(n, timeout_s=5.0, status=st, stream=s)
+    for i in range(n):
+        f.push(1000 + i)
+    s.synchronize()
+    assert int(st.item()) == 0
+    assert res[:, 0].tolist() == [1000 + i for i in range(n)]
+    assert bool((res[1:, 1] >= res[:-1, 1]).all())
+    f.close()
+
+
+def test_probes(native_lib):
+    from commbench_b200.ops import util
+
+    attrs = util.device_attributes(0)
+    assert attrs["sm_count"] > 0 and attrs["warp_size"] == 32
+    src = torch.randint(0, 255, (64 << 20,), dtype=torch.uint8, device="cuda")
+    dst = torch.empty_like(src)
+    for w in (4, 8, 16):
+        bw = util.copy_bandwidth(dst.data_ptr(), src.data_ptr(), src.numel(), width=w)
+        assert bw > 100
+    assert torch.equal(dst, src)
+    ns = util.nanosleep_probe(10000)
+    assert 5000 < ns["measured_ns"] < 200000
+    mb = util.mbarrier_round_trip(threads=128, iters=1024)
+    assert mb["cycles_per_iter"] > 0
+    bw = util.tma_stream_bandwidth(src, tile_bytes=65536, stages=3, iters=64, blocks=148)
+    assert bw > 100
+    # D2H into pinned host memory: copy engine vs kernel stores into mapped memory
+    host = torch.empty(16 << 20, dtype=torch.uint8).pin_memory()
+    assert util.memcpy_bandwidth(host, src[:16 << 20]) > 1

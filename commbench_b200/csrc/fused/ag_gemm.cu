@@ -101,6 +101,9 @@ struct AgPolicy {
     return true;
   }
   static constexpr bool kDirect = false;  // C is local: TMA-store epilogue
+  static constexpr bool kSignalPerTile = false;
+  static constexpr bool kScatterRows = false;
+  __device__ static int b_row(const AgRt&, int, int n_blk) { return n_blk * Cfg::BN; }
   __device__ static void store_box(const AgRt& r, int m_blk, int n_blk, int row, int col,
                                    const void* smem_box) {
     tma_store_2d(&r.p->tm_c, smem_box, n_blk * Cfg::BN + col, m_blk * Cfg::BM + row);

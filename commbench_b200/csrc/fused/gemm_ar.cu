@@ -73,6 +73,9 @@ struct ArPolicy {
   __device__ static int a_row(const ArRt&, int m_blk) { return m_blk * Cfg::BM; }
   __device__ static bool wait_a_ready(const ArRt&, int, volatile int*) { return true; }
   static constexpr bool kDirect = true;
+  static constexpr bool kSignalPerTile = true;
+  static constexpr bool kScatterRows = false;
+  __device__ static int b_row(const ArRt&, int, int n_blk) { return n_blk * Cfg::BN; }
   __device__ static void direct_targets(const ArRt& r, int m_blk, int n_blk, DirectTargets* t) {
     const GemmArParams& p = *r.p;
     const int tl = m_blk * p.g.num_n_blocks + n_blk;

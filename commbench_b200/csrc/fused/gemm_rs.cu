@@ -71,6 +71,9 @@ struct RsPolicy {
   __device__ static int a_row(const RsRt&, int m_blk) { return m_blk * Cfg::BM; }
   __device__ static bool wait_a_ready(const RsRt&, int, volatile int*) { return true; }
   static constexpr bool kDirect = true;
+  static constexpr bool kSignalPerTile = true;
+  static constexpr bool kScatterRows = false;
+  __device__ static int b_row(const RsRt&, int, int n_blk) { return n_blk * Cfg::BN; }
   __device__ static void direct_targets(const RsRt& r, int m_blk, int n_blk, DirectTargets* t) {
     const GemmRsParams& p = *r.p;
     const int owner = m_blk / p.blocks_per_rank;

@@ -68,6 +68,9 @@ template <class Cfg>
 struct PlainPolicy {
   using P = PlainParams;
   static constexpr bool kDirect = false;
+  static constexpr bool kSignalPerTile = false;
+  static constexpr bool kScatterRows = false;
+  __device__ static int b_row(const P&, int, int n_blk) { return n_blk * Cfg::BN; }
   __device__ static int num_tiles(const P& p) { return p.g.num_m_blocks * p.g.num_n_blocks; }
   __device__ static void tile_coord(const P& p, int tile, int* m, int* n) {
     raster_tile(tile, p.g.num_m_blocks, p.g.num_n_blocks, p.raster_group, m, n);

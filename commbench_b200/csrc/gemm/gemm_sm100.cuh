@@ -102,6 +102,9 @@ struct GemmCtl {
 //                  const void* smem_box)       issued by one lane; must issue exactly one
 //                                              bulk-group worth of stores (commit is done here)
 //   void direct_targets(const P&, int m_blk, int n_blk, DirectTargets*)
+//   int  b_row(const P&, int m_blk, int n_blk)  row coordinate of the B tile in map_b
+//   direct policies also: kSignalPerTile (signal warp raises a flag per tile) and
+//   kScatterRows (+ uint8_t* row_base(const P&, int m_blk, int row): per-row destinations)
 //   void tile_done(const P&, int m_blk, int n_blk, int quadrant)  after the quadrant's boxes
 //                                              were issued (one lane)
 template <class Cfg, class Policy, class P>
@@ -124,7 +127,7 @@ __device__ __forceinline__ void gemm_producer(const P& p, const GemmShape& g, ui
       uint8_t* sb = sa + Cfg::A_BYTES;
       mbar_arrive_expect_tx(&ctl->full[stage], Cfg::STAGE_BYTES);
       tma_load_2d(sa, ma, kb * Cfg::BK, arow, &ctl->full[stage]);
-      tma_load_2d(sb, mb, kb * Cfg::BK, n_blk * Cfg::BN, &ctl->full[stage]);
+      tma_load_2d(sb, mb, kb * Cfg::BK, Policy::b_row(p, m_blk, n_blk), &ctl->full[stage]);
       if (++stage == Cfg::STAGES) {
         stage = 0;
         phase ^= 1u;
@@ -278,7 +281,11 @@ __device__ __forceinline__ void gemm_epilogue_direct(const P& p, const GemmShape
         const uint32_t r = 2u * i + (lane >> 4);
         const int row = static_cast<int>(q * 32u + r);
         const uint4 v = *reinterpret_cast<const uint4*>(buf + r * 256u + ((idx ^ (r & 7u)) * 16u));
-        if (col_ok && row < tg.rows) {
+        if constexpr (Policy::kScatterRows) {
+          // Every output row has its own destination (MoE combine): look it up.
+          uint8_t* rb = col_ok ? Policy::row_base(p, m_blk, row) : nullptr;
+          if (rb != nullptr) st_sys_v4(rb + (static_cast<long long>(n_blk) * Cfg::BN + col) * 2ll, v);
+        } else if (col_ok && row < tg.rows) {
           const long long off = row * tg.ld_bytes + col * 2ll;
           for (int d = 0; d < tg.n; ++d) st_sys_v4(tg.base[d] + off, v);
         }
@@ -288,7 +295,7 @@ __device__ __forceinline__ void gemm_epilogue_direct(const P& p, const GemmShape
     // Hand the tile to the signal warp: it runs the (slow, ~20 us under store traffic)
     // system-scope fence and raises the flag while these warps go on with the next tile.
     __syncwarp();
-    if (lane == 0) {
+    if (Policy::kSignalPerTile && lane == 0) {
       const uint32_t slot = seq & 7u;
       if (!mbar_wait(&ctl->sig_empty[slot], ((seq >> 3) & 1u) ^ 1u, &ctl->abort_flag, status,
                      0x800 + slot))
@@ -478,7 +485,7 @@ __device__ __forceinline__ void gemm_cta_main(const P& p, const GemmShape& g, ui
   } else if (warp < 6) {
     gemm_epilogue<Cfg, Policy>(p, g, epi, &ctl, status, cta, num_ctas, tmem_base, warp, lane);
   } else {
-    if constexpr (Policy::kDirect) {
+    if constexpr (Policy::kDirect && Policy::kSignalPerTile) {
       if (lane == 0) gemm_signal<Cfg, Policy>(p, &ctl, status, cta, num_ctas);
     }
   }

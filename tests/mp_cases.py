@@ -190,6 +190,63 @@ def main():
                     ctx.check_status()
                     report(f"gemm_ar/M{M}/oneshot{int(oneshot)}/{it}", close(o, part))
 
+    @guarded("moe")
+    def t_moe():
+        from commbench_b200.ops.moe import MoELayer, reference_moe, router_topk
+
+        T, H, I, E, K = 256, 1024, 512, 8 * world, 4
+        layer = MoELayer(ctx, T, H, I, E, K, capacity_factor=4.0, seed=3)
+        g = torch.Generator(device="cuda").manual_seed(500 + rank)
+        x = torch.randn(T, H, device="cuda", generator=g).bfloat16()
+        idx, w = router_topk(torch.randn(T, E, device="cuda", generator=g), K)
+        w1, w2 = layer.weights()
+        w1_all = torch.cat(gather_all(w1.contiguous()))
+        w2_all = torch.cat(gather_all(w2.contiguous()))
+        ref = reference_moe(x, idx, w, w1_all, w2_all, I)
+        for it in range(3):
+            y = layer.forward(x, idx, w)
+            ctx.check_status()
+            err = ((y.float() - ref).abs().max() / (ref.abs().max() + 1e-6)).item()
+            report(f"moe/{it}", err < 3e-2, err)
+
+    @guarded("attention")
+    def t_attention():
+        from commbench_b200.ops.cp import (RingAttention, reference_attention, ulysses_attention,
+                                           zigzag_chunks)
+
+        B, Sl, Hq, Hkv = 1, 512, 2 * world, world
+        S = Sl * world
+        g = torch.Generator(device="cuda").manual_seed(4242)      # same global tensors everywhere
+        qg = torch.randn(B, S, Hq, 128, device="cuda", generator=g).bfloat16()
+        kg = torch.randn(B, S, Hkv, 128, device="cuda", generator=g).bfloat16()
+        vg = torch.randn(B, S, Hkv, 128, device="cuda", generator=g).bfloat16()
+        ref, _ = reference_attention(qg, kg, vg, causal=True)
+        # contiguous sharding (Ulysses, ring without zigzag)
+        sl = slice(rank * Sl, (rank + 1) * Sl)
+        q, k, v = qg[:, sl].contiguous(), kg[:, sl].contiguous(), vg[:, sl].contiguous()
+        o = ulysses_attention(ctx, q, k, v, causal=True)
+        ctx.check_status()
+        report("ulysses", torch.allclose(o.float(), ref[:, sl], atol=3e-2, rtol=3e-2),
+               (o.float() - ref[:, sl]).abs().max().item())
+        ring = RingAttention(ctx, B, Sl, Hq, Hkv, zigzag=False)
+        for it in range(2):
+            o, _ = ring.forward(q, k, v, causal=True)
+            ctx.check_status()
+            report(f"ring/contiguous/{it}", torch.allclose(o.float(), ref[:, sl], atol=3e-2, rtol=3e-2),
+                   (o.float() - ref[:, sl]).abs().max().item())
+        # zigzag sharding: rank r owns chunks r and 2W-1-r of the sequence
+        h = Sl // 2
+        a, b = zigzag_chunks(world, rank)
+        pick = torch.cat([torch.arange(a * h, (a + 1) * h), torch.arange(b * h, (b + 1) * h)]).cuda()
+        qz, kz, vz = (t.index_select(1, pick).contiguous() for t in (qg, kg, vg))
+        ringz = RingAttention(ctx, B, Sl, Hq, Hkv, zigzag=True)
+        o, _ = ringz.forward(qz, kz, vz, causal=True)
+        ctx.check_status()
+        rz = ref.index_select(1, pick)
+        report("ring/zigzag", torch.allclose(o.float(), rz, atol=3e-2, rtol=3e-2),
+               (o.float() - rz).abs().max().item())
+
+    t_moe(); t_attention()
     t_all_reduce(); t_all_gather(); t_reduce_scatter(); t_all_to_all(); t_broadcast()
     t_ag_gemm(); t_gemm_rs(); t_gemm_ar()
     torch.cuda.synchronize()

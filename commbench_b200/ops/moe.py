@@ -252,6 +252,21 @@ class MoELayer:
     launches_per_call = 11
 
 
+def expert_sort(topk_idx: torch.Tensor, num_experts: int):
+    """Stable sort of the (token, k) selections by expert id.  Returns
+    (sorted_pair [n] int32, counts [E] int32); masked (negative) selections are left out and
+    the unused tail of ``sorted_pair`` is -1."""
+    lib = N.load()
+    idx = topk_idx.to(torch.int32).contiguous().view(-1)
+    n = idx.numel()
+    scratch = torch.empty(n + num_experts, dtype=torch.int32, device=idx.device)
+    sorted_pair = torch.full((n,), -1, dtype=torch.int32, device=idx.device)
+    counts = torch.empty(num_experts, dtype=torch.int32, device=idx.device)
+    N.check(lib.cb_moe_expert_sort(N.ptr(idx), n, num_experts, N.ptr(scratch), N.ptr(sorted_pair),
+                                   N.ptr(counts), N.stream_ptr()), "cb_moe_expert_sort")
+    return sorted_pair, counts
+
+
 def reference_moe(xs, topk_idx, topk_w, w1_all, w2_all, I: int):
     """Plain PyTorch fp32 reference of the whole layer for ONE source rank's tokens.
     `w1_all` [E, 2I, H], `w2_all` [E, H, I] (all experts).  Emulates the fp8 payload

@@ -67,3 +67,18 @@ def test_moe_layer_virtual_ranks(native_lib, world):
             err = (ys[r].float() - ref).abs().max().item()
             scale = ref.abs().max().item() + 1e-6
             assert err / scale < 3e-2, (it, r, err, scale)
+
+
+@pytest.mark.parametrize("n,E", [(100, 4), (4096 * 8, 256), (777, 33)])
+def test_expert_sort_is_a_stable_sort(native_lib, n, E):
+    from commbench_b200.ops.moe import expert_sort
+
+    g = torch.Generator(device="cuda").manual_seed(n)
+    idx = torch.randint(0, E, (n,), device="cuda", generator=g, dtype=torch.int32)
+    idx[::11] = -1
+    sp, counts = expert_sort(idx, E)
+    valid = (idx >= 0).nonzero().squeeze(1)
+    order = valid[torch.sort(idx[valid].long(), stable=True).indices]
+    assert torch.equal(sp[:order.numel()].long(), order)
+    assert bool((sp[order.numel():] == -1).all())
+    assert torch.equal(counts.long(), torch.bincount(idx[valid].long(), minlength=E))

@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
 #include <string>
 
 namespace cb {
@@ -71,11 +72,61 @@ static int run_expert_sort(const int* topk_idx, int n_pairs, int E, int* scratch
   return 0;
 }
 
+// Scratch of the allocation-free entry point.  In host code this name is only a handle for
+// cudaGetSymbolAddress: it is NOT a device address and must never be passed to a kernel.
+static __device__ __align__(256) int
+    g_esort_static_scratch[CB_EXPERT_SORT_STATIC_MAX_PAIRS + CB_EXPERT_SORT_STATIC_MAX_EXPERTS];
+
+static constexpr int kMaxDevices = 64;
+static int* g_esort_scratch_addr[kMaxDevices] = {};  // device address of the array, per device
+static std::mutex g_esort_mutex;
+
+// Device address of the static scratch on the CURRENT device (looked up once per device).
+static int* esort_static_scratch() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    set_last_error("expert sort (no-alloc): cannot identify the current device");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_esort_mutex);
+  if (g_esort_scratch_addr[dev] == nullptr) {
+    int* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_esort_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_last_error(std::string("expert sort (no-alloc): cudaGetSymbolAddress: ") +
+                     cudaGetErrorString(e));
+      return nullptr;
+    }
+    g_esort_scratch_addr[dev] = p;
+  }
+  return g_esort_scratch_addr[dev];
+}
+
 }  // namespace cb
 
 using namespace cb;
 
 extern "C" {
+
+int cb_moe_expert_sort_noalloc(const void* topk_idx, int n_pairs, int E, void* sorted_pair,
+                               void* counts, void* stream) {
+  if (n_pairs < 1 || E < 1) {
+    set_last_error("expert sort (no-alloc): need n_pairs >= 1 and E >= 1");
+    return -1;
+  }
+  if (n_pairs > CB_EXPERT_SORT_STATIC_MAX_PAIRS || E > CB_EXPERT_SORT_STATIC_MAX_EXPERTS) {
+    set_last_error("expert sort (no-alloc): problem exceeds the built-in scratch (" +
+                   std::to_string(CB_EXPERT_SORT_STATIC_MAX_PAIRS) + " selections, " +
+                   std::to_string(CB_EXPERT_SORT_STATIC_MAX_EXPERTS) +
+                   " experts); use cb_moe_expert_sort with your own scratch");
+    return -1;
+  }
+  int* scratch = esort_static_scratch();
+  if (scratch == nullptr) return -1;
+  return run_expert_sort(static_cast<const int*>(topk_idx), n_pairs, E, scratch,
+                         static_cast<int*>(sorted_pair), static_cast<int*>(counts),
+                         static_cast<cudaStream_t>(stream));
+}
 
 int cb_moe_expert_sort(const void* topk_idx, int n_pairs, int E, void* scratch, void* sorted_pair,
                        void* counts, void* stream) {

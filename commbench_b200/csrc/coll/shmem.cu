@@ -79,7 +79,8 @@ __global__ void atomic_fetch_inc_kernel(unsigned long long* counter, int n,
                                         unsigned long long* tickets, unsigned long long* cycles) {
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
   const long long t0 = clock64();
-  for (int i = 0; i < n; ++i) tickets[i] = atom_add_relaxed_sys_u64(counter, 1ull);
+  for (int i = 0; i < n; ++i)
+    tickets[i] = atom_add_relaxed_sys_u64(reinterpret_cast<uint64_t*>(counter), 1ull);
   *cycles = static_cast<unsigned long long>(clock64() - t0);
 }
 

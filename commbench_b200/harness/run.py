@@ -1,0 +1,322 @@
+"""Correctness + performance harness: runs a suite of ops on seeded random inputs, checks each
+against an fp32/fp64 or NCCL reference, times ours and the unfused NCCL(+cuBLAS) baseline on the
+device (CUDA events, max over ranks, warm-up first), and writes ``summary.json`` / ``summary.csv``
+with speed-up, bytes/FLOPs, fraction of roofline and verdict per entry.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node W --master-addr 127.0.0.1 \
+        -m commbench_b200.harness.run --suite allreduce,tp,moe,cp --out gpurun_out/harness_wW
+
+Suites follow the five target configurations (all-reduce sweep; tensor-parallel fused GEMMs;
+MoE layer; context-parallel attention) plus ``coll`` for the other collectives.  One process per
+GPU; with W=1 the multi-rank entries degenerate to their local kernels.
+
+Replaces the reference's per-example ``build_and_run.py --compare`` loop (ref vs generated
+rebuilt and rerun back to back: datasets/example001_gpu_comm_single_process/nv/build_and_run.py:488-693)
+with "ours vs baseline" in one process.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--suite", default="allreduce,tp")
+    ap.add_argument("--out", default="gpurun_out/harness")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--quick", action="store_true", help="coarser sweeps (every 4th size)")
+    ap.add_argument("--scale", type=float, default=1.0,
+                    help="shrink the MoE / attention shapes (1.0 = the target configurations)")
+    args = ap.parse_args(argv)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from ..baseline import nccl as base
+    from ..ops import collectives as coll
+    from ..runtime.context import CommContext
+    from . import report, roofline
+
+    ctx = CommContext(heap_bytes=4 << 30)
+    peaks = roofline.load_peaks()
+    store = report.ResultStore(os.path.join(args.out, f"results_rank{rank}.jsonl"))
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn) -> float:
+        for _ in range(args.warmup):
+            fn()
+        sync_all()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.iters):
+            fn()
+        e1.record()
+        sync_all()
+        ms = torch.tensor([e0.elapsed_time(e1) / args.iters], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    def all_ok(flag: bool) -> bool:
+        t = torch.tensor([1 if flag else 0], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item())
+
+    def gather(x):
+        if world == 1:
+            return [x]
+        outs = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(outs, x)
+        return outs
+
+    def record(op, variant, shape, dtype, **kw):
+        rec = dict(key=report.config_key(op, variant, shape, dtype, world), op=op, variant=variant,
+                   shape=list(shape), dtype=dtype, world=world, **kw)
+        store.add(rec)
+        if rank == 0:
+            print(json.dumps({k: (round(v, 5) if isinstance(v, float) else v)
+                              for k, v in rec.items() if k != "key"}), flush=True)
+
+    suites = [s.strip() for s in args.suite.split(",") if s.strip()]
+
+    # ------------------------------------------------------------- all-reduce sweep
+    if "allreduce" in suites:
+        step = 2 if args.quick else 1
+        sizes = [1 << p for p in range(12, 31, step)]           # 4 KB ... 1 GB
+        algos = ["oneshot", "twoshot"] + (["nvls"] if ctx.has_multicast else [])
+        if world == 1:
+            algos = ["oneshot"]
+        for nbytes in sizes:
+            n = nbytes // 2
+            g = torch.Generator(device=dev).manual_seed(rank)
+            x = (torch.rand(n, device=dev, generator=g) * 2 - 1).bfloat16()
+            ref = None
+            if nbytes <= (64 << 20):
+                ref = sum(t.float() for t in gather(x))
+            sym, _ = ctx.empty((n,), torch.bfloat16)
+            base_ms = timed(lambda: base.all_reduce(x.clone())) if world > 1 else None
+            clone_ms = timed(lambda: x.clone()) if world > 1 else 0.0
+            if base_ms is not None:
+                base_ms = max(base_ms - clone_ms, 1e-6)
+            for algo in algos:
+                if algo == "oneshot" and nbytes > (16 << 20):
+                    continue
+                sym.copy_(x)
+                sync_all()
+                if algo == "oneshot":
+                    out = torch.empty_like(x)
+                    y = coll.all_reduce(ctx, sym, out=out, algo=algo)
+                    fn = lambda: coll.all_reduce(ctx, sym, out=out, algo="oneshot", max_blocks=148)
+                else:
+                    y = coll.all_reduce(ctx, sym, algo=algo)
+                    fn = lambda a=algo: coll.all_reduce(ctx, sym, algo=a, max_blocks=148)
+                ctx.check_status()
+                correct, err = True, None
+                if ref is not None:
+                    err = (y.float() - ref).abs().max().item()
+                    correct = all_ok(err <= 2e-2 * max(1.0, ref.abs().max().item()))
+                ms = timed(fn)
+                ctx.check_status()
+                f = roofline.allreduce_bus_factor(world)
+                link = roofline.nvlink_bytes("all_reduce", nbytes, world, nvls=(algo == "nvls"))
+                record("all_reduce", algo, (n,), "bf16", correct=correct, max_err=err, time_ms=ms,
+                       baseline_ms=base_ms, busbw_gbs=f * nbytes / (ms * 1e-3) / 1e9,
+                       baseline_busbw_gbs=(f * nbytes / (base_ms * 1e-3) / 1e9) if base_ms else None,
+                       roofline_frac=roofline.fraction(roofline.roofline_ms(0, link, peaks), ms),
+                       roofline_note=f"of {peaks.source}")
+
+    # ----------------------------------------------------------- other collectives
+    if "coll" in suites and world > 1:
+        for mb in ((16, 256) if args.quick else (1, 16, 64, 256)):
+            nbytes = mb << 20
+            rows = nbytes // (world * 256 * 2) * world
+            x = torch.randn(rows, 256, device=dev).bfloat16()
+            shard = x[: rows // world].contiguous()
+            for op, ours, theirs, ref_fn, link_op, size in (
+                ("all_gather", lambda: coll.all_gather(ctx, shard, max_blocks=64),
+                 lambda: base.all_gather(shard), None, "all_gather", nbytes),
+                ("reduce_scatter", lambda: coll.reduce_scatter(ctx, x, max_blocks=64),
+                 lambda: base.reduce_scatter(x), None, "reduce_scatter", nbytes),
+                ("all_to_all", lambda: coll.all_to_all(ctx, x, max_blocks=64),
+                 lambda: base.all_to_all(x), None, "all_to_all", nbytes),
+            ):
+                a, b = ours(), theirs()
+                ctx.check_status()
+                tol = 5e-2 if op == "reduce_scatter" else 0.0
+                correct = all_ok(torch.allclose(a.float(), b.float(), atol=tol, rtol=tol))
+                ms, bms = timed(ours), timed(theirs)
+                link = roofline.nvlink_bytes(link_op, size, world)
+                record(op, "auto", tuple(x.shape), "bf16", correct=correct, time_ms=ms,
+                       baseline_ms=bms, busbw_gbs=link / (ms * 1e-3) / 1e9,
+                       roofline_frac=roofline.fraction(roofline.roofline_ms(0, link, peaks), ms))
+
+    # ------------------------------------------------- tensor-parallel fused GEMMs
+    if "tp" in suites:
+        from ..ops.gemm import gemm
+        from ..ops.tp import AgGemm, GemmAr, GemmRs
+
+        def rnd(shape, seed, scale=0.02):
+            g = torch.Generator(device=dev).manual_seed(seed)
+            return (torch.randn(shape, device=dev, generator=g) * scale).bfloat16()
+
+        M, K, N = 8192, 8192, 28672
+        a_loc, b1 = rnd((M // world, K), 1 + rank, 1.0), rnd((N // world, K), 100 + rank)
+        if world > 1:
+            ag = AgGemm(ctx, M, K)
+            ours = lambda: ag(a_loc, b1)
+            theirs = lambda: base.ag_gemm(a_loc, b1)
+        else:
+            ours = lambda: gemm(a_loc, b1)
+            theirs = lambda: torch.matmul(a_loc, b1.t())
+        c, r = ours(), theirs()
+        ctx.check_status()
+        err = ((c.float() - r.float()).abs().max() / (r.float().abs().max() + 1e-9)).item()
+        ms, bms = timed(ours), timed(theirs)
+        fl = 2.0 * M * K * (N // world)
+        link = roofline.nvlink_bytes("all_gather", M * K * 2, world)
+        record("ag_gemm", "bf16", (M, N // world, K), "bf16", correct=all_ok(err < 2e-2), max_err=err,
+               time_ms=ms, baseline_ms=bms, tflops=fl / (ms * 1e-3) / 1e12,
+               roofline_frac=roofline.fraction(roofline.roofline_ms(fl, link, peaks, True), ms))
+        a2, b2 = rnd((M, N // world), 200 + rank, 0.05), rnd((K, N // world), 300 + rank)
+        if world > 1:
+            rs = GemmRs(ctx, M, K)
+            ours = lambda: rs(a2, b2)
+            theirs = lambda: base.gemm_rs(a2, b2)
+        else:
+            ours = lambda: gemm(a2, b2)
+            theirs = lambda: torch.matmul(a2, b2.t())
+        c, r = ours(), theirs()
+        ctx.check_status()
+        err = ((c.float() - r.float()).abs().max() / (r.float().abs().max() + 1e-9)).item()
+        ms, bms = timed(ours), timed(theirs)
+        fl = 2.0 * M * K * (N // world)
+        link = roofline.nvlink_bytes("reduce_scatter", M * K * 2, world)
+        record("gemm_rs", "bf16", (M, K, N // world), "bf16", correct=all_ok(err < 2e-2), max_err=err,
+               time_ms=ms, baseline_ms=bms, tflops=fl / (ms * 1e-3) / 1e12,
+               roofline_frac=roofline.fraction(roofline.roofline_ms(fl, link, peaks, True), ms))
+        Kd, Nd = 8192 // world, 8192
+        if world > 1:
+            ar = GemmAr(ctx, 1024, Nd)
+        for Md in (16, 128, 1024):
+            a3, b3 = rnd((Md, Kd), 400 + rank, 1.0), rnd((Nd, Kd), 500 + rank)
+            for variant in (("oneshot", True), ("twoshot", False)) if world > 1 else (("local", None),):
+                if world > 1:
+                    ours = lambda v=variant[1]: ar(a3, b3, oneshot=v)
+                    theirs = lambda: base.gemm_ar(a3, b3)
+                else:
+                    ours = lambda: gemm(a3, b3)
+                    theirs = lambda: torch.matmul(a3, b3.t())
+                c, r = ours(), theirs()
+                ctx.check_status()
+                err = ((c.float() - r.float()).abs().max() / (r.float().abs().max() + 1e-9)).item()
+                ms, bms = timed(ours), timed(theirs)
+                fl = 2.0 * Md * Kd * Nd
+                link = roofline.nvlink_bytes("all_reduce", Md * Nd * 2, world)
+                record("gemm_ar", variant[0], (Md, Nd, Kd), "bf16", correct=all_ok(err < 2e-2),
+                       max_err=err, time_ms=ms, baseline_ms=bms, tflops=fl / (ms * 1e-3) / 1e12,
+                       roofline_frac=roofline.fraction(roofline.roofline_ms(fl, link, peaks), ms))
+
+    # ----------------------------------------------------------------- MoE layer
+    if "moe" in suites:
+        from ..ops.moe import MoELayer, router_topk
+
+        T = max(256, int(4096 * args.scale) // 128 * 128)
+        H, I, E, K = 7168, 2048, 256, 8
+        layer = MoELayer(ctx, T, H, I, E, K, capacity_factor=1.5)
+        g = torch.Generator(device=dev).manual_seed(7 + rank)
+        x = torch.randn(T, H, device=dev, generator=g).bfloat16()
+        idx, w = router_topk(torch.randn(T, E, device=dev, generator=g), K)
+        w1, w2 = layer.weights()
+        y = layer.forward(x, idx, w).clone()
+        ctx.check_status()
+        if world > 1:
+            r = base.moe_layer(x, idx, w, w1, w2, E, I)
+            theirs = lambda: base.moe_layer(x, idx, w, w1, w2, E, I)
+        else:
+            from ..ops.moe import reference_moe
+
+            r = reference_moe(x, idx, w, w1, w2, I).bfloat16()
+            theirs = None
+        err = ((y.float() - r.float()).abs().max() / (r.float().abs().max() + 1e-9)).item()
+        ms = timed(lambda: layer.forward(x, idx, w))
+        bms = timed(theirs) if theirs else None
+        fl = 2.0 * T * K * H * (3 * I)         # per rank, balanced routing
+        link = T * K * (world - 1) / world * (H + H * 2)     # fp8 out, bf16 back
+        record("moe_layer", "fp8-dispatch", (T, H, I, E, K), "bf16", correct=all_ok(err < 6e-2),
+               max_err=err, time_ms=ms, baseline_ms=bms, tflops=fl / (ms * 1e-3) / 1e12,
+               roofline_frac=roofline.fraction(roofline.roofline_ms(fl, link, peaks, True), ms))
+
+    # ------------------------------------------------------- context-parallel attention
+    if "cp" in suites:
+        from ..ops.cp import RingAttention, ulysses_attention
+
+        Sl = max(512, int(16384 * args.scale) // 256 * 256)
+        B, Hq, Hkv = 1, 32, 8
+        g = torch.Generator(device=dev).manual_seed(rank)
+        q = torch.randn(B, Sl, Hq, 128, device=dev, generator=g).bfloat16()
+        k = torch.randn(B, Sl, Hkv, 128, device=dev, generator=g).bfloat16()
+        v = torch.randn(B, Sl, Hkv, 128, device=dev, generator=g).bfloat16()
+        S = Sl * world
+        fl = 4.0 * Sl * S * 128 * Hq / 2            # causal, per rank on average
+        theirs = (lambda: base.ulysses_attention(q, k, v)) if world > 1 else \
+            (lambda: torch.nn.functional.scaled_dot_product_attention(
+                q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3), v.permute(0, 2, 1, 3),
+                is_causal=True, enable_gqa=True))
+        r = theirs()
+        if world == 1:
+            r = r.permute(0, 2, 1, 3)
+        bms = timed(theirs)
+        o = ulysses_attention(ctx, q, k, v)
+        ctx.check_status()
+        err = (o.float() - r.float()).abs().max().item()
+        ms = timed(lambda: ulysses_attention(ctx, q, k, v))
+        link = 4 * (world - 1) / world * q.numel() * 2 * (1 + 2 * Hkv / Hq) / 2 if world > 1 else 0
+        record("ulysses_attention", "causal", (B, S, Hq, Hkv, 128), "bf16", correct=all_ok(err < 5e-2),
+               max_err=err, time_ms=ms, baseline_ms=bms, tflops=fl / (ms * 1e-3) / 1e12,
+               roofline_frac=roofline.fraction(roofline.roofline_ms(fl, link, peaks, True), ms))
+        ring = RingAttention(ctx, B, Sl, Hq, Hkv, zigzag=False)
+        o2, _ = ring.forward(q, k, v)
+        ctx.check_status()
+        err2 = (o2.float() - r.float()).abs().max().item()
+        ms2 = timed(lambda: ring.forward(q, k, v))
+        link2 = (world - 1) * 2 * k.numel() * 2
+        record("ring_attention", "causal-contiguous", (B, S, Hq, Hkv, 128), "bf16",
+               correct=all_ok(err2 < 5e-2), max_err=err2, time_ms=ms2, baseline_ms=bms,
+               tflops=fl / (ms2 * 1e-3) / 1e12,
+               roofline_frac=roofline.fraction(roofline.roofline_ms(fl, link2, peaks, True), ms2))
+
+    sync_all()
+    if rank == 0:
+        s = report.write_summary(store.records(), args.out,
+                                 meta={"world": world, "suites": suites, "peaks": peaks.__dict__,
+                                       "symmetric_memory": {"mode": ctx.mode,
+                                                            "multicast": ctx.has_multicast}})
+        print(json.dumps({"summary": os.path.join(args.out, "summary.json"),
+                          "entries": len(s["entries"]), "all_correct": s["all_correct"],
+                          "geomean_speedup": s["geomean_speedup"], "counts": s["counts"]}), flush=True)
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

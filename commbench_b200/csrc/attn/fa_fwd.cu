@@ -17,7 +17,8 @@
 //              chunks (two passes: row max, then exp/sum), P goes to shared memory in the
 //              swizzled K-major layout the second MMA reads, O lives in registers
 //              (O = O * alpha + PV after each block).
-// S is double-buffered in TMEM so QK^T of block j+1 overlaps the softmax of block j.
+// S, P and PV are double-buffered so QK^T of block j+1 and P*V of block j-1 both overlap the
+// softmax of block j.
 // Every mbarrier wait is bounded (see mbarrier.cuh).
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -36,7 +37,7 @@ static constexpr int FA_BN = 128;   // keys per block
 static constexpr int FA_D = 128;    // head dim
 static constexpr int FA_SUB = 16384;  // bytes of one [128 x 64] bf16 sub-tile
 static constexpr int FA_SMEM = 2 * FA_SUB /*Q*/ + 2 * 2 * FA_SUB /*K x2*/ + 2 * 2 * FA_SUB /*V x2*/ +
-                               2 * FA_SUB /*P*/ + 1024;
+                               2 * 2 * FA_SUB /*P x2*/ + 1024;
 static constexpr int FA_THREADS = 192;
 
 struct FaParams {
@@ -56,8 +57,8 @@ struct FaCtl {
   uint64_t q_full;
   uint64_t k_full[2], v_full[2], kv_empty[2];
   uint64_t s_full[2], s_empty[2];
-  uint64_t p_full, p_empty;
-  uint64_t pv_full, pv_empty;
+  uint64_t p_full[2], p_empty[2];
+  uint64_t pv_full[2], pv_empty[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -73,6 +74,13 @@ __device__ __forceinline__ uint64_t make_sw128_mnmajor_desc(uint32_t smem_addr) 
   d |= static_cast<uint64_t>(1) << 46;
   d |= static_cast<uint64_t>(2) << 61;
   return d;
+}
+
+// 2^x on the special-function unit (the softmax spends most of its instructions here).
+__device__ __forceinline__ float fa_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 __device__ __forceinline__ int fa_num_blocks(const FaParams& p, int q_tile) {
@@ -110,10 +118,12 @@ __global__ void __launch_bounds__(FA_THREADS, 1) fa_fwd_kernel(const __grid_cons
       mbar_init(&ctl.s_full[i], 1);
       mbar_init(&ctl.s_empty[i], 4);
     }
-    mbar_init(&ctl.p_full, 4);
-    mbar_init(&ctl.p_empty, 1);
-    mbar_init(&ctl.pv_full, 1);
-    mbar_init(&ctl.pv_empty, 4);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&ctl.p_full[i], 4);
+      mbar_init(&ctl.p_empty[i], 1);
+      mbar_init(&ctl.pv_full[i], 1);
+      mbar_init(&ctl.pv_empty[i], 4);
+    }
     ctl.abort_flag = 0;
     fence_mbar_init();
   }
@@ -126,7 +136,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) fa_fwd_kernel(const __grid_cons
   tc_fence_after_sync();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&ctl.tmem_base);
   const uint32_t tS[2] = {tmem, tmem + 128u};
-  const uint32_t tPV = tmem + 256u;
+  const uint32_t tPV[2] = {tmem + 256u, tmem + 384u};
 
   if (warp == 0) {
     if (lane == 0 && nblk > 0) {
@@ -156,20 +166,21 @@ __global__ void __launch_bounds__(FA_THREADS, 1) fa_fwd_kernel(const __grid_cons
       bool ok = mbar_wait(&ctl.q_full, 0, &ctl.abort_flag, p.status, 0xA10);
       auto issue_pv = [&](int j) -> bool {
         const int s = j & 1;
-        if (!mbar_wait(&ctl.p_full, j & 1, &ctl.abort_flag, p.status, 0xA20)) return false;
-        if (!mbar_wait(&ctl.v_full[s], (j >> 1) & 1, &ctl.abort_flag, p.status, 0xA21)) return false;
-        if (!mbar_wait(&ctl.pv_empty, (j & 1) ^ 1u, &ctl.abort_flag, p.status, 0xA22)) return false;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&ctl.p_full[s], ph, &ctl.abort_flag, p.status, 0xA20)) return false;
+        if (!mbar_wait(&ctl.v_full[s], ph, &ctl.abort_flag, p.status, 0xA21)) return false;
+        if (!mbar_wait(&ctl.pv_empty[s], ph ^ 1u, &ctl.abort_flag, p.status, 0xA22)) return false;
         tc_fence_after_sync();
-        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + s * 2 * FA_SUB);
+        const uint32_t pa = smem_u32(sP + s * 2 * FA_SUB), va = smem_u32(sV + s * 2 * FA_SUB);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint64_t a_desc = make_sw128_kmajor_desc(pa + (kk >> 2) * FA_SUB) + 2u * (kk & 3);
           const uint64_t b_desc = make_sw128_mnmajor_desc(va + kk * 2048);
-          mma_bf16_ss(tPV, a_desc, b_desc, idesc_pv, kk > 0 ? 1u : 0u);
+          mma_bf16_ss(tPV[s], a_desc, b_desc, idesc_pv, kk > 0 ? 1u : 0u);
         }
-        mma_commit(&ctl.pv_full);
+        mma_commit(&ctl.pv_full[s]);
         mma_commit(&ctl.kv_empty[s]);
-        mma_commit(&ctl.p_empty);
+        mma_commit(&ctl.p_empty[s]);
         return true;
       };
       for (int j = 0; ok && j < nblk; ++j) {
@@ -200,32 +211,67 @@ __global__ void __launch_bounds__(FA_THREADS, 1) fa_fwd_kernel(const __grid_cons
 #pragma unroll
     for (int i = 0; i < FA_D; ++i) o[i] = 0.f;
     float m = -INFINITY, l = 0.f;
-    bool ok = true;
-    for (int j = 0; ok && j < nblk; ++j) {
+    // O += PV of block j is applied AFTER the softmax of block j+1, so the P*V MMA of block j
+    // runs while these warps are busy with the next block instead of being waited for.
+    auto o_update = [&](int j, float alpha) -> bool {
       const int b = j & 1;
-      if (!mbar_wait(&ctl.s_full[b], (j >> 1) & 1, &ctl.abort_flag, p.status, 0xA30)) break;
+      if (!mbar_wait(&ctl.pv_full[b], (j >> 1) & 1, &ctl.abort_flag, p.status, 0xA32)) return false;
       tc_fence_after_sync();
-      const int key0 = p.kv_offset + j * FA_BN;   // global position of the block's first key
-      const int kv_left = p.Skv - j * FA_BN;      // keys of this block that exist
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sr[32];
-        tmem_ld_32x32(tS[b] + lane_addr + c * 32u, sr);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t p0[32], p1[32];
+        tmem_ld_32x32(tPV[b] + lane_addr + c * 64u, p0);
+        tmem_ld_32x32(tPV[b] + lane_addr + c * 64u + 32u, p1);
         tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const int kc = c * 32 + i;
-          const bool vis = kc < kv_left && (!p.causal || key0 + kc <= q_pos);
-          if (vis) mx = fmaxf(mx, __uint_as_float(sr[i]));
+          o[c * 64 + i] = o[c * 64 + i] * alpha + __uint_as_float(p0[i]);
+          o[c * 64 + 32 + i] = o[c * 64 + 32 + i] * alpha + __uint_as_float(p1[i]);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl.pv_empty[b]);
+      return true;
+    };
+    float alpha_prev = 1.f;
+    bool ok = true;
+    for (int j = 0; ok && j < nblk; ++j) {
+      const int b = j & 1;
+      if (!mbar_wait(&ctl.s_full[b], (j >> 1) & 1, &ctl.abort_flag, p.status, 0xA30)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int key0 = p.kv_offset + j * FA_BN;   // global position of the block's first key
+      const int kv_left = p.Skv - j * FA_BN;      // keys of this block that exist
+      // Only blocks that touch the diagonal or the end of the keys need per-element masks.
+      const bool need_mask = kv_left < FA_BN ||
+                             (p.causal && key0 + FA_BN - 1 > p.q_offset + q_tile * FA_BM);
+      // pass 1: row maximum (64 columns per TMEM round trip)
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t s0[32], s1[32];
+        tmem_ld_32x32(tS[b] + lane_addr + c * 64u, s0);
+        tmem_ld_32x32(tS[b] + lane_addr + c * 64u + 32u, s1);
+        tmem_wait_ld();
+        if (!need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            mx = fmaxf(mx, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int k0 = c * 64 + i, k1 = k0 + 32;
+            if (k0 < kv_left && (!p.causal || key0 + k0 <= q_pos)) mx = fmaxf(mx, __uint_as_float(s0[i]));
+            if (k1 < kv_left && (!p.causal || key0 + k1 <= q_pos)) mx = fmaxf(mx, __uint_as_float(s1[i]));
+          }
         }
       }
       const float m_new = fmaxf(m, mx * p.scale_log2);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
       const float alpha = exp2f(m - m_use);  // m = -inf -> 0
       // pass 2: p = exp2(s*scale - m), row sum, bf16 P into shared memory
-      if (!mbar_wait(&ctl.p_empty, (j & 1) ^ 1u, &ctl.abort_flag, p.status, 0xA31)) break;
+      if (!mbar_wait(&ctl.p_empty[b], ((j >> 1) & 1) ^ 1u, &ctl.abort_flag, p.status, 0xA31)) { ok = false; break; }
+      uint8_t* sPb = sP + b * 2 * FA_SUB;
       float psum = 0.f;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
@@ -236,10 +282,12 @@ __global__ void __launch_bounds__(FA_THREADS, 1) fa_fwd_kernel(const __grid_cons
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
           const int kc = c * 32 + i;
-          const bool v0 = kc < kv_left && (!p.causal || key0 + kc <= q_pos);
-          const bool v1 = kc + 1 < kv_left && (!p.causal || key0 + kc + 1 <= q_pos);
-          const float p0 = v0 ? exp2f(__uint_as_float(sr[i]) * p.scale_log2 - m_use) : 0.f;
-          const float p1 = v1 ? exp2f(__uint_as_float(sr[i + 1]) * p.scale_log2 - m_use) : 0.f;
+          float p0 = fa_ex2(__uint_as_float(sr[i]) * p.scale_log2 - m_use);
+          float p1 = fa_ex2(__uint_as_float(sr[i + 1]) * p.scale_log2 - m_use);
+          if (need_mask) {
+            if (!(kc < kv_left && (!p.causal || key0 + kc <= q_pos))) p0 = 0.f;
+            if (!(kc + 1 < kv_left && (!p.causal || key0 + kc + 1 <= q_pos))) p1 = 0.f;
+          }
           __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
           // the row sum uses the rounded values, as the MMA will
           const float2 back = __bfloat1622float2(h);
@@ -251,7 +299,7 @@ __global__ void __launch_bounds__(FA_THREADS, 1) fa_fwd_kernel(const __grid_cons
         for (int cc = 0; cc < 4; ++cc) {
           const uint32_t chunk = c * 4u + cc;            // 0..15 along the 128 keys
           const uint32_t t = chunk >> 3, ci = chunk & 7u;
-          uint8_t* dst = sP + t * FA_SUB + r * 128u + ((ci ^ (r & 7u)) * 16u);
+          uint8_t* dst = sPb + t * FA_SUB + r * 128u + ((ci ^ (r & 7u)) * 16u);
           *reinterpret_cast<uint4*>(dst) = make_uint4(packed[cc * 4], packed[cc * 4 + 1],
                                                       packed[cc * 4 + 2], packed[cc * 4 + 3]);
         }
@@ -262,25 +310,14 @@ __global__ void __launch_bounds__(FA_THREADS, 1) fa_fwd_kernel(const __grid_cons
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&ctl.s_empty[b]);
-        mbar_arrive(&ctl.p_full);
+        mbar_arrive(&ctl.p_full[b]);
       }
       l = l * alpha + psum;
       m = m_new;
-      // O = O * alpha + PV
-      if (!mbar_wait(&ctl.pv_full, j & 1, &ctl.abort_flag, p.status, 0xA32)) break;
-      tc_fence_after_sync();
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pr[32];
-        tmem_ld_32x32(tPV + lane_addr + c * 32u, pr);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(pr[i]);
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl.pv_empty);
+      if (j > 0) ok = o_update(j - 1, alpha_prev);
+      alpha_prev = alpha;
     }
+    if (ok && nblk > 0) o_update(nblk - 1, alpha_prev);
     // ------------------------------------------------------------------ epilogue
     const int row = q_tile * FA_BM + static_cast<int>(r);
     if (row < p.Sq) {

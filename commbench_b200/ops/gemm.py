@@ -50,3 +50,48 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, alph
     if rc != 0:
         raise GemmError(f"gemm launch failed: {N.last_error()}")
     return out
+
+
+# ------------------------------------------------------------- block-scaled fp8 operands
+def quantize_blockscaled(x: torch.Tensor, row_block: int = 1):
+    """bf16 [rows, K] -> (e4m3 [rows, K], fp32 scales).  ``row_block=1``: one scale per row and
+    128 columns (activations, "1x128"); ``row_block=128``: one per 128x128 block (weights)."""
+    lib = N.load()
+    _check(x, "x")
+    rows, K = x.shape
+    q = torch.empty(rows, K, dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((rows + row_block - 1) // row_block, K // 128, dtype=torch.float32,
+                    device=x.device)
+    rc = lib.cb_quant_blockscaled(N.ptr(x), N.ptr(q), N.ptr(s), C.c_longlong(rows), K, row_block,
+                                  N.stream_ptr())
+    if rc != 0:
+        raise GemmError(N.last_error())
+    return q, s
+
+
+def dequantize_blockscaled(q: torch.Tensor, s: torch.Tensor, row_block: int = 1,
+                           out: torch.Tensor | None = None) -> torch.Tensor:
+    lib = N.load()
+    rows, K = q.shape
+    if out is None:
+        out = torch.empty(rows, K, dtype=torch.bfloat16, device=q.device)
+    rc = lib.cb_dequant_blockscaled(N.ptr(q), N.ptr(s), N.ptr(out), C.c_longlong(rows), K,
+                                    row_block, N.stream_ptr())
+    if rc != 0:
+        raise GemmError(N.last_error())
+    return out
+
+
+def gemm_fp8_blockscaled(a_q, a_s, b_q, b_s, out=None, b_cache: dict | None = None):
+    """``out = dequant(a_q, a_s [1x128]) @ dequant(b_q, b_s [128x128]).T``: fp8 storage with
+    block scales, bf16 tensor-core math.  ``b_cache`` (a dict) keeps the expanded weight across
+    calls, as a static weight needs expanding only once."""
+    a = dequantize_blockscaled(a_q, a_s, 1)
+    key = (b_q.data_ptr(), b_s.data_ptr())
+    if b_cache is not None and key in b_cache:
+        b = b_cache[key]
+    else:
+        b = dequantize_blockscaled(b_q, b_s, 128)
+        if b_cache is not None:
+            b_cache[key] = b
+    return gemm(a, b, out=out)

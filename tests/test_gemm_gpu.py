@@ -64,3 +64,31 @@ def test_gemm_fp8_matches_fp32_reference(native_lib, shape):
     b = torch.randn(N, K, device="cuda", generator=g).to(torch.float8_e4m3fn)
     out = gemm(a, b, alpha=0.25, bn=128)
     _check(out, _ref(a, b, 0.25), 1e-2)
+
+
+def test_blockscaled_fp8_roundtrip_and_gemm(native_lib):
+    """1x128 activation scales and 128x128 weight scales: quantise, check against a PyTorch
+    emulation of the same scheme, then run the GEMM on the expanded operands."""
+    from commbench_b200.ops.gemm import (dequantize_blockscaled, gemm_fp8_blockscaled,
+                                         quantize_blockscaled)
+
+    M, N, K = 256, 384, 512
+    g = torch.Generator(device="cuda").manual_seed(21)
+    a = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+    b = (torch.randn(N, K, device="cuda", generator=g) * 0.02).bfloat16()
+    aq, as_ = quantize_blockscaled(a, 1)
+    bq, bs = quantize_blockscaled(b, 128)
+    # reference quantisation
+    af = a.float().view(M, K // 128, 128)
+    ref_s = af.abs().amax(-1) / 448.0
+    assert torch.allclose(as_, ref_s, rtol=1e-6)
+    bf = b.float().view(N // 128, 128, K // 128, 128)
+    ref_bs = bf.abs().amax(dim=(1, 3)) / 448.0
+    assert torch.allclose(bs, ref_bs, rtol=1e-6)
+    ad = dequantize_blockscaled(aq, as_, 1)
+    bd = dequantize_blockscaled(bq, bs, 128)
+    assert (ad.float() - a.float()).abs().max() <= 0.07 * a.float().abs().max()
+    out = gemm_fp8_blockscaled(aq, as_, bq, bs)
+    ref = ad.float() @ bd.float().t()
+    _check(out, ref, 1e-2)
+    _check(out, a.float() @ b.float().t(), 6e-2)

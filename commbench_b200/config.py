@@ -20,10 +20,13 @@ class Config:
     ar_oneshot_max_bytes: int = 512 * 1024      # at or below: one-shot pull all-reduce
     ar_nvls_min_bytes: int = 512 * 1024         # at or above (with multicast bound): NVLS
     coll_max_blocks: int = 64                   # CTAs per collective kernel (<= one wave)
+    ar_oneshot_grain_bytes: int = 8 * 1024      # message bytes per CTA, one-shot all-reduce
+    ar_chunk_grain_bytes: int = 64 * 1024       # message bytes per CTA, two-shot / NVLS
     # --- fused GEMMs -------------------------------------------------------
     ag_gemm_comm_ctas: int = 8                  # CTAs reserved for pushing the local A shard
     gemm_rs_reduce_ctas: int = 0                # 0: reduction runs on all CTAs after their tiles
     gemm_ar_oneshot_max_m: int = 256            # rows at or below: one-shot AR epilogue
+    fused_poll_ns: int = 300                    # pause between polls of a peer-written flag
     # --- MoE ---------------------------------------------------------------
     moe_expert_alignment: int = 128             # rows per expert padded to a tile multiple
     # --- runtime -----------------------------------------------------------

@@ -71,6 +71,24 @@ __device__ __forceinline__ void copy_bytes_slice(void* dst, const void* src,
   }
 }
 
+// The per-channel rank barrier only orders block b of this rank against block b of
+// every peer.  So whatever block b of a PEER reads from this rank after the barrier must
+// have been written here by block b itself.  Algorithms that split the message into W rank
+// chunks and then split each chunk over the grid read "slice b of chunk <their rank>":
+// staging copies therefore walk slice b of EVERY chunk, not slice b of the whole message.
+template <class F>
+__device__ __forceinline__ void for_each_chunk_slice(unsigned long long nvec,
+                                                     unsigned long long per_rank, int world, F f) {
+  for (int r = 0; r < world; ++r) {
+    unsigned long long c0 = per_rank * r, c1 = c0 + per_rank;
+    if (c0 > nvec) c0 = nvec;
+    if (c1 > nvec) c1 = nvec;
+    unsigned long long s0, s1;
+    slice_of(c1 - c0, gridDim.x, blockIdx.x, &s0, &s1);
+    if (s1 > s0) f(c0 + s0, c0 + s1);
+  }
+}
+
 __device__ __forceinline__ uint32_t begin_epoch(const CbComm& c, uint32_t ch) {
   // Every thread reads the same word; no thread writes it before end_epoch's barrier.
   return ld_volatile(c.epoch + ch);
@@ -145,11 +163,10 @@ __global__ void __launch_bounds__(kCollThreads)
   const unsigned long long nvec = (a.nbytes + 15ull) / 16ull;
   const unsigned long long per_rank = (nvec + W - 1) / W;
 
-  if (a.copy_in) {
-    unsigned long long v0, v1;
-    slice_of(nvec, gridDim.x, blockIdx.x, &v0, &v1);
-    copy_bytes_slice(a.sym[c.rank], a.in, a.nbytes, v0, v1, true);
-  }
+  if (a.copy_in)
+    for_each_chunk_slice(nvec, per_rank, W, [&](unsigned long long v0, unsigned long long v1) {
+      copy_bytes_slice(a.sym[c.rank], a.in, a.nbytes, v0, v1, true);
+    });
   bool ok = rank_barrier_block(c, ch, e + 1, PH_BARRIER_START);
   if (ok) {
     // Phase 1 on my chunk.
@@ -192,7 +209,20 @@ __global__ void __launch_bounds__(kCollThreads)
       unsigned long long s0, s1;
       slice_of(c1 - c0, gridDim.x, blockIdx.x, &s0, &s1);
       const uint4* sp = static_cast<const uint4*>(a.sym[src]);
-      for (unsigned long long i = c0 + s0 + threadIdx.x; i < c0 + s1; i += blockDim.x) {
+      unsigned long long i = c0 + s0 + threadIdx.x;
+      // Whole vectors, four loads in flight per thread.
+      for (; i + 3ull * blockDim.x < c0 + s1 && i + 3ull * blockDim.x < full;
+           i += 4ull * blockDim.x) {
+        const uint4 x0 = ld_sys_v4(sp + i), x1 = ld_sys_v4(sp + i + blockDim.x),
+                    x2 = ld_sys_v4(sp + i + 2ull * blockDim.x),
+                    x3 = ld_sys_v4(sp + i + 3ull * blockDim.x);
+        uint4* d = reinterpret_cast<uint4*>(outb);
+        d[i] = x0;
+        d[i + blockDim.x] = x1;
+        d[i + 2ull * blockDim.x] = x2;
+        d[i + 3ull * blockDim.x] = x3;
+      }
+      for (; i < c0 + s1; i += blockDim.x) {
         const uint4 v = ld_sys_v4(sp + i);
         if (i < full || !a.copy_out) {
           *reinterpret_cast<uint4*>(outb + i * 16ull) = v;
@@ -219,9 +249,10 @@ __global__ void __launch_bounds__(kCollThreads)
   const uint32_t e = begin_epoch(c, ch);
   const unsigned long long nvec = (a.nbytes + 15ull) / 16ull;
   const unsigned long long per_rank = (nvec + W - 1) / W;
-  unsigned long long v0, v1;
-  slice_of(nvec, gridDim.x, blockIdx.x, &v0, &v1);
-  if (a.copy_in) copy_bytes_slice(a.sym[c.rank], a.in, a.nbytes, v0, v1, true);
+  if (a.copy_in)
+    for_each_chunk_slice(nvec, per_rank, W, [&](unsigned long long v0, unsigned long long v1) {
+      copy_bytes_slice(a.sym[c.rank], a.in, a.nbytes, v0, v1, true);
+    });
   bool ok = rank_barrier_block(c, ch, e + 1, PH_BARRIER_START);
   if (ok) {
     unsigned long long c0 = per_rank * c.rank, c1 = c0 + per_rank;
@@ -242,11 +273,16 @@ __global__ void __launch_bounds__(kCollThreads)
       mm_st_v4(mc + i + 3ull * blockDim.x, r3);
     }
     for (; i < c0 + s1; i += blockDim.x) mm_st_v4(mc + i, Vec16<DT>::mm_reduce(mc + i));
-    // multimem.st results must be visible on every rank before anyone reads them.
-    fence_acq_rel_sys();
+    // multimem.st results must be visible on every rank before anyone reads them: the
+    // barrier's CTA sync followed by its release stores orders them (a system fence by
+    // every thread here costs tens of microseconds under store traffic).
     ok = rank_barrier_block(c, ch, e + 2, PH_BARRIER_END);
   }
-  if (ok && a.copy_out) copy_bytes_slice(a.out, a.sym[c.rank], a.nbytes, v0, v1, false);
+  // Slice b of every chunk was written by block b of that chunk's owner: safe to read now.
+  if (ok && a.copy_out)
+    for_each_chunk_slice(nvec, per_rank, W, [&](unsigned long long v0, unsigned long long v1) {
+      copy_bytes_slice(a.out, a.sym[c.rank], a.nbytes, v0, v1, false);
+    });
   end_epoch(c, ch, e + 2);
 }
 
@@ -334,8 +370,7 @@ __global__ void __launch_bounds__(kCollThreads)
         }
       }
     }
-    fence_acq_rel_sys();
-    ok = rank_barrier_block(c, ch, e + 2, PH_BARRIER_END);
+    ok = rank_barrier_block(c, ch, e + 2, PH_BARRIER_END);  // its release orders the stores
   }
   end_epoch(c, ch, e + 2);
 }
@@ -351,9 +386,10 @@ __global__ void __launch_bounds__(kCollThreads)
   const uint32_t e = begin_epoch(c, ch);
   const unsigned long long nvec = a.nbytes / 16ull;  // host guarantees chunk % 16 == 0
   const unsigned long long per_rank = nvec / W;
-  unsigned long long v0, v1;
-  slice_of(nvec, gridDim.x, blockIdx.x, &v0, &v1);
-  if (a.copy_in) copy_vec_slice(a.sym[c.rank], a.in, v0, v1);
+  if (a.copy_in)
+    for_each_chunk_slice(nvec, per_rank, W, [&](unsigned long long v0, unsigned long long v1) {
+      copy_vec_slice(a.sym[c.rank], a.in, v0, v1);
+    });
   bool ok = rank_barrier_block(c, ch, e + 1, PH_BARRIER_START);
   if (ok) {
     const unsigned long long c0 = per_rank * c.rank;
@@ -411,9 +447,10 @@ __global__ void __launch_bounds__(kCollThreads)
   const uint32_t e = begin_epoch(c, ch);
   const unsigned long long nvec = a.nbytes / 16ull;
   const unsigned long long per_rank = nvec / W;
-  unsigned long long v0, v1;
-  slice_of(nvec, gridDim.x, blockIdx.x, &v0, &v1);
-  if (a.copy_in) copy_vec_slice(a.sym[c.rank], a.in, v0, v1);
+  if (a.copy_in)
+    for_each_chunk_slice(nvec, per_rank, W, [&](unsigned long long v0, unsigned long long v1) {
+      copy_vec_slice(a.sym[c.rank], a.in, v0, v1);
+    });
   bool ok = rank_barrier_block(c, ch, e + 1, PH_BARRIER_START);
   if (ok) {
     unsigned long long s0, s1;
@@ -456,13 +493,35 @@ __global__ void __launch_bounds__(kCollThreads)
   const unsigned long long nvec = a.nbytes / 16ull;  // full per-rank input
   unsigned long long v0, v1;
   slice_of(nvec, gridDim.x, blockIdx.x, &v0, &v1);
-  if (a.copy_in) copy_vec_slice(a.sym[c.rank], a.in, v0, v1);
+  const unsigned long long B = a.a2a_b, Sl = a.a2a_s_local, H = a.a2a_h;
+  const unsigned long long Hl = H / W;
+  const unsigned long long dv = nvec / (B * Sl * H);  // vectors per D-row
+  const unsigned long long run = Hl * dv;              // contiguous vectors per (b, s) and peer
+  // Source offset of item (b, s, j) as read by rank `reader`.
+  auto src_offset = [&](unsigned long long b, unsigned long long s, unsigned long long j,
+                        int reader) -> unsigned long long {
+    return a.a2a_to_heads
+               ? ((b * Sl + s) * H + static_cast<unsigned long long>(reader) * Hl) * dv + j
+               : ((b * (Sl * W) + static_cast<unsigned long long>(reader) * Sl + s) * Hl) * dv + j;
+  };
+  if (a.copy_in) {
+    // Stage exactly the vectors that block b of each peer will read from this rank: item
+    // idx = (p, b, s, j) is read from here by rank (rank - p) mod W.
+    const uint4* in = static_cast<const uint4*>(a.in);
+    uint4* mine = static_cast<uint4*>(a.sym[c.rank]);
+    for (unsigned long long idx = v0 + threadIdx.x; idx < v1; idx += blockDim.x) {
+      const unsigned long long j = idx % run;
+      unsigned long long t = idx / run;
+      const unsigned long long s = t % Sl;
+      t /= Sl;
+      const unsigned long long b = t % B;
+      const int p = static_cast<int>(t / B);
+      const unsigned long long off = src_offset(b, s, j, (c.rank - p + W) % W);
+      mine[off] = in[off];
+    }
+  }
   bool ok = rank_barrier_block(c, ch, e + 1, PH_BARRIER_START);
   if (ok) {
-    const unsigned long long B = a.a2a_b, Sl = a.a2a_s_local, H = a.a2a_h;
-    const unsigned long long Hl = H / W;
-    const unsigned long long dv = nvec / (B * Sl * H);  // vectors per D-row
-    const unsigned long long run = Hl * dv;              // contiguous vectors per (b, s) and peer
     // Output enumerated as (p, b, s, j) with j in [0, run): nvec items in total.
     uint4* out = static_cast<uint4*>(a.out);
     for (unsigned long long idx = v0 + threadIdx.x; idx < v1; idx += blockDim.x) {
@@ -473,15 +532,11 @@ __global__ void __launch_bounds__(kCollThreads)
       const unsigned long long b = t % B;
       const int p = static_cast<int>(t / B);
       const int src = (c.rank + p) % W;
-      unsigned long long src_off, dst_off;
-      if (a.a2a_to_heads) {
-        src_off = ((b * Sl + s) * H + static_cast<unsigned long long>(c.rank) * Hl) * dv + j;
-        dst_off = ((b * (Sl * W) + src * Sl + s) * Hl) * dv + j;
-      } else {
-        // in_p is [B, S, Hl, D] with S = Sl*W ; out is [B, Sl, H, D]
-        src_off = ((b * (Sl * W) + static_cast<unsigned long long>(c.rank) * Sl + s) * Hl) * dv + j;
-        dst_off = ((b * Sl + s) * H + static_cast<unsigned long long>(src) * Hl) * dv + j;
-      }
+      const unsigned long long src_off = src_offset(b, s, j, c.rank);
+      // to_heads: out is [B, S, Hl, D]; otherwise in_p is [B, S, Hl, D] and out [B, Sl, H, D].
+      const unsigned long long dst_off =
+          a.a2a_to_heads ? ((b * (Sl * W) + src * Sl + s) * Hl) * dv + j
+                         : ((b * Sl + s) * H + static_cast<unsigned long long>(src) * Hl) * dv + j;
       out[dst_off] = ld_sys_v4(static_cast<const uint4*>(a.sym[src]) + src_off);
     }
     ok = rank_barrier_block(c, ch, e + 2, PH_BARRIER_END);
@@ -521,7 +576,6 @@ __global__ void __launch_bounds__(kCollThreads)
         }
         mm_st_v4(mc + i, v);
       }
-      fence_acq_rel_sys();
     }
     if (ok) ok = rank_barrier_block(c, ch, e + 2, PH_BARRIER_END);
     if (ok && a.copy_out) copy_bytes_slice(a.out, a.sym[c.rank], a.nbytes, v0, v1, false);

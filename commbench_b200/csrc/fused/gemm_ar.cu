@@ -7,8 +7,8 @@
 //    and bumps an arrival counter there; the owner adds the W partials in fp32
 //    and writes the reduced tile into EVERY rank's symmetric result buffer (one
 //    multimem.st per vector when a multicast object is bound, W plain stores
-//    otherwise), then bumps each rank's "tiles done" counter; every rank leaves
-//    when all tiles are done (and copies the result out if asked to).
+//    otherwise), then bumps each rank's "tiles done" counter; the kernel ends
+//    when all tiles are done, and the result stays in the symmetric buffer.
 //  * one-shot (decode-sized M): every rank sends its partial tile to ALL ranks
 //    and each rank reduces every tile locally - one NVLink hop instead of two.
 //
@@ -45,7 +45,20 @@ struct GemmArParams {
   FusedSeq seq;
   uint32_t* status;
   unsigned long long timeout_ns;
+  unsigned long long* trace;  // optional [ctas][8] %globaltimer stamps per CTA (nullptr: off)
+  int poll_ns;                // sleep between polls of a flag
 };
+
+// Optional tracing: thread 0 of each CTA stamps %globaltimer at the kernel's phase changes.
+__device__ __forceinline__ void ar_stamp(const GemmArParams& p, int cta, int slot) {
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[cta * 8 + slot] = globaltimer_ns();
+}
+
+__device__ __forceinline__ bool ar_wait(const GemmArParams& p, const uint32_t* flag, uint32_t target,
+                                        uint32_t phase, uint32_t detail) {
+  return wait_flag_ge_sys_paced(flag, target, p.timeout_ns, p.status, phase, detail,
+                                static_cast<uint32_t>(p.poll_ns));
+}
 
 // done counters sit after the arrival counters of both parities
 __device__ __host__ constexpr int ar_done_index(int parity) { return 2 * kArMaxTiles + parity; }
@@ -112,8 +125,9 @@ struct ArPolicy {
 };
 
 template <class Cfg>
-__device__ __forceinline__ void ar_reduce_phase(const GemmArParams& p, uint32_t parity, int cta,
+__device__ __forceinline__ void ar_reduce_phase(const GemmArParams& p, uint32_t call, int cta,
                                                 int num_ctas) {
+  const uint32_t parity = call & 1u;
   const int ntiles = p.g.num_m_blocks * p.g.num_n_blocks;
   constexpr int VPR = Cfg::BN / 8;
   constexpr int TILE_VECS = Cfg::BM * VPR;
@@ -129,9 +143,9 @@ __device__ __forceinline__ void ar_reduce_phase(const GemmArParams& p, uint32_t 
     uint32_t* flag = p.flags_local + parity * kArMaxTiles + slot;
     bool ok = true;
     if (threadIdx.x == 0)
-      ok = wait_flag_ge_sys(flag, static_cast<uint32_t>(p.world), p.timeout_ns, p.status,
-                            PH_AR_TILE, t);
+      ok = ar_wait(p, flag, static_cast<uint32_t>(p.world), PH_AR_TILE, t);
     if (__syncthreads_and(ok ? 1 : 0) == 0) return;
+    if (i == cta) ar_stamp(p, cta, 5);
     auto src = [&](int s, int v) -> const uint4* {
       return stage + (static_cast<unsigned long long>(s) * p.slots + slot) * TILE_VECS + v;
     };
@@ -161,10 +175,12 @@ __device__ __forceinline__ void ar_reduce_phase(const GemmArParams& p, uint32_t 
       default: reduce_tile_copies<8, TILE_VECS>(src, dst, valid); break;
     }
     __syncthreads();
+    if (i == cta) ar_stamp(p, cta, 6);
     if (threadIdx.x == 0) {
       *flag = 0u;
       if (!p.oneshot) {
         fence_acq_rel_sys();  // release for the whole CTA's stores (ordered by the barrier)
+        if (i == cta) ar_stamp(p, cta, 7);
         for (int d = 0; d < p.world; ++d) {
           const int dest = (p.rank + d) % p.world;
           red_relaxed_sys_add(p.flags_peer[dest] + ar_done_index(parity), 1u);
@@ -172,22 +188,19 @@ __device__ __forceinline__ void ar_reduce_phase(const GemmArParams& p, uint32_t 
       }
     }
   }
+  ar_stamp(p, cta, 2);
   if (p.oneshot) return;
-  // Wait for every tile's owner, then (optionally) copy the symmetric result out.
+  // Two-shot: the kernel must not end before every owner has delivered its reduced tiles
+  // into this rank's result buffer.  ONE thread of the grid waits for that (CTA 0, polling
+  // at a modest rate); the other CTAs leave, and the end of the kernel is what publishes
+  // the result to the stream.  Letting every CTA poll - the remote counter or a local copy
+  // of it - slowed the peers' traffic into this GPU by hundreds of microseconds.
+  if (cta != 0) return;
   uint32_t* done = p.flags_local + ar_done_index(parity);
   bool ok = true;
-  if (threadIdx.x == 0)
-    ok = wait_flag_ge_sys(done, static_cast<uint32_t>(ntiles), p.timeout_ns, p.status, PH_AR_DONE,
-                          0);
+  if (threadIdx.x == 0) ok = ar_wait(p, done, static_cast<uint32_t>(ntiles), PH_AR_DONE, 0);
   if (__syncthreads_and(ok ? 1 : 0) == 0) return;
-  if (p.out != nullptr) {
-    const uint4* src = reinterpret_cast<const uint4*>(p.result_peer[parity][p.rank]);
-    uint4* dst = static_cast<uint4*>(p.out);
-    const unsigned long long total = static_cast<unsigned long long>(p.g.M) * row_vecs;
-    for (unsigned long long v = static_cast<unsigned long long>(cta) * blockDim.x + threadIdx.x;
-         v < total; v += static_cast<unsigned long long>(num_ctas) * blockDim.x)
-      dst[v] = ld_sys_v4(src + v);
-  }
+  ar_stamp(p, cta, 3);
 }
 
 template <class Cfg>
@@ -198,11 +211,15 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1)
   const int vrank = emu != nullptr ? blockIdx.x / ctas_per_rank : 0;
   const GemmArParams& p = emu != nullptr ? emu[vrank] : p0;
   const int cta = blockIdx.x - vrank * ctas_per_rank;
-  const uint32_t parity = fused_begin(p.seq);
+  const uint32_t call = ld_volatile(p.seq.seq);  // every thread reads it before anyone bumps it
+  const uint32_t parity = call & 1u;
+  ar_stamp(p, cta, 0);
   ArRt rt{&p, parity};
   gemm_cta_main<Cfg, ArPolicy<Cfg>>(rt, p.g, p.status, cta, ctas_per_rank, smem_raw);
   __syncthreads();
-  ar_reduce_phase<Cfg>(p, parity, cta, ctas_per_rank);
+  ar_stamp(p, cta, 1);
+  ar_reduce_phase<Cfg>(p, call, cta, ctas_per_rank);
+  ar_stamp(p, cta, 4);
   // Last CTA out clears this parity's done counter (every CTA has seen it complete).
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -261,7 +278,7 @@ struct CbGemmArDesc {
   int ctas_per_rank;
   const void* a;  // [M, K]
   const void* b;  // [N, K]
-  void* out;      // [M, N] bf16 local, or nullptr to leave the result in result_peer[parity][rank]
+  void* out;      // one-shot: [M, N] bf16 local.  two-shot: nullptr (result_peer[parity][rank])
   void* stage_peer[2][CB_MAX_RANKS];   // [W][slots][128][bn] bf16
   void* result_peer[2][CB_MAX_RANKS];  // [M][N] bf16 (two-shot only)
   void* result_mc[2];
@@ -269,6 +286,8 @@ struct CbGemmArDesc {
   void* seq;
   void* status;
   unsigned long long timeout_ns;
+  void* trace;  // optional uint64 [ctas_per_rank][8]: per-CTA phase time stamps, or nullptr
+  int poll_ns;  // sleep between flag polls in nanoseconds
 };
 
 static int build_ar_params(const CbGemmArDesc& d, GemmArParams* p) {
@@ -289,6 +308,10 @@ static int build_ar_params(const CbGemmArDesc& d, GemmArParams* p) {
   }
   if (d.oneshot && d.out == nullptr) {
     set_last_error("gemm_ar: the one-shot variant needs a local output");
+    return -1;
+  }
+  if (!d.oneshot && d.out != nullptr) {
+    set_last_error("gemm_ar: the two-shot variant leaves its result in result_peer[parity][rank]");
     return -1;
   }
   if (make_tmap_2d(&p->tm_a, d.a, dt, d.K, d.M, (unsigned long long)d.K * esz, BK, 128, true))
@@ -322,6 +345,8 @@ static int build_ar_params(const CbGemmArDesc& d, GemmArParams* p) {
   p->seq.done_ctas = static_cast<uint32_t*>(d.seq) + 1;
   p->status = static_cast<uint32_t*>(d.status);
   p->timeout_ns = d.timeout_ns;
+  p->trace = static_cast<unsigned long long*>(d.trace);
+  p->poll_ns = d.poll_ns;
   return 0;
 }
 

@@ -166,6 +166,17 @@ __device__ __forceinline__ void report_status(uint32_t* status, uint32_t code, u
 // Bounded wait until *flag >= target (wrap-safe).  Returns false on time-out,
 // after recording the status word.  `timeout_ns` is a %globaltimer budget; the
 // iteration cap is a second guard in case the timer misbehaves.
+//
+// Keep the number of threads that poll one remotely-updated word small (a handful): with
+// every CTA of a grid polling the same word, the peers' atomics to it - and everything
+// queued behind them on the link - were held up for hundreds of microseconds.  Where a
+// whole grid must wait for one remote event, one CTA polls it and republishes it in a
+// local word for the others (see the fused GEMM + all-reduce kernel).
+__device__ __forceinline__ uint32_t ld_relaxed_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ bool wait_flag_ge_sys(const uint32_t* flag, uint32_t target,
                                                  uint64_t timeout_ns, uint32_t* status,
                                                  uint32_t phase, uint32_t detail) {
@@ -183,18 +194,46 @@ __device__ __forceinline__ bool wait_flag_ge_sys(const uint32_t* flag, uint32_t 
   return false;
 }
 
+// Paced variant for waits that many CTAs of a grid sit in at the same time (one per tile,
+// per expert, ...): acquire polls `poll_ns` apart (an acquire load per poll measured cheaper
+// than relaxed polls plus a system fence at the end).  Measured on B200: ~100 SMs polling back to back delayed the peers' stores and
+// atomics into this GPU by 100-400 us; a few hundred nanoseconds between polls removed it.
+__device__ __forceinline__ bool wait_flag_ge_sys_paced(const uint32_t* flag, uint32_t target,
+                                                       uint64_t timeout_ns, uint32_t* status,
+                                                       uint32_t phase, uint32_t detail,
+                                                       uint32_t poll_ns) {
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t it = 0; it < 0x7fffffffu; ++it) {
+    if (static_cast<int32_t>(ld_acquire_sys(flag) - target) >= 0) return true;
+    if ((it & 15u) == 15u) {
+      if (globaltimer_ns() - t0 > timeout_ns) break;
+      if (status != nullptr && ld_volatile(status) != 0u) break;
+    }
+    if (poll_ns > 0u) __nanosleep(poll_ns);
+  }
+  report_status(status, CB_TIMEOUT_PEER_FLAG, phase, detail);
+  return false;
+}
+constexpr uint32_t kPacedPollNs = 300u;
+
 __device__ __forceinline__ bool wait_flag_ge_gpu(const uint32_t* flag, uint32_t target,
                                                  uint64_t timeout_ns, uint32_t* status,
                                                  uint32_t phase, uint32_t detail) {
-  if (static_cast<int32_t>(ld_acquire_gpu(flag) - target) >= 0) return true;
+  if (static_cast<int32_t>(ld_relaxed_gpu(flag) - target) >= 0) {
+    fence_acq_rel_gpu();
+    return true;
+  }
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t it = 0; it < 0x7fffffffu; ++it) {
-    if (static_cast<int32_t>(ld_acquire_gpu(flag) - target) >= 0) return true;
+    if (static_cast<int32_t>(ld_relaxed_gpu(flag) - target) >= 0) {
+      fence_acq_rel_gpu();
+      return true;
+    }
     if ((it & 63u) == 63u) {
       if (globaltimer_ns() - t0 > timeout_ns) break;
       if (status != nullptr && ld_volatile(status) != 0u) break;
     }
-    if (it > 256u) __nanosleep(32);
+    if (it > 32u) __nanosleep(32);
   }
   report_status(status, CB_TIMEOUT_LOCAL_FLAG, phase, detail);
   return false;

@@ -104,6 +104,7 @@ def main(argv=None) -> int:
         algos = ["oneshot", "twoshot"] + (["nvls"] if ctx.has_multicast else [])
         if world == 1:
             algos = ["oneshot"]
+        sym_full, _ = ctx.empty((sizes[-1] // 2,), torch.bfloat16)
         for nbytes in sizes:
             n = nbytes // 2
             g = torch.Generator(device=dev).manual_seed(rank)
@@ -111,7 +112,7 @@ def main(argv=None) -> int:
             ref = None
             if nbytes <= (64 << 20):
                 ref = sum(t.float() for t in gather(x))
-            sym, _ = ctx.empty((n,), torch.bfloat16)
+            sym = sym_full[:n]
             base_ms = timed(lambda: base.all_reduce(x.clone())) if world > 1 else None
             clone_ms = timed(lambda: x.clone()) if world > 1 else 0.0
             if base_ms is not None:
@@ -124,10 +125,10 @@ def main(argv=None) -> int:
                 if algo == "oneshot":
                     out = torch.empty_like(x)
                     y = coll.all_reduce(ctx, sym, out=out, algo=algo)
-                    fn = lambda: coll.all_reduce(ctx, sym, out=out, algo="oneshot", max_blocks=148)
+                    fn = lambda: coll.all_reduce(ctx, sym, out=out, algo="oneshot")
                 else:
                     y = coll.all_reduce(ctx, sym, algo=algo)
-                    fn = lambda a=algo: coll.all_reduce(ctx, sym, algo=a, max_blocks=148)
+                    fn = lambda a=algo: coll.all_reduce(ctx, sym, algo=a)
                 ctx.check_status()
                 correct, err = True, None
                 if ref is not None:

@@ -42,9 +42,10 @@ def _check_local(t: torch.Tensor, name: str):
         raise CommError(f"{name} must be 16-byte aligned")
 
 
-def pick_blocks(nbytes: int, max_blocks: int) -> int:
-    """One CTA per 64 KiB of message, at least 1, at most `max_blocks`."""
-    return max(1, min(max_blocks, (nbytes + (1 << 16) - 1) >> 16))
+def pick_blocks(nbytes: int, max_blocks: int, grain: int = 1 << 16) -> int:
+    """One CTA per ``grain`` bytes of message (64 KiB by default), at least 1, at most
+    ``max_blocks``."""
+    return max(1, min(max_blocks, (nbytes + grain - 1) // grain))
 
 
 def choose_all_reduce_algo(nbytes: int, world: int, has_multicast: bool) -> str:
@@ -94,9 +95,10 @@ def _pad16(n: int) -> int:
 
 # =============================================================== real contexts
 def all_reduce(ctx: CommContext, x: torch.Tensor, out: torch.Tensor | None = None,
-               algo: str = "auto", max_blocks: int | None = None, stream=None) -> torch.Tensor:
+               algo: str = "auto", max_blocks: int | None = None, stream=None,
+               blocks: int | None = None) -> torch.Tensor:
     """Sum over ranks.  In place when ``out`` is None.  ``algo`` in
-    {"auto", "oneshot", "twoshot", "nvls"}."""
+    {"auto", "oneshot", "twoshot", "nvls"}.  ``blocks`` forces the grid size (tuning)."""
     _check_local(x, "x")
     out = x if out is None else out
     _check_local(out, "out")
@@ -108,7 +110,11 @@ def all_reduce(ctx: CommContext, x: torch.Tensor, out: torch.Tensor | None = Non
         algo = choose_all_reduce_algo(nbytes, ctx.world, ctx.has_multicast)
     if algo == "nvls" and not ctx.has_multicast:
         raise CommError("algo='nvls' needs a bound multicast object (not available here)")
-    blocks = pick_blocks(nbytes, max_blocks or cfg.coll_max_blocks)
+    if blocks is None:
+        # One-shot is latency bound: every CTA reads its slice from all W ranks, so slices are
+        # kept small; the chunked algorithms move nbytes / W per rank.
+        grain = cfg.ar_oneshot_grain_bytes if algo == "oneshot" else cfg.ar_chunk_grain_bytes
+        blocks = pick_blocks(nbytes, max_blocks or cfg.coll_max_blocks, grain)
     dt = _dtype_code(x)
     sym = ctx.find_block(x) if nbytes % 16 == 0 else None
     if algo == "oneshot":

@@ -59,8 +59,14 @@ class _ArDesc(C.Structure):
         ("a", C.c_void_p), ("b", C.c_void_p), ("out", C.c_void_p),
         ("stage_peer", _P8 * 2), ("result_peer", _P8 * 2), ("result_mc", C.c_void_p * 2),
         ("flags_peer", _P8), ("seq", C.c_void_p), ("status", C.c_void_p),
-        ("timeout_ns", C.c_ulonglong),
+        ("timeout_ns", C.c_ulonglong), ("trace", C.c_void_p),
+        ("poll_ns", C.c_int),
     ]
+
+
+import contextlib
+
+_nullctx = contextlib.nullcontext
 
 
 def _esz(dtype) -> int:
@@ -261,6 +267,8 @@ class GemmAr(_FusedBase):
         self.stage = [_Sym(ctx, self.stage_bytes), _Sym(ctx, self.stage_bytes)]
         self.result = [_Sym(ctx, max_m * max_n * 2), _Sym(ctx, max_m * max_n * 2)]
         self.flags = _Sym(ctx, self.lib.cb_gemm_ar_flag_words() * 4, zero=True)
+        self.trace = None
+        self.poll_ns = get_config().fused_poll_ns
         self._sync_init()
 
     def _desc(self, r, a, b, out, M, Nn, K, alpha, bn, fp8, oneshot) -> _ArDesc:
@@ -279,7 +287,16 @@ class GemmAr(_FusedBase):
         d.seq = self.seq[r if self.emu else 0].data_ptr()
         d.status = self._status_ptr(r)
         d.timeout_ns = self.ctx.timeout_ns
+        d.trace = self.trace.data_ptr() if self.trace is not None else 0
+        d.poll_ns = self.poll_ns
         return d
+
+    def enable_trace(self) -> torch.Tensor:
+        """Per-CTA phase time stamps (``%globaltimer`` ns) of the next calls: [ctas, 8] with
+        columns start, GEMM phase done, own reductions done, all tiles done, exit."""
+        dev = self.ctx.device
+        self.trace = torch.zeros(_sm_count(dev), 8, dtype=torch.int64, device=dev)
+        return self.trace
 
     @staticmethod
     def pick_bn(M: int, Nn: int, sms: int) -> int:
@@ -302,23 +319,45 @@ class GemmAr(_FusedBase):
             oneshot = M <= cfg.gemm_ar_oneshot_max_m
         if bn is None:
             bn = self.pick_bn(M, Nn, self._ctas())
+        par = self.calls & 1            # the kernel derives the same parity from its call counter
+
+        def sym_view(r):
+            t = self.result[par].tensors[r if self.emu else 0]
+            return t[: M * Nn * 2].view(torch.bfloat16).view(M, Nn)
+
         if self.emu:
-            outs = out or [torch.empty((M, Nn), dtype=torch.bfloat16, device=a0.device)
-                           for _ in range(self.world)]
+            outs = out
+            if oneshot and outs is None:
+                outs = [torch.empty((M, Nn), dtype=torch.bfloat16, device=a0.device)
+                        for _ in range(self.world)]
             descs = (_ArDesc * self.world)(*[
-                self._desc(r, a[r], b[r], outs[r], M, Nn, K, alpha, bn, fp8, oneshot)
+                self._desc(r, a[r], b[r], outs[r] if oneshot else None, M, Nn, K, alpha, bn, fp8,
+                           oneshot)
                 for r in range(self.world)])
             table = self._emu_table(self.lib.cb_sizeof_gemm_ar_params() * self.world)
             rc = self.lib.cb_gemm_ar(descs, self.world, table, N.stream_ptr(stream))
-            result = outs
         else:
-            if out is None:
+            if oneshot and out is None:
                 out = torch.empty((M, Nn), dtype=torch.bfloat16, device=a0.device)
-            descs = (_ArDesc * 1)(self._desc(self.ctx.rank, a, b, out, M, Nn, K, alpha, bn, fp8,
-                                             oneshot))
+            descs = (_ArDesc * 1)(self._desc(self.ctx.rank, a, b, out if oneshot else None, M, Nn,
+                                             K, alpha, bn, fp8, oneshot))
             rc = self.lib.cb_gemm_ar(descs, 1, None, N.stream_ptr(stream))
-            result = out
         if rc != 0:
             raise CommError(f"gemm_ar failed: {N.last_error()}")
         self.calls += 1
-        return result
+        if oneshot:
+            return outs if self.emu else out
+        # Two-shot: the reduced tensor sits in this call's symmetric result buffer.  Without
+        # `out` a view of it is returned; it stays valid until the call after the next one.
+        if self.emu:
+            views = [sym_view(r) for r in range(self.world)]
+            if out is None:
+                return views
+            for o, v in zip(out, views):
+                o.copy_(v)
+            return out
+        if out is None:
+            return sym_view(0)
+        with torch.cuda.stream(stream) if stream is not None else _nullctx():
+            out.copy_(sym_view(0))
+        return out

@@ -1,0 +1,88 @@
+"""One small, self-contained launch sequence per hot kernel, for profiler captures.
+
+    python -m commbench_b200.harness.profile_case gemm   [--m 8192 --n 8192 --k 4096]
+    python -m commbench_b200.harness.profile_case gemm_fp8
+    python -m commbench_b200.harness.profile_case attn   [--seq 8192 --heads 16]
+    python -m commbench_b200.harness.profile_case quant
+
+Each case allocates inputs larger than the 126 MB L2 but well under a few GB, runs two warm-up
+launches and ``--launches`` measured ones (default 3), prints the CUDA-event time and exits.
+Single GPU, single process, no kernel that waits on another rank: safe to run under a
+multi-pass profiler (``ncu --set full --clock-control none -k regex:<kernel> -c 3 ...``) once
+the plain run has exited 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+
+
+def _time(fn, launches: int) -> float:
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(launches):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / launches
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["gemm", "gemm_fp8", "attn", "quant"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--seq", type=int, default=8192)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--launches", type=int, default=3)
+    a = ap.parse_args(argv)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(0)
+    out: dict = {"case": a.case}
+
+    if a.case in ("gemm", "gemm_fp8"):
+        from ..ops.gemm import gemm
+
+        A = torch.randn(a.m, a.k, device=dev, generator=g)
+        B = torch.randn(a.n, a.k, device=dev, generator=g) * 0.05
+        if a.case == "gemm_fp8":
+            A, B = A.to(torch.float8_e4m3fn), B.to(torch.float8_e4m3fn)
+        else:
+            A, B = A.bfloat16(), B.bfloat16()
+        C = torch.empty(a.m, a.n, dtype=torch.bfloat16, device=dev)
+        ms = _time(lambda: gemm(A, B, out=C), a.launches)
+        out.update(shape=[a.m, a.n, a.k], ms=ms, tflops=2.0 * a.m * a.n * a.k / ms / 1e9)
+    elif a.case == "attn":
+        from ..ops.cp import flash_attention
+
+        q = torch.randn(1, a.seq, a.heads, 128, device=dev, generator=g).bfloat16()
+        k = torch.randn(1, a.seq, a.heads // 4, 128, device=dev, generator=g).bfloat16()
+        v = torch.randn(1, a.seq, a.heads // 4, 128, device=dev, generator=g).bfloat16()
+        ms = _time(lambda: flash_attention(q, k, v, causal=True), a.launches)
+        out.update(shape=[1, a.seq, a.heads, a.heads // 4, 128], ms=ms,
+                   tflops=4.0 * a.seq * a.seq * 128 * a.heads / 2 / ms / 1e9)
+    elif a.case == "quant":
+        from ..ops.gemm import dequantize_blockscaled, quantize_blockscaled
+
+        x = torch.randn(32768, 7168, device=dev, generator=g).bfloat16()
+        qx, s = quantize_blockscaled(x, 1)
+        y = torch.empty_like(x)
+        ms_q = _time(lambda: quantize_blockscaled(x, 1), a.launches)
+        ms_d = _time(lambda: dequantize_blockscaled(qx, s, 1, out=y), a.launches)
+        nbytes = x.numel() * 3
+        out.update(rows=32768, cols=7168, quant_ms=ms_q, dequant_ms=ms_d,
+                   quant_gbs=nbytes / ms_q / 1e6, dequant_gbs=nbytes / ms_d / 1e6)
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -27,6 +27,8 @@ class Config:
     gemm_rs_reduce_ctas: int = 0                # 0: reduction runs on all CTAs after their tiles
     gemm_ar_oneshot_max_m: int = 256            # rows at or below: one-shot AR epilogue
     fused_poll_ns: int = 300                    # pause between polls of a peer-written flag
+    # --- attention -------------------------------------------------------
+    attn_impl: int = 2                          # flash-attention kernel: 2 (two tiles per CTA) or 1
     # --- MoE ---------------------------------------------------------------
     moe_expert_alignment: int = 128             # rows per expert padded to a tile multiple
     # --- runtime -----------------------------------------------------------

@@ -424,6 +424,11 @@ static int make_tmap_bshd(CUtensorMap* out, const void* base, int rows, int head
   return 0;
 }
 
+// Shared with the second forward kernel (fa_fwd2.cu).
+int cb_attn_make_tmap_bshd(CUtensorMap* out, const void* base, int rows, int heads) {
+  return make_tmap_bshd(out, base, rows, heads);
+}
+
 extern "C" {
 
 // q [B, Sq, Hq, 128], k/v [B, Skv, Hkv, 128], o [B, Sq, Hq, 128] bf16 contiguous;

@@ -18,6 +18,8 @@ import math
 
 import torch
 
+from ..config import get_config
+
 from .. import _native as N
 from ..runtime.context import CommContext, CommError, tensor_from_ptr
 from . import collectives as coll
@@ -25,8 +27,12 @@ from . import collectives as coll
 
 def flash_attention(q, k, v, causal: bool = True, q_offset: int = 0, kv_offset: int = 0,
                     scale: float | None = None, out=None, lse=None, status_ptr: int = 0,
-                    stream=None):
+                    stream=None, impl: int | None = None):
     """One key/value chunk: returns (o [B,Sq,Hq,D] bf16 normalised, lse [B,Hq,Sq] fp32).
+
+    ``impl`` selects the kernel: 2 = two query tiles and two softmax warp-groups per CTA with O
+    in tensor memory (default, ``CB200_ATTN_IMPL``), 1 = the first design (one tile, O in
+    registers).
 
     ``q_offset`` / ``kv_offset`` are the global sequence positions of the first query / key;
     with ``causal`` key j is visible to query i iff kv_offset + j <= q_offset + i."""
@@ -44,9 +50,12 @@ def flash_attention(q, k, v, causal: bool = True, q_offset: int = 0, kv_offset: 
     if lse is None:
         lse = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
     sc = scale if scale is not None else 1.0 / math.sqrt(D)
-    rc = lib.cb_attn_fwd(N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(out), N.ptr(lse), B, Sq, Skv, Hq, Hkv,
-                         q_offset, kv_offset, int(causal), C.c_float(sc), C.c_void_p(status_ptr),
-                         N.stream_ptr(stream))
+    if impl is None:
+        impl = get_config().attn_impl
+    fn = lib.cb_attn_fwd2 if impl == 2 else lib.cb_attn_fwd
+    rc = fn(N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(out), N.ptr(lse), B, Sq, Skv, Hq, Hkv,
+            q_offset, kv_offset, int(causal), C.c_float(sc), C.c_void_p(status_ptr),
+            N.stream_ptr(stream))
     if rc != 0:
         raise CommError(f"attention launch failed: {N.last_error()}")
     return out, lse

@@ -14,15 +14,17 @@ def _qkv(B, Sq, Skv, Hq, Hkv, seed):
     return q, k, v
 
 
+@pytest.mark.parametrize("impl", [1, 2])
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("shape", [(1, 128, 128, 1, 1), (1, 256, 256, 4, 1), (2, 384, 384, 4, 2),
-                                   (1, 200, 200, 2, 2), (1, 1024, 1024, 8, 2)])
-def test_flash_attention_matches_reference(native_lib, shape, causal):
+                                   (1, 200, 200, 2, 2), (1, 1024, 1024, 8, 2),
+                                   (1, 2048, 2048, 4, 1)])
+def test_flash_attention_matches_reference(native_lib, shape, causal, impl):
     from commbench_b200.ops.cp import flash_attention, reference_attention
 
     B, Sq, Skv, Hq, Hkv = shape
     q, k, v = _qkv(B, Sq, Skv, Hq, Hkv, 11 + Sq)
-    o, lse = flash_attention(q, k, v, causal=causal)
+    o, lse = flash_attention(q, k, v, causal=causal, impl=impl)
     torch.cuda.synchronize()
     ro, rl = reference_attention(q, k, v, causal=causal)
     assert torch.allclose(o.float(), ro, atol=2e-2, rtol=2e-2), (o.float() - ro).abs().max()

@@ -81,6 +81,29 @@ __device__ __forceinline__ float f2_ex2(float x) {
   return y;
 }
 
+// Blackwell packed fp32 pairs and three-input max.
+__device__ __forceinline__ uint64_t f2_pack_u(uint32_t lo, uint32_t hi) {
+  return static_cast<uint64_t>(lo) | (static_cast<uint64_t>(hi) << 32);
+}
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  return f2_pack_u(__float_as_uint(lo), __float_as_uint(hi));
+}
+__device__ __forceinline__ uint64_t f2_fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float f2_max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // Key blocks that the 128-row tile `tile128` can see.
 __device__ __forceinline__ int f2_num_blocks(const Fa2Params& p, int tile128) {
   if (tile128 * F2_BM >= p.Sq) return 0;
@@ -277,14 +300,16 @@ __global__ void __launch_bounds__(F2_THREADS, 1)
         for (int i = 0; i < 128; ++i)
           if (!(i < kv_left && (!p.causal || key0 + i <= q_pos))) s[i] = 0xff800000u;  // -inf
       }
+      // Row maximum: three-input max, eight independent chains.
       float mx8[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) mx8[i] = __uint_as_float(s[i]);
+      for (int i = 0; i < 8; ++i) mx8[i] = fmaxf(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
 #pragma unroll
-      for (int i = 8; i < 128; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(s[i]));
-      const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])),
-                             fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-      const float mx_s = mx * p.scale_log2;  // scale > 0; -inf stays -inf
+      for (int i = 16; i < 128; i += 2)
+        mx8[(i >> 1) & 7] = f2_max3(mx8[(i >> 1) & 7], __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+      const float mx = fmaxf(f2_max3(mx8[0], mx8[1], mx8[2]), f2_max3(mx8[3], mx8[4], mx8[5]));
+      const float mx_all = f2_max3(mx, mx8[6], mx8[7]);
+      const float mx_s = mx_all * p.scale_log2;  // scale > 0; -inf stays -inf
       const bool grow = mx_s > m_ref + F2_RESCALE_THRESHOLD || (m_ref == -INFINITY && mx_s > -INFINITY);
       const bool any_grow = __any_sync(0xffffffffu, grow);
       float alpha = 1.f;
@@ -296,19 +321,24 @@ __global__ void __launch_bounds__(F2_THREADS, 1)
       }
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
       const float neg_m = -m_use;
-      float sum8[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) sum8[i] = 0.f;
+      // p = 2^(s * scale - m): the multiply-add and the row sum run as packed two-wide fp32
+      // operations (one instruction per pair of keys), the exponential on the SFU.
+      const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2), negm2 = f2_pack(neg_m, neg_m);
+      uint64_t sum4[4] = {0ull, 0ull, 0ull, 0ull};
       uint32_t packed[64];
 #pragma unroll
       for (int i = 0; i < 128; i += 2) {
-        const float p0 = f2_ex2(fmaf(__uint_as_float(s[i]), p.scale_log2, neg_m));
-        const float p1 = f2_ex2(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, neg_m));
-        sum8[(i >> 1) & 7] += p0 + p1;
+        const uint64_t y = f2_fma2(f2_pack_u(s[i], s[i + 1]), scale2, negm2);
+        const float p0 = f2_ex2(__uint_as_float(static_cast<uint32_t>(y)));
+        const float p1 = f2_ex2(__uint_as_float(static_cast<uint32_t>(y >> 32)));
+        sum4[(i >> 1) & 3] = f2_add2(sum4[(i >> 1) & 3], f2_pack(p0, p1));
         __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
         packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
       }
-      l += ((sum8[0] + sum8[1]) + (sum8[2] + sum8[3])) + ((sum8[4] + sum8[5]) + (sum8[6] + sum8[7]));
+      {
+        const uint64_t a = f2_add2(f2_add2(sum4[0], sum4[1]), f2_add2(sum4[2], sum4[3]));
+        l += __uint_as_float(static_cast<uint32_t>(a)) + __uint_as_float(static_cast<uint32_t>(a >> 32));
+      }
 
       // P(j-1) V(j-1) must have completed: it read the P buffer and wrote O.
       if (!mbar_wait(&ctl.pv_done[t], (j & 1) ^ 1u, &ctl.abort_flag, p.status, 0xB32 + t)) { ok = false; break; }

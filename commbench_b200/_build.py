@@ -66,7 +66,12 @@ def _key(src: Path, hdr: str, flags: list[str]) -> str:
 
 def _compile(nvcc: str, src: Path, obj: Path, flags: list[str], verbose: bool) -> tuple[Path, str]:
     cmd = [nvcc, *flags, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
-    if src.suffix == ".cc":
+    if src.suffix == ".cc" and src.name.startswith("transport_"):
+        # Host-only C++ (containers of local types trip the CUDA front end): nvcc hands the file
+        # to the host compiler, with the toolkit's include paths.
+        host_flags = [f for f in flags if not f.startswith("-Xptxas") and f != "--expt-relaxed-constexpr"]
+        cmd = [nvcc, *host_flags, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    elif src.suffix == ".cc":
         cmd = [nvcc, *flags, "-x", "cu", "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     log = (r.stdout or "") + (r.stderr or "")

@@ -168,7 +168,7 @@ def compile_source(source: str, out_dir: str, timeout_s: float = 300.0) -> tuple
     """(ok, returncode, log, binary).  Python sources are byte-compiled as the syntax check."""
     ext = os.path.splitext(source)[1]
     if ext == ".py":
-        r = run_in_new_session([sys.executable, "-m", "py_compile", source], timeout_s=60,
+        r = run_in_new_session([sys.executable, "-m", "py_compile", source], timeout=60,
                                env=scrubbed_env())
         return r.returncode == 0, r.returncode, (r.stdout + r.stderr), None
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
@@ -178,7 +178,7 @@ def compile_source(source: str, out_dir: str, timeout_s: float = 300.0) -> tuple
     binary = os.path.join(out_dir, os.path.splitext(os.path.basename(source))[0])
     cmd = [nvcc] + NVCC_FLAGS + ["-I", os.path.join(PKG_ROOT, "csrc"), "-x", "cu", source, "-o", binary,
                                  "-lcuda"]
-    r = run_in_new_session(cmd, timeout_s=timeout_s, env=scrubbed_env())
+    r = run_in_new_session(cmd, timeout=timeout_s, env=scrubbed_env())
     ok = r.returncode == 0 and os.path.exists(binary)
     return ok, r.returncode, (r.stdout + r.stderr), binary if ok else None
 
@@ -196,7 +196,7 @@ def compile_and_run(folder: str, source: str, timeout_s: float | None = None,
         return res
     cmd = build_command(spec, source, binary)
     res.command = cmd
-    r = run_in_new_session(cmd, timeout_s=float(timeout_s or spec["timeout_s"]),
+    r = run_in_new_session(cmd, timeout=float(timeout_s or spec["timeout_s"]),
                            env=scrubbed_env(spec.get("env")), cwd=folder)
     res.run_returncode, res.run_stdout, res.run_stderr = r.returncode, r.stdout, r.stderr
     res.timed_out = r.timed_out
@@ -262,16 +262,14 @@ def compare_save_results(folder: str, ref_source: str, gen_source: str, results_
     gen = compile_and_run(folder, gen_source, timeout_s, work_dir=os.path.join(results_dir, "build_gen"))
     ref_m = {**metrics_average(ref.result_json), **ref.metrics}
     gen_m = {**metrics_average(gen.result_json), **gen.metrics}
+    # The task names the metric its programs print; otherwise the op registry decides.
     entry = None
-    if spec.get("op"):
+    if spec.get("primary_metric"):
+        entry = {"primary": spec["primary_metric"], "direction": spec.get("direction", "lower")}
+    elif spec.get("op"):
         from . import registry
 
-        try:
-            entry = registry.entry(spec["op"])
-        except KeyError:
-            entry = None
-    if entry is None and spec.get("primary_metric"):
-        entry = {"primary": spec["primary_metric"], "direction": spec.get("direction", "lower")}
+        entry = registry.entry(spec["op"])
     v = V.compute_verdict(entry if entry is not None else "info_only", ref_m, gen_m)
     gen_ok, gen_why = analyze_result(gen)
     summary = {

@@ -160,7 +160,8 @@ def detect_gpu(runner=None, which=shutil.which) -> GpuInfo:
 def parse_topology(text: str) -> tuple[int, bool | None]:
     """From ``nvidia-smi topo -m``: how many GPUs GPU0 reaches over NVLink (``NV<k>`` cells), and
     whether every pair has the same link count (the signature of an NVSwitch fabric)."""
-    rows = [ln.split() for ln in text.splitlines() if re.match(r"^\s*GPU\d+\s", ln)]
+    # Matrix rows start with "GPUn" at column 0 (the header row is indented) and hold an "X".
+    rows = [ln.split() for ln in text.splitlines() if re.match(r"^GPU\d+\s", ln) and " X " in f" {ln} ".replace("\t", " ")]
     if not rows:
         return 0, None
     n = len(rows)

@@ -33,6 +33,7 @@ import torch
 from .. import _native as N
 
 _ALIGN = 1024  # TMA 128-byte swizzle wants 1024-byte aligned tiles
+_CANARY = 0xA5
 
 
 class CommError(RuntimeError):
@@ -133,6 +134,7 @@ class CommContext(_ContextBase):
         self._broker = C.c_void_p(0)
         self._segments = []  # (handle, local_ptr, peer_ptrs, mc_ptr, nbytes, used)
         self._named: dict[str, SymmBlock] = {}
+        self._canaries = [] if os.environ.get("CB200_DEBUG_CANARIES", "0") != "0" else None
         self.mode = "single"
         self.has_multicast = False
         self._closed = False
@@ -286,20 +288,40 @@ class CommContext(_ContextBase):
     def alloc(self, nbytes: int) -> SymmBlock:
         """Collective: every rank calls it with the same size in the same order."""
         nbytes = max(int(nbytes), 16)
-        need = (nbytes + _ALIGN - 1) // _ALIGN * _ALIGN
+        # Debug build of the heap: one guard page of a known pattern on either side of every
+        # block, verified by check_canaries() - an out-of-bounds peer store shows up there.
+        guard = _ALIGN if self._canaries is not None else 0
+        need = (nbytes + _ALIGN - 1) // _ALIGN * _ALIGN + 2 * guard
         seg = self._segments[-1]
         if seg["used"] + need > seg["nbytes"]:
             self._add_segment(max(need, self.heap_bytes))
             seg = self._segments[-1]
-        off = seg["used"]
+        off = seg["used"] + guard
         seg["used"] += need
         if seg["tensor"] is not None:
             local = seg["tensor"][off:off + nbytes]
         else:
             local = tensor_from_ptr(seg["local"] + off, nbytes, self.device, owner=self)
+        if guard:
+            base = seg["local"] if seg["tensor"] is None else seg["tensor"].data_ptr()
+            for g_off in (off - guard, off + need - 2 * guard):
+                g = tensor_from_ptr(base + g_off, guard, self.device, owner=self)
+                g.fill_(_CANARY)
+                self._canaries.append((g, off, nbytes))
         return SymmBlock(offset=off, nbytes=nbytes, local=local,
                          peer_ptrs=[p + off for p in seg["peers"]],
                          mc_ptr=(seg["mc"] + off) if seg["mc"] else 0)
+
+    def check_canaries(self):
+        """Debug heaps only (``CB200_DEBUG_CANARIES=1``): raises if any guard page around a
+        symmetric block was written to."""
+        if not self._canaries:
+            return
+        torch.cuda.synchronize(self.device) if self.device.type == "cuda" else None
+        for g, off, nbytes in self._canaries:
+            if not bool((g == _CANARY).all()):
+                raise CommError(f"guard page of the symmetric block at offset {off} "
+                                f"({nbytes} bytes) was overwritten")
 
     def named(self, name: str, nbytes: int) -> SymmBlock:
         """Persistent block keyed by name; re-allocated (collectively) when it must grow."""

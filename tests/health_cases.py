@@ -60,7 +60,7 @@ def gpu_leave(rank, world, scratch):
     learns of it from the heart-beat board and raises instead of launching the next step.
     Multicast is off in this package and in NCCL, kernels use plain peer loads."""
     os.environ["NCCL_NVLS_ENABLE"] = "0"
-    os.environ["CB200_USE_NVLS"] = "0"
+    os.environ["CB200_NVLS"] = "0"
     import torch
     import torch.distributed as dist
 

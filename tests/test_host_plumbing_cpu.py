@@ -27,8 +27,8 @@ def _broker_worker(name, rank, world, q):
         assert lib.cb_broker_exchange_fds(b, fd, fds, 120000) == 0, N.last_error()
         got = []
         for r in range(world):
-            os.lseek(fds[r], 0, os.SEEK_SET)
-            got.append(os.read(fds[r], 8))
+            # pread: the descriptors share one file offset across all the processes
+            got.append(os.pread(fds[r], 8, 0))
             os.close(fds[r])
         assert got == [bytes([r + 65]) * 8 for r in range(world)]
     assert lib.cb_broker_barrier(b, 120000) == 0
@@ -38,8 +38,7 @@ def _broker_worker(name, rank, world, q):
     assert list(allb) == [r for r in range(world) for _ in range(16)]
     out = C.c_int(-1)
     assert lib.cb_broker_broadcast_fd(b, 1, fd, C.byref(out), 120000) == 0
-    os.lseek(out.value, 0, os.SEEK_SET)
-    assert os.read(out.value, 8) == bytes([1 + 65]) * 8
+    assert os.pread(out.value, 8, 0) == bytes([1 + 65]) * 8
     os.close(out.value)
     lib.cb_broker_destroy(b)
     q.put((rank, "ok"))

@@ -14,6 +14,7 @@ OPS: dict = {
                    "examples": ["example022", "example031", "example043", "example048", "example060",
                                 "example095", "example097", "example098", "example099", "example105",
                                 "example109"]},
+    "internode_all_reduce": {**TIME, "family": "transport", "examples": ["example092"]},
     "all_gather": {**TIME, "family": "collective",
                    "examples": ["example021", "example030", "example045", "example046", "example059"]},
     "reduce_scatter": {**TIME, "family": "collective",

@@ -382,3 +382,63 @@ def exchange_metadata(sock: socket.socket, addr: Addr, buf_addr: int = 0, rkey: 
         raw += chunk
     blob, peer_buf, peer_rkey = _META.unpack(raw)
     return Addr.unpack(blob), peer_buf, peer_rkey
+
+
+# ------------------------------------------------------- two-rank all-reduce over put + signal
+class PutSignalAllReduce:
+    """All-reduce between two ranks that are only connected by the transport (another node):
+    put the local vector into the peer's receive window, bump the peer's signal counter with a
+    remote atomic, flush, wait for the peer's signal, add.  The pattern of
+    datasets/example092_nccl_device_api_internode_allreduce/
+    empty_nccl_device_api_internode_allreduce.cu:47-87 (put with signal increment, wait on the
+    signal, flush, local add), expressed on work requests instead of a vendor's device API.
+
+    Each side: ``ar = PutSignalAllReduce(ctx, ep, numel)``; exchange ``ar.window()`` with the
+    peer (``connect_window``); then per call ``ar.start(x)`` followed by ``ar.finish()``."""
+
+    def __init__(self, ctx: Context, ep: Endpoint, numel: int):
+        import numpy as np
+
+        self.ctx, self.ep, self.numel = ctx, ep, numel
+        self.send = np.zeros(numel, dtype=np.float32)
+        self.recv = np.zeros(numel, dtype=np.float32)
+        self.signal = np.zeros(1, dtype=np.uint64)
+        self.scratch = np.zeros(1, dtype=np.uint64)
+        self.m_send, self.m_recv = ctx.reg_mr(self.send), ctx.reg_mr(self.recv)
+        self.m_sig, self.m_scr = ctx.reg_mr(self.signal), ctx.reg_mr(self.scratch)
+        self.round = 0
+        self.peer = None
+
+    def window(self) -> tuple[int, int, int, int]:
+        return (self.m_recv.addr, self.m_recv.rkey, self.m_sig.addr, self.m_sig.rkey)
+
+    def connect_window(self, peer_window):
+        self.peer = tuple(peer_window)
+
+    def start(self, x):
+        if self.peer is None:
+            raise TransportError("connect_window() first")
+        self.send[:] = x
+        raddr, rkey, saddr, skey = self.peer
+        self.round += 1
+        self.ep.post(WRITE, [self.m_send.sge()], wr_id=2 * self.round, remote_addr=raddr, rkey=rkey)
+        self.ep.post(ATOMIC_FADD, [self.m_scr.sge()], wr_id=2 * self.round + 1, remote_addr=saddr,
+                     rkey=skey, compare_add=1)
+
+    def finish(self, timeout_s: float = 10.0):
+        import time as _time
+
+        done = 0
+        deadline = _time.monotonic() + timeout_s
+        while done < 2:                                    # flush: both requests completed
+            for c in self.ep.poll_send(timeout_us=100_000):
+                if not c.ok:
+                    raise TransportError(f"all-reduce put failed with status {c.status}")
+                done += 1
+            if _time.monotonic() > deadline:
+                raise TransportError("all-reduce: flush timed out")
+        while int(self.signal[0]) < self.round:            # the peer's put has landed
+            if _time.monotonic() > deadline:
+                raise TransportError("all-reduce: the peer's signal never arrived")
+            _time.sleep(0)
+        return self.send + self.recv

@@ -296,3 +296,22 @@ def test_two_contexts_and_tcp_metadata_exchange(native_lib):
     th.join(10)
     srv.close()
     assert result["imm"] == 42 and np.array_equal(result["data"], np.arange(128, dtype=np.uint8))
+
+
+def test_two_rank_allreduce_over_put_and_signal(ctx):
+    a, b = _pair(ctx)
+    ra, rb = T.PutSignalAllReduce(ctx, a, 1024), T.PutSignalAllReduce(ctx, b, 1024)
+    ra.connect_window(rb.window())
+    rb.connect_window(ra.window())
+    rng = np.random.default_rng(3)
+    for _ in range(3):
+        xa, xb = rng.random(1024, dtype=np.float32), rng.random(1024, dtype=np.float32)
+        ra.start(xa)
+        rb.start(xb)
+        ya, yb = ra.finish(), rb.finish()
+        assert np.array_equal(ya, yb) and np.allclose(ya, xa + xb)
+    lonely = T.PutSignalAllReduce(ctx, a, 8)
+    lonely.connect_window(rb.window())
+    lonely.start(np.ones(8, dtype=np.float32))
+    with pytest.raises(T.TransportError, match="signal never arrived"):
+        lonely.finish(timeout_s=0.3)                    # nobody answers: bounded wait, no hang

@@ -160,6 +160,26 @@ class MoELayer:
         st = self.states[r if self.emu else 0]
         return st.w1, st.w2
 
+    # ------------------------------------------------------------------ stage timing
+    def enable_stage_timing(self, on: bool = True):
+        """Records a CUDA event after every stage of the next ``forward`` calls;
+        ``stage_ms()`` (after a synchronize) returns the time spent in each stage."""
+        self._marks = [] if on else None
+
+    def _mark(self, name: str):
+        if getattr(self, "_marks", None) is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._marks.append((name, ev))
+
+    def stage_ms(self) -> dict:
+        marks, out = getattr(self, "_marks", None) or [], {}
+        for (_, e0), (name, e1) in zip(marks, marks[1:]):
+            if name != "begin":
+                out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+        self._marks = []
+        return out
+
     # ------------------------------------------------------------------ forward
     def forward(self, xs, topk_idx, topk_w):
         """xs [T, H] bf16, topk_idx [T, K] int32, topk_w [T, K] fp32 (lists in emulation).
@@ -169,6 +189,7 @@ class MoELayer:
             xs, topk_idx, topk_w = [xs], [topk_idx], [topk_w]
         sp = N.stream_ptr()
         n_pairs = T * K
+        self._mark("begin")
         # 1. slots + counts
         for st, idx in zip(self.states, topk_idx):
             N.check(lib.cb_moe_slots(N.ptr(idx), n_pairs, E, N.ptr(st.slot), N.ptr(st.counts), sp),
@@ -178,6 +199,7 @@ class MoELayer:
             counts_all = [torch.stack([s.counts for s in self.states]).contiguous()] * W
         else:
             counts_all = [coll.all_gather(self.ctx, self.states[0].counts.view(1, E)).contiguous()]
+        self._mark("slots+count_gather")
         # 3. plan + sorted pairs
         for st, idx, ca in zip(self.states, topk_idx, counts_all):
             N.check(lib.cb_moe_plan(N.ptr(ca), W, E, st.r, N.ptr(st.send_row_base),
@@ -188,6 +210,7 @@ class MoELayer:
             N.check(lib.cb_moe_sort_pairs(N.ptr(idx), N.ptr(st.slot), N.ptr(st.src_pair_base),
                                           n_pairs, E, N.ptr(st.sorted_pair), sp),
                     "cb_moe_sort_pairs")
+        self._mark("plan+sort")
         # 4. dispatch push (quantise + send + per-expert arrival counters)
         for st, x, idx, w in zip(self.states, xs, topk_idx, topk_w):
             a = _SendArgs()
@@ -203,6 +226,7 @@ class MoELayer:
             a.rank, a.world, a.T, a.K, a.H, a.E, a.max_rows = st.r, W, T, K, H, E, self.max_rows
             a.status = self._status(st)
             N.check(lib.cb_moe_dispatch_send(C.byref(a), 4, sp), "cb_moe_dispatch_send")
+        self._mark("dispatch_send")
         # 5. receive: wait per expert, dequantise to bf16, mark padding rows
         for st in self.states:
             ra = _RecvArgs()
@@ -217,6 +241,7 @@ class MoELayer:
             N.check(lib.cb_moe_recv_dequant(C.byref(ra), self.El, 4, sp), "cb_moe_recv_dequant")
             self._local(self.arrived, st)[:self.El * 4].zero_()   # counters ready for the next call
             st.n_rows.copy_(st.n_mblocks * 128)
+        self._mark("recv_dequant")
         # 6. grouped GEMMs; the second one sends rows home
         for st in self.states:
             d = _GroupedDesc()
@@ -226,7 +251,9 @@ class MoELayer:
             d.mblk_expert, d.n_mblocks = st.mblk_expert.data_ptr(), st.n_mblocks.data_ptr()
             d.status = self._status(st)
             N.check(lib.cb_moe_grouped_gemm(C.byref(d), sp), "grouped gemm (up)")
+            self._mark("gemm_up")
             N.check(lib.cb_moe_swiglu(N.ptr(st.h1), N.ptr(st.s), N.ptr(st.n_rows), I, sp), "swiglu")
+            self._mark("swiglu")
             d2 = _GroupedDesc()
             d2.max_rows, d2.N, d2.K, d2.n_local_experts = self.max_rows, H, I, self.El
             d2.down, d2.rank, d2.world, d2.ctas = 1, st.r, W, self.sms
@@ -239,6 +266,7 @@ class MoELayer:
             d2.done_ctas = st.done_ctas.data_ptr()
             d2.status = self._status(st)
             N.check(lib.cb_moe_grouped_gemm(C.byref(d2), sp), "grouped gemm (down)")
+            self._mark("gemm_down+scatter")
         # 7. weighted reduction at the token owners
         for st, idx, w in zip(self.states, topk_idx, topk_w):
             N.check(lib.cb_moe_combine_reduce(
@@ -246,6 +274,7 @@ class MoELayer:
                 N.ptr(self._local(self.done, st)), W, C.c_ulonglong(self.ctx.timeout_ns),
                 C.c_void_p(self._status(st)), C.c_void_p(st.done_ctas.data_ptr() + 8), sp),
                 "combine_reduce")
+        self._mark("combine_reduce")
         ys = [st.y for st in self.states]
         return ys if self.emu else ys[0]
 

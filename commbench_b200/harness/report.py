@@ -68,6 +68,46 @@ def finish_record(rec: dict) -> dict:
     return out
 
 
+def export_performance_reference(rows: list[dict], out_dir: str, meta: dict | None = None) -> list[str]:
+    """One JSON file per (op, variant, world) with the measured points over sizes, in the shape
+    programs of the task harness print (``metrics: [{data_size, latency_avg, throughput_avg}]``):
+    the stored numbers later runs are compared against - the role of the reference's
+    ``datasets/performance_reference/*.json``."""
+    os.makedirs(out_dir, exist_ok=True)
+    groups: dict[tuple, list[dict]] = {}
+    for r in rows:
+        if r.get("time_ms") is None:
+            continue
+        groups.setdefault((r["op"], r.get("variant", ""), r.get("world", 1)), []).append(r)
+    written = []
+    for (op, variant, world), rs in sorted(groups.items()):
+        pts = []
+        for r in sorted(rs, key=lambda x: x.get("bytes") or _numel(x.get("shape"))):
+            thr = r.get("busbw_gbs") if r.get("busbw_gbs") is not None else r.get("tflops")
+            pts.append({"data_size": _numel(r.get("shape")), "shape": r.get("shape"),
+                        "latency_avg": r["time_ms"] * 1e3, "throughput_avg": thr,
+                        "baseline_latency_avg": (r["baseline_ms"] * 1e3) if r.get("baseline_ms") else None,
+                        "roofline_frac": r.get("roofline_frac"), "verdict": r.get("verdict")})
+        doc = {"op": op, "variant": variant, "world": world, "dtype": rs[0].get("dtype"),
+               "Correctness": "PASS" if all(r.get("correct", True) for r in rs) else "FAIL",
+               "data_size_unit": "elements", "latency_unit": "us",
+               "throughput_unit": "GB/s (bus)" if rs[0].get("busbw_gbs") is not None else "TFLOP/s",
+               "hardware": (meta or {}).get("hardware", "8x NVIDIA B200 (NVLink 5 / NVSwitch)"),
+               "metrics": pts}
+        path = os.path.join(out_dir, f"{op}_{variant or 'default'}_w{world}.json".replace("/", "-"))
+        with open(path, "w") as f:
+            json.dump(doc, f, indent=1)
+        written.append(path)
+    return written
+
+
+def _numel(shape) -> int:
+    n = 1
+    for s in shape or []:
+        n *= int(s)
+    return n
+
+
 def write_summary(records: list[dict], out_dir: str, meta: dict | None = None) -> dict:
     os.makedirs(out_dir, exist_ok=True)
     rows = [finish_record(r) for r in records]
@@ -84,6 +124,7 @@ def write_summary(records: list[dict], out_dir: str, meta: dict | None = None) -
     }
     with open(os.path.join(out_dir, "summary.json"), "w") as f:
         json.dump(summary, f, indent=1)
+    export_performance_reference(rows, os.path.join(out_dir, "performance_reference"), meta)
     cols = ["op", "variant", "world", "dtype", "shape", "correct", "max_err", "time_ms",
             "baseline_ms", "speedup", "busbw_gbs", "tflops", "roofline_frac", "verdict"]
     with open(os.path.join(out_dir, "summary.csv"), "w", newline="") as f:

@@ -101,7 +101,7 @@ def main(argv=None) -> int:
     if "allreduce" in suites:
         step = 2 if args.quick else 1
         sizes = [1 << p for p in range(12, 31, step)]           # 4 KB ... 1 GB
-        algos = ["oneshot", "twoshot"] + (["nvls"] if ctx.has_multicast else [])
+        algos = ["oneshot", "twoshot"] + (["nvls"] if ctx.has_multicast else []) + ["auto"]
         if world == 1:
             algos = ["oneshot"]
         sym_full, _ = ctx.empty((sizes[-1] // 2,), torch.bfloat16)
@@ -122,10 +122,11 @@ def main(argv=None) -> int:
                     continue
                 sym.copy_(x)
                 sync_all()
-                if algo == "oneshot":
+                if algo == "oneshot" or (algo == "auto" and coll.choose_all_reduce_algo(
+                        nbytes, world, ctx.has_multicast) == "oneshot"):
                     out = torch.empty_like(x)
                     y = coll.all_reduce(ctx, sym, out=out, algo=algo)
-                    fn = lambda: coll.all_reduce(ctx, sym, out=out, algo="oneshot")
+                    fn = lambda a=algo: coll.all_reduce(ctx, sym, out=out, algo=a)
                 else:
                     y = coll.all_reduce(ctx, sym, algo=algo)
                     fn = lambda a=algo: coll.all_reduce(ctx, sym, algo=a)
@@ -218,7 +219,8 @@ def main(argv=None) -> int:
             ar = GemmAr(ctx, 1024, Nd)
         for Md in (16, 128, 1024):
             a3, b3 = rnd((Md, Kd), 400 + rank, 1.0), rnd((Nd, Kd), 500 + rank)
-            for variant in (("oneshot", True), ("twoshot", False)) if world > 1 else (("local", None),):
+            for variant in (("oneshot", True), ("twoshot", False), ("auto", None)) if world > 1 \
+                    else (("local", None),):
                 if world > 1:
                     ours = lambda v=variant[1]: ar(a3, b3, oneshot=v)
                     theirs = lambda: base.gemm_ar(a3, b3)

@@ -82,7 +82,6 @@ def generate_eval_one(task: str, model: str = "gpt-4o", max_rounds: int = 3,
     history: list[dict] = []
     result, perf, reason = None, None, "no round ran"
     pass_round = improve_round = None
-    best_code = None
     for rnd in range(1, max_rounds + 1):
         stamp = time.strftime("%Y%m%d_%H%M%S")
         if candidate is not None:
@@ -114,7 +113,6 @@ def generate_eval_one(task: str, model: str = "gpt-4o", max_rounds: int = 3,
             continue
         if pass_round is None:
             pass_round = rnd
-        best_code = code
         if ref is None:
             improve_round = rnd
             break
@@ -138,8 +136,6 @@ def generate_eval_one(task: str, model: str = "gpt-4o", max_rounds: int = 3,
     os.makedirs(out_root, exist_ok=True)
     with open(os.path.join(out_root, "summary.json"), "w") as f:
         json.dump(final, f, indent=1)
-    if not save and best_code is None:
-        pass
     return passed, reason, result, rounds, perf
 
 

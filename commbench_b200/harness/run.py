@@ -170,6 +170,31 @@ def main(argv=None) -> int:
                        baseline_ms=bms, busbw_gbs=link / (ms * 1e-3) / 1e9,
                        roofline_frac=roofline.fraction(roofline.roofline_ms(0, link, peaks), ms))
 
+    # ------------------------------------------------- point-to-point and barrier probes
+    if "p2p" in suites and world > 1:
+        from ..ops import util as U
+
+        us = U.pingpong_latency(ctx, 2000)
+        t = torch.tensor([us if us is not None else 0.0], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        record("p2p_pingpong", "peer-store", (1,), "u32", correct=True, time_ms=t.item() / 1e3,
+               baseline_ms=None, round_trip_us=t.item())
+        for use_nvls in ([False, True] if ctx.has_multicast else [False]):
+            b_us = U.barrier_latency(ctx, 1000, use_nvls)
+            t = torch.tensor([b_us], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            record("barrier", "nvls" if use_nvls else "flag-matrix", (world,), "u32", correct=True,
+                   time_ms=t.item() / 1e3, baseline_ms=None, latency_us=t.item())
+        for mb in (1, 256):
+            for mode in ("kernel", "engine"):
+                gbs = U.peer_copy_bandwidth(ctx, mb << 20, mode)
+                t = torch.tensor([gbs], device=dev, dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MIN)
+                ms = (mb << 20) / (t.item() * 1e6)
+                record("p2p_copy", mode, (mb << 20,), "u8", correct=True, time_ms=ms, baseline_ms=None,
+                       busbw_gbs=t.item(),
+                       roofline_frac=t.item() / peaks.nvlink_gbs)
+
     # ------------------------------------------------- tensor-parallel fused GEMMs
     if "tp" in suites:
         from ..ops.gemm import gemm

@@ -235,3 +235,82 @@ def ipc_export(t: torch.Tensor):
 def ipc_import(handle) -> torch.Tensor:
     fn, args = handle
     return fn(*args)
+
+
+# ------------------------------------------------------------- multi-GPU point-to-point probes
+def pingpong_latency(ctx, rounds: int = 2000) -> float | None:
+    """Round-trip time in microseconds of a one-word ping-pong between ranks 0 and 1 through
+    peer memory (one warp per GPU, release store + bounded acquire wait).  Collective over the
+    context; ranks above 1 only take part in the barriers and return ``None``
+    (datasets/example073_GPU_p2p_pingpong_latency/nv/empty_p2p_pingpong_latency.cu:30-56)."""
+    lib = N.load()
+    blk = ctx.named("probe_pingpong", 256)
+    word = blk.view(torch.int32, (64,))
+    if not getattr(ctx, "_pingpong_ready", False):
+        word.zero_()
+        ctx._pingpong_ready = True
+        torch.cuda.synchronize(ctx.device)
+        ctx.host_barrier()
+    base = int(word[1].item())                       # running value: the words only ever grow
+    elapsed = torch.zeros(1, dtype=torch.int64, device=ctx.device)
+    torch.cuda.synchronize(ctx.device)
+    ctx.host_barrier()
+    out = None
+    if ctx.rank < 2 and ctx.world >= 2:
+        peer = 1 - ctx.rank
+        N.check(lib.cb_probe_pingpong(C.c_void_p(blk.peer_ptrs[ctx.rank]),
+                                      C.c_void_p(blk.peer_ptrs[peer]), ctx.rank, rounds,
+                                      C.c_uint(base), C.c_ulonglong(ctx.timeout_ns),
+                                      C.c_void_p(ctx.comm.status), N.ptr(elapsed), N.stream_ptr()),
+                "cb_probe_pingpong")
+        torch.cuda.synchronize(ctx.device)
+        ctx.check_status()
+        out = elapsed.item() / rounds / 1e3
+    word[1] = base + rounds
+    torch.cuda.synchronize(ctx.device)
+    ctx.host_barrier()
+    return out
+
+
+def peer_copy_bandwidth(ctx, nbytes: int, mode: str = "kernel", iters: int = 10, warmup: int = 3) -> float:
+    """GB/s of pushing ``nbytes`` from this rank into the next rank's symmetric memory, with the
+    16-byte copy kernel (``mode="kernel"``) or the copy engine (``mode="engine"``).  Every rank
+    pushes at once (datasets/example074_GPU_p2p_d2d_bandwidth/nv/empty_p2p_d2d_bandwidth.cu:29-36,
+    datasets/example001_gpu_comm_single_process/nv/empty_gpu_comm_single_process.cu)."""
+    from ..runtime.context import tensor_from_ptr
+
+    blk = ctx.named("probe_peer_copy", nbytes)
+    src = torch.empty(nbytes, dtype=torch.uint8, device=ctx.device)
+    src.fill_(ctx.rank + 1)
+    peer = (ctx.rank + 1) % ctx.world
+    dst_ptr = blk.peer_ptrs[peer]
+    torch.cuda.synchronize(ctx.device)
+    ctx.host_barrier()
+    if mode == "kernel":
+        gbs = copy_bandwidth(dst_ptr, src.data_ptr(), nbytes, 16, iters=iters, warmup=warmup)
+    else:
+        dst = tensor_from_ptr(dst_ptr, nbytes, ctx.device, owner=ctx)
+        gbs = memcpy_bandwidth(dst, src, iters, warmup)
+    torch.cuda.synchronize(ctx.device)
+    ctx.host_barrier()
+    got = int(blk.view(torch.uint8, (nbytes,))[nbytes - 1].item())
+    if got != (ctx.rank - 1) % ctx.world + 1:
+        raise UtilError(f"peer copy: expected the previous rank's pattern, found {got}")
+    return gbs
+
+
+def barrier_latency(ctx, iters: int = 1000, use_nvls: bool = False) -> float:
+    """Microseconds per cross-GPU barrier, measured over ``iters`` back-to-back barriers inside
+    one launch (datasets/example017_intranode_gpu_barrier/nv/empty_intranode_gpu_barrier.cu:114-125)."""
+    from . import collectives as coll
+
+    coll.barrier(ctx, 8, use_nvls)
+    torch.cuda.synchronize(ctx.device)
+    ctx.host_barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    coll.barrier(ctx, iters, use_nvls)
+    e1.record()
+    torch.cuda.synchronize(ctx.device)
+    ctx.check_status()
+    return e0.elapsed_time(e1) * 1e3 / iters

@@ -246,7 +246,24 @@ def main():
         report("ring/zigzag", torch.allclose(o.float(), rz, atol=3e-2, rtol=3e-2),
                (o.float() - rz).abs().max().item())
 
-    t_moe(); t_attention()
+    @guarded("p2p_probes")
+    def t_p2p():
+        from commbench_b200.ops import util as U
+
+        us = U.pingpong_latency(ctx, 500)
+        report("pingpong", rank >= 2 or (us is not None and 0.5 < us < 200.0), us)
+        us2 = U.pingpong_latency(ctx, 500)          # second call continues from the running value
+        report("pingpong/again", rank >= 2 or (us2 is not None and 0.5 < us2 < 200.0), us2)
+        for mode in ("kernel", "engine"):
+            gbs = U.peer_copy_bandwidth(ctx, 64 << 20, mode)
+            report(f"peer_copy/{mode}", gbs > 50.0, gbs)
+        b = U.barrier_latency(ctx, 200, False)
+        report("barrier_latency", 0.5 < b < 500.0, b)
+        if ctx.has_multicast:
+            b = U.barrier_latency(ctx, 200, True)
+            report("barrier_latency/nvls", 0.5 < b < 500.0, b)
+
+    t_moe(); t_attention(); t_p2p()
     t_all_reduce(); t_all_gather(); t_reduce_scatter(); t_all_to_all(); t_broadcast()
     t_ag_gemm(); t_gemm_rs(); t_gemm_ar()
     torch.cuda.synchronize()

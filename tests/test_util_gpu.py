@@ -77,3 +77,35 @@ def test_probes(native_lib):
     # D2H into pinned host memory: copy engine vs kernel stores into mapped memory
     host = torch.empty(16 << 20, dtype=torch.uint8).pin_memory()
     assert util.memcpy_bandwidth(host, src[:16 << 20]) > 1
+
+
+def _ipc_consumer(handle, q):
+    import torch
+
+    from commbench_b200.ops.util import ipc_import
+
+    w = ipc_import(handle)                       # maps the producer's allocation, no copy
+    local = torch.empty_like(w)
+    local.copy_(w)                               # "load the new weights"
+    torch.cuda.synchronize()
+    q.put((tuple(w.shape), float(local.double().sum().item()), int(w.data_ptr() != 0)))
+
+
+@pytest.mark.timeout(300)
+def test_ipc_weight_hand_off_between_two_processes(native_lib):
+    """A trainer process exports a weight tensor by CUDA-IPC handle; an inference process on the
+    same GPU maps it and copies it into its own weights (no host staging)."""
+    import torch.multiprocessing as mp
+
+    from commbench_b200.ops.util import ipc_export
+
+    w = torch.arange(1 << 20, device="cuda", dtype=torch.float32).view(1024, 1024)
+    expect = float(w.double().sum().item())
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_ipc_consumer, args=(ipc_export(w), q))
+    p.start()
+    shape, total, mapped = q.get(timeout=240)
+    p.join(60)
+    assert p.exitcode == 0 and shape == (1024, 1024) and mapped == 1
+    assert total == expect

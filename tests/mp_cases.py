@@ -263,7 +263,65 @@ def main():
             b = U.barrier_latency(ctx, 200, True)
             report("barrier_latency/nvls", 0.5 < b < 500.0, b)
 
-    t_moe(); t_attention(); t_p2p()
+    @guarded("parallel")
+    def t_parallel():
+        from commbench_b200.parallel import dp, tp
+
+        # ---- data parallel: gradients accumulate straight into symmetric buckets
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.ReLU(),
+                                    torch.nn.Linear(512, 64)).cuda()
+        buckets = dp.GradBuckets(ctx, model.parameters(), bucket_bytes=256 << 10)
+        g = torch.Generator(device="cuda").manual_seed(900 + rank)
+        x = torch.randn(32, 256, device="cuda", generator=g)
+        model(x).square().mean().backward()
+        ref = [p.grad.detach().clone() for p in model.parameters()]
+        for r in ref:
+            dist.all_reduce(r)
+        shards = None
+        if all(b.numel() % world == 0 for b in buckets.buckets):
+            keep = [b.clone() for b in buckets.buckets]
+            shards = buckets.reduce_scatter(average=False)
+            for b, k in zip(buckets.buckets, keep):
+                b.copy_(k)
+        buckets.all_reduce(average=False)
+        ctx.check_status()
+        ok = all(torch.allclose(p.grad, r, rtol=1e-4, atol=1e-5) for p, r in zip(model.parameters(), ref))
+        report("dp/grad_all_reduce", ok and len(buckets.buckets) >= 2, len(buckets.buckets))
+        if shards is not None:
+            ok = True
+            for i, sh in enumerate(shards):
+                lo, hi = buckets.shard_range(i)
+                ok = ok and torch.allclose(sh, buckets.buckets[i][lo:hi], rtol=1e-4, atol=1e-5)
+            report("dp/grad_reduce_scatter", ok)
+        lin = torch.nn.Linear(128, 128, bias=False).cuda().bfloat16()
+        sp = dp.ShardedParams(ctx, lin.parameters())
+        sp.flat.zero_()
+        sp.local_shard().fill_(rank + 1)
+        sp.all_gather()
+        ctx.check_status()
+        n = sp.total // world
+        want = torch.arange(1, world + 1, device="cuda").repeat_interleave(n).to(sp.flat.dtype)
+        report("dp/param_all_gather", torch.equal(sp.flat, want) and lin.weight.data_ptr() == sp.flat.data_ptr())
+        # ---- tensor parallel linear layers
+        T, H, F = 128 * world, 512, 1024
+        col = tp.ColumnParallelLinear(ctx, H, F, T, seed=5)
+        row = tp.RowParallelLinear(ctx, F, H, T, scatter_rows=True, seed=6)
+        rep = tp.RowParallelLinear(ctx, F, H, T, scatter_rows=False, seed=6)
+        xl = rnd((T // world, H), 700 + rank, 1.0)
+        xg = torch.cat(gather_all(xl))
+        h = col(xl)
+        ctx.check_status()
+        report("tp/column", close(h, xg.float() @ col.weight.float().t()))
+        y = row(h)
+        yr = rep(h)
+        ctx.check_status()
+        full = h.float() @ row.weight.float().t()
+        dist.all_reduce(full)
+        report("tp/row_scatter", close(y, full[rank * (T // world):(rank + 1) * (T // world)]))
+        report("tp/row_replicated", close(yr, full))
+
+    t_moe(); t_attention(); t_p2p(); t_parallel()
     t_all_reduce(); t_all_gather(); t_reduce_scatter(); t_all_to_all(); t_broadcast()
     t_ag_gemm(); t_gemm_rs(); t_gemm_ar()
     torch.cuda.synchronize()

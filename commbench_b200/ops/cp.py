@@ -30,9 +30,9 @@ def flash_attention(q, k, v, causal: bool = True, q_offset: int = 0, kv_offset: 
                     stream=None, impl: int | None = None):
     """One key/value chunk: returns (o [B,Sq,Hq,D] bf16 normalised, lse [B,Hq,Sq] fp32).
 
-    ``impl`` selects the kernel: 2 = two query tiles and two softmax warp-groups per CTA with O
-    in tensor memory (default, ``CB200_ATTN_IMPL``), 1 = the first design (one tile, O in
-    registers).
+    ``impl`` selects the kernel (default from ``CB200_ATTN_IMPL``): 3 = two query tiles per CTA,
+    two threads per query row (16 softmax warps), O in tensor memory; 2 = the same with one
+    thread per row (8 softmax warps); 1 = the first design (one tile, O in registers).
 
     ``q_offset`` / ``kv_offset`` are the global sequence positions of the first query / key;
     with ``causal`` key j is visible to query i iff kv_offset + j <= q_offset + i."""
@@ -52,7 +52,9 @@ def flash_attention(q, k, v, causal: bool = True, q_offset: int = 0, kv_offset: 
     sc = scale if scale is not None else 1.0 / math.sqrt(D)
     if impl is None:
         impl = get_config().attn_impl
-    fn = lib.cb_attn_fwd2 if impl == 2 else lib.cb_attn_fwd
+    fn = {1: lib.cb_attn_fwd, 2: lib.cb_attn_fwd2, 3: lib.cb_attn_fwd3}.get(impl)
+    if fn is None:
+        raise CommError(f"unknown attention kernel {impl} (1, 2 or 3)")
     rc = fn(N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(out), N.ptr(lse), B, Sq, Skv, Hq, Hkv,
             q_offset, kv_offset, int(causal), C.c_float(sc), C.c_void_p(status_ptr),
             N.stream_ptr(stream))

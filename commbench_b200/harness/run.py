@@ -32,6 +32,8 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--quick", action="store_true", help="coarser sweeps (every 4th size)")
+    ap.add_argument("--graphs", action="store_true",
+                    help="also time small all-reduces replayed from CUDA graphs (ours and NCCL)")
     ap.add_argument("--scale", type=float, default=1.0,
                     help="shrink the MoE / attention shapes (1.0 = the target configurations)")
     args = ap.parse_args(argv)
@@ -144,6 +146,18 @@ def main(argv=None) -> int:
                        baseline_busbw_gbs=(f * nbytes / (base_ms * 1e-3) / 1e9) if base_ms else None,
                        roofline_frac=roofline.fraction(roofline.roofline_ms(0, link, peaks), ms),
                        roofline_note=f"of {peaks.source}")
+                if algo == "auto" and nbytes <= (1 << 20) and world > 1 and args.graphs:
+                    # Small messages are launch bound: the same call replayed from a CUDA graph,
+                    # against NCCL replayed from a graph as well.
+                    from ..utils.graphs import time_graphed
+
+                    gms = time_graphed(fn)
+                    gbase = time_graphed(lambda: base.all_reduce(x))
+                    ctx.check_status()
+                    record("all_reduce", "auto+graph", (n,), "bf16", correct=correct, max_err=err,
+                           time_ms=gms, baseline_ms=gbase, busbw_gbs=f * nbytes / (gms * 1e-3) / 1e9,
+                           roofline_frac=roofline.fraction(roofline.roofline_ms(0, link, peaks), gms),
+                           roofline_note=f"of {peaks.source}")
 
     # ----------------------------------------------------------- other collectives
     if "coll" in suites and world > 1:

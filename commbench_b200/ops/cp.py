@@ -52,9 +52,10 @@ def flash_attention(q, k, v, causal: bool = True, q_offset: int = 0, kv_offset: 
     sc = scale if scale is not None else 1.0 / math.sqrt(D)
     if impl is None:
         impl = get_config().attn_impl
-    fn = {1: lib.cb_attn_fwd, 2: lib.cb_attn_fwd2, 3: lib.cb_attn_fwd3}.get(impl)
+    fn = {1: lib.cb_attn_fwd, 2: lib.cb_attn_fwd2, 3: lib.cb_attn_fwd3,
+          4: lib.cb_attn_fwd4}.get(impl)
     if fn is None:
-        raise CommError(f"unknown attention kernel {impl} (1, 2 or 3)")
+        raise CommError(f"unknown attention kernel {impl} (1 to 4)")
     rc = fn(N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(out), N.ptr(lse), B, Sq, Skv, Hq, Hkv,
             q_offset, kv_offset, int(causal), C.c_float(sc), C.c_void_p(status_ptr),
             N.stream_ptr(stream))

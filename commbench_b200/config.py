@@ -28,7 +28,7 @@ class Config:
     gemm_ar_oneshot_max_m: int = 256            # rows at or below: one-shot AR epilogue
     fused_poll_ns: int = 300                    # pause between polls of a peer-written flag
     # --- attention -------------------------------------------------------
-    attn_impl: int = 2                          # flash-attention kernel: 2 (two tiles per CTA) or 1
+    attn_impl: int = 4                          # flash-attention kernel, 1..5 (4: P kept in TMEM)
     # --- MoE ---------------------------------------------------------------
     moe_expert_alignment: int = 128             # rows per expert padded to a tile multiple
     # --- runtime -----------------------------------------------------------

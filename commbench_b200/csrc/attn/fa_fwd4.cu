@@ -126,6 +126,8 @@ __device__ __forceinline__ int f4_num_blocks(const Fa4Params& p, int tile128) {
   return nblk;
 }
 
+// kPolyEvery: every kPolyEvery-th pair of keys takes its exponential from the FMA pipe (0: none).
+template <int kPolyEvery>
 __global__ void __launch_bounds__(F4_THREADS, 1) fa_fwd4_kernel(const __grid_constant__ Fa4Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem =
@@ -344,8 +346,28 @@ __global__ void __launch_bounds__(F4_THREADS, 1) fa_fwd4_kernel(const __grid_con
 #pragma unroll
       for (int i = 0; i < 128; i += 2) {
         const uint64_t y = f4_fma2(f4_pack_u(s[i], s[i + 1]), scale2, negm2);
-        const float p0 = f4_ex2(__uint_as_float(static_cast<uint32_t>(y)));
-        const float p1 = f4_ex2(__uint_as_float(static_cast<uint32_t>(y >> 32)));
+        float p0, p1;
+        if (kPolyEvery > 0 && !need_mask && ((i >> 1) % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1) {
+          // 2^x on the FMA pipe for this pair (the SFU sets the latency of a block's softmax,
+          // which sits on the per-tile critical path S -> P -> O): nearest-integer split with the
+          // 1.5 * 2^23 trick, a cubic on the fraction in [-0.5, 0.5] (relative error 7.5e-5), the
+          // exponent added as an integer; inputs clamped to -126 so the exponent cannot wrap.
+          // Masked blocks keep the SFU everywhere: -inf must give an exact zero.
+          const float x0 = fmaxf(__uint_as_float(static_cast<uint32_t>(y)), -126.f);
+          const float x1 = fmaxf(__uint_as_float(static_cast<uint32_t>(y >> 32)), -126.f);
+          const uint64_t xx = f4_pack(x0, x1);
+          const uint64_t rr = f4_add2(xx, f4_pack(12582912.f, 12582912.f));
+          const uint64_t xf = f4_add2(rr, f4_pack(-12582912.f, -12582912.f));
+          const uint64_t fr = f4_fma2(xf, f4_pack(-1.f, -1.f), xx);
+          uint64_t qq = f4_fma2(fr, f4_pack(0.05517116f, 0.05517116f), f4_pack(0.24261014f, 0.24261014f));
+          qq = f4_fma2(qq, fr, f4_pack(0.69326097f, 0.69326097f));
+          qq = f4_fma2(qq, fr, f4_pack(0.99992812f, 0.99992812f));
+          p0 = __uint_as_float(static_cast<uint32_t>(qq) + (static_cast<uint32_t>(rr) << 23));
+          p1 = __uint_as_float(static_cast<uint32_t>(qq >> 32) + (static_cast<uint32_t>(rr >> 32) << 23));
+        } else {
+          p0 = f4_ex2(__uint_as_float(static_cast<uint32_t>(y)));
+          p1 = f4_ex2(__uint_as_float(static_cast<uint32_t>(y >> 32)));
+        }
         sum4[(i >> 1) & 3] = f4_add2(sum4[(i >> 1) & 3], f4_pack(p0, p1));
         __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
         s[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
@@ -418,7 +440,12 @@ using namespace cb;
 
 int cb_attn_make_tmap_bshd(CUtensorMap* out, const void* base, int rows, int heads);
 
+static int g_fa4_poly_every = 0;
+
 extern "C" {
+
+// Every n-th pair of keys computes its exponential on the FMA pipe (0 = none, 2, 3 or 4).
+void cb_attn4_set_poly_every(int n) { g_fa4_poly_every = n; }
 
 // Same contract as cb_attn_fwd (fa_fwd.cu).
 int cb_attn_fwd4(const void* q, const void* k, const void* v, void* o, void* lse, int B, int Sq,
@@ -444,14 +471,26 @@ int cb_attn_fwd4(const void* q, const void* k, const void* v, void* o, void* lse
   p.causal = causal;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = static_cast<uint32_t*>(status);
-  cudaError_t e = cudaFuncSetAttribute(fa_fwd4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       F4_SMEM);
+  dim3 grid((Sq + 2 * F4_BM - 1) / (2 * F4_BM), Hq, B);
+  cudaError_t e = cudaSuccess;
+#define CB_FA4_LAUNCH(POLY)                                                                     \
+  do {                                                                                          \
+    e = cudaFuncSetAttribute(fa_fwd4_kernel<POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                             F4_SMEM);                                                          \
+    if (e == cudaSuccess)                                                                       \
+      fa_fwd4_kernel<POLY><<<grid, F4_THREADS, F4_SMEM, static_cast<cudaStream_t>(stream)>>>(p); \
+  } while (0)
+  switch (g_fa4_poly_every) {
+    case 2: CB_FA4_LAUNCH(2); break;
+    case 3: CB_FA4_LAUNCH(3); break;
+    case 4: CB_FA4_LAUNCH(4); break;
+    default: CB_FA4_LAUNCH(0); break;
+  }
+#undef CB_FA4_LAUNCH
   if (e != cudaSuccess) {
     set_last_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
     return -1;
   }
-  dim3 grid((Sq + 2 * F4_BM - 1) / (2 * F4_BM), Hq, B);
-  fa_fwd4_kernel<<<grid, F4_THREADS, F4_SMEM, static_cast<cudaStream_t>(stream)>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(std::string("attention launch: ") + cudaGetErrorString(e));

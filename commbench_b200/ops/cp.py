@@ -53,9 +53,9 @@ def flash_attention(q, k, v, causal: bool = True, q_offset: int = 0, kv_offset: 
     if impl is None:
         impl = get_config().attn_impl
     fn = {1: lib.cb_attn_fwd, 2: lib.cb_attn_fwd2, 3: lib.cb_attn_fwd3,
-          4: lib.cb_attn_fwd4}.get(impl)
+          4: lib.cb_attn_fwd4, 5: lib.cb_attn_fwd5}.get(impl)
     if fn is None:
-        raise CommError(f"unknown attention kernel {impl} (1 to 4)")
+        raise CommError(f"unknown attention kernel {impl} (1 to 5)")
     rc = fn(N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(out), N.ptr(lse), B, Sq, Skv, Hq, Hkv,
             q_offset, kv_offset, int(causal), C.c_float(sc), C.c_void_p(status_ptr),
             N.stream_ptr(stream))

@@ -17,15 +17,17 @@ from dataclasses import dataclass
 @dataclass
 class Config:
     # --- collectives -------------------------------------------------------
-    ar_oneshot_max_bytes: int = 512 * 1024      # at or below: one-shot pull all-reduce
-    ar_nvls_min_bytes: int = 512 * 1024         # at or above (with multicast bound): NVLS
+    ar_oneshot_max_bytes: int = 512 * 1024      # no multicast, at or below: one-shot pull all-reduce
+    ar_nvls_min_bytes: int = 16                 # multicast bound, at or above: NVLS
+    ar_nvls_max_bytes_two_ranks: int = 8 << 20  # with 2 ranks, NVLS only below this size
     coll_max_blocks: int = 64                   # CTAs per collective kernel (<= one wave)
+    coll_max_blocks_large: int = 148            # two-shot all-reduce of 16 MB and more
     ar_oneshot_grain_bytes: int = 8 * 1024      # message bytes per CTA, one-shot all-reduce
     ar_chunk_grain_bytes: int = 64 * 1024       # message bytes per CTA, two-shot / NVLS
     # --- fused GEMMs -------------------------------------------------------
     ag_gemm_comm_ctas: int = 8                  # CTAs reserved for pushing the local A shard
     gemm_rs_reduce_ctas: int = 0                # 0: reduction runs on all CTAs after their tiles
-    gemm_ar_oneshot_max_m: int = 256            # rows at or below: one-shot AR epilogue
+    gemm_ar_oneshot_max_m: int = 256            # 2 ranks only: rows at or below use the one-shot epilogue
     fused_poll_ns: int = 300                    # pause between polls of a peer-written flag
     # --- attention -------------------------------------------------------
     attn_impl: int = 4                          # flash-attention kernel, 1..5 (4: P kept in TMEM)

@@ -140,7 +140,9 @@ def main(argv=None) -> int:
                 ms = timed(fn)
                 ctx.check_status()
                 f = roofline.allreduce_bus_factor(world)
-                link = roofline.nvlink_bytes("all_reduce", nbytes, world, nvls=(algo == "nvls"))
+                resolved = algo if algo != "auto" else \
+                    coll.choose_all_reduce_algo(nbytes, world, ctx.has_multicast)
+                link = roofline.nvlink_bytes("all_reduce", nbytes, world, nvls=(resolved == "nvls"))
                 record("all_reduce", algo, (n,), "bf16", correct=correct, max_err=err, time_ms=ms,
                        baseline_ms=base_ms, busbw_gbs=f * nbytes / (ms * 1e-3) / 1e9,
                        baseline_busbw_gbs=(f * nbytes / (base_ms * 1e-3) / 1e9) if base_ms else None,
@@ -176,8 +178,15 @@ def main(argv=None) -> int:
             ):
                 a, b = ours(), theirs()
                 ctx.check_status()
-                tol = 5e-2 if op == "reduce_scatter" else 0.0
-                correct = all_ok(torch.allclose(a.float(), b.float(), atol=tol, rtol=tol))
+                if op == "reduce_scatter":
+                    # fp32 reference: NCCL's bf16 ring rounds after every hop, so two correct bf16
+                    # results can differ by several units in the last place.
+                    ref32 = base.reduce_scatter(x.float())
+                    err = (a.float() - ref32).abs().max().item()
+                    correct = all_ok(err <= 2e-2 * max(1.0, ref32.abs().max().item()))
+                    del ref32
+                else:
+                    correct = all_ok(torch.equal(a, b))
                 ms, bms = timed(ours), timed(theirs)
                 link = roofline.nvlink_bytes(link_op, size, world)
                 record(op, "auto", tuple(x.shape), "bf16", correct=correct, time_ms=ms,
@@ -344,6 +353,18 @@ def main(argv=None) -> int:
                correct=all_ok(err2 < 5e-2), max_err=err2, time_ms=ms2, baseline_ms=bms,
                tflops=fl / (ms2 * 1e-3) / 1e12,
                roofline_frac=roofline.fraction(roofline.roofline_ms(fl, link2, peaks, True), ms2))
+        if world > 1:
+            # Zig-zag sharding (rank r owns chunks r and 2W-1-r) balances the causal work; the
+            # rank-local random tensors stand for such shards here, so this entry is a timing
+            # only - its numerics are checked against a full-sequence reference in the tests.
+            ringz = RingAttention(ctx, B, Sl, Hq, Hkv, zigzag=True)
+            ringz.forward(q, k, v)
+            ctx.check_status()
+            ms3 = timed(lambda: ringz.forward(q, k, v))
+            record("ring_attention", "causal-zigzag", (B, S, Hq, Hkv, 128), "bf16", correct=True,
+                   time_ms=ms3, baseline_ms=bms, tflops=fl / (ms3 * 1e-3) / 1e12,
+                   roofline_frac=roofline.fraction(roofline.roofline_ms(fl, link2, peaks, True), ms3),
+                   note="timing only; numerics covered by the multi-rank tests")
 
     sync_all()
     if rank == 0:

@@ -27,7 +27,7 @@ class Config:
     # --- fused GEMMs -------------------------------------------------------
     ag_gemm_comm_ctas: int = 8                  # CTAs reserved for pushing the local A shard
     gemm_rs_reduce_ctas: int = 0                # 0: reduction runs on all CTAs after their tiles
-    gemm_ar_oneshot_max_m: int = 256            # 2 ranks only: rows at or below use the one-shot epilogue
+    gemm_ar_oneshot_max_m: int = 0              # rows at or below use the one-shot epilogue (0: never)
     fused_poll_ns: int = 300                    # pause between polls of a peer-written flag
     # --- attention -------------------------------------------------------
     attn_impl: int = 4                          # flash-attention kernel, 1..5 (4: P kept in TMEM)

@@ -316,10 +316,11 @@ class GemmAr(_FusedBase):
         fp8 = a0.dtype == torch.float8_e4m3fn
         cfg = get_config()
         if oneshot is None:
-            # One-shot sends every partial tile to every rank: W times the traffic.  Measured on
-            # 8 GPUs it loses at every M (116 us against 39 us at M=16); with 2 ranks it is a
-            # few microseconds ahead for decode-sized M.
-            oneshot = self.world <= 2 and M <= cfg.gemm_ar_oneshot_max_m
+            # One-shot sends every partial tile to every rank (W times the traffic) and has one
+            # polling CTA per tile.  Measured on 8 GPUs it loses at every M (116 us against 39 us
+            # at M=16); with 2 ranks it is at best a few microseconds ahead and sometimes far
+            # behind, so it is opt-in (gemm_ar_oneshot_max_m > 0).
+            oneshot = M <= cfg.gemm_ar_oneshot_max_m
         if bn is None:
             bn = self.pick_bn(M, Nn, self._ctas())
         par = self.calls & 1            # the kernel derives the same parity from its call counter

@@ -1,9 +1,9 @@
 """Roofline arithmetic of the harness: target time = the slower of (FLOPs / measured GEMM
 peak) and (bytes that must cross NVLink per GPU and direction / measured link bandwidth).
 
-Peaks come from ``MEASURED_PEAKS.json`` at the repository root when present (driver-written:
-copy bandwidth and cuBLAS bf16 throughput of this pool's B200s), otherwise from the stated
-fall-back; every fraction is labelled with its source.  Bandwidth formulas follow the
+Peaks come from ``MEASURED_PEAKS.json`` at the repository root when present (a STREAM-style
+copy bandwidth and the cuBLAS bf16 throughput measured on the machines the numbers are taken
+on), otherwise from the stated fall-back; every fraction is labelled with its source.  Bandwidth formulas follow the
 reference's own conventions: ring-equivalent all-reduce bytes ``2(W-1)/W * S``
 (datasets/example048_thunderkitten_all_reduce_easy/nv/empty_thunderkitten_all_reduce.cu:436,
 datasets/example022_torch_distributed_nccl_allreduce/empty_nccl_allreduce.py:107-115), all-gather /

@@ -4,11 +4,12 @@ device (CUDA events, max over ranks, warm-up first), and writes ``summary.json``
 with speed-up, bytes/FLOPs, fraction of roofline and verdict per entry.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node W --master-addr 127.0.0.1 \
-        -m commbench_b200.harness.run --suite allreduce,tp,moe,cp --out gpurun_out/harness_wW
+        -m commbench_b200.harness.run --suite allreduce,coll,p2p,tp,moe,cp --out results/w8
 
 Suites follow the five target configurations (all-reduce sweep; tensor-parallel fused GEMMs;
-MoE layer; context-parallel attention) plus ``coll`` for the other collectives.  One process per
-GPU; with W=1 the multi-rank entries degenerate to their local kernels.
+MoE layer; context-parallel attention) plus ``coll`` for the other collectives and ``p2p`` for
+the ping-pong / peer-copy / barrier probes.  One process per GPU; with W=1 the multi-rank
+entries degenerate to their local kernels.
 
 Replaces the reference's per-example ``build_and_run.py --compare`` loop (ref vs generated
 rebuilt and rerun back to back: datasets/example001_gpu_comm_single_process/nv/build_and_run.py:488-693)
@@ -28,7 +29,7 @@ import torch.distributed as dist
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--suite", default="allreduce,tp")
-    ap.add_argument("--out", default="gpurun_out/harness")
+    ap.add_argument("--out", default="results/harness")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--quick", action="store_true", help="coarser sweeps (every 4th size)")

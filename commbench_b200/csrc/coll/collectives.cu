@@ -358,8 +358,17 @@ __global__ void __launch_bounds__(kCollThreads)
     const unsigned long long off = nvec * c.rank;
     if (a.mc != nullptr) {
       uint4* mc = static_cast<uint4*>(a.mc) + off;
-      for (unsigned long long i = v0 + threadIdx.x; i < v1; i += blockDim.x)
-        mm_st_v4(mc + i, src[i]);
+      unsigned long long i = v0 + threadIdx.x;
+      // Four independent loads in flight per thread before the first multicast store.
+      for (; i + 3ull * blockDim.x < v1; i += 4ull * blockDim.x) {
+        const uint4 x0 = src[i], x1 = src[i + blockDim.x], x2 = src[i + 2ull * blockDim.x],
+                    x3 = src[i + 3ull * blockDim.x];
+        mm_st_v4(mc + i, x0);
+        mm_st_v4(mc + i + blockDim.x, x1);
+        mm_st_v4(mc + i + 2ull * blockDim.x, x2);
+        mm_st_v4(mc + i + 3ull * blockDim.x, x3);
+      }
+      for (; i < v1; i += blockDim.x) mm_st_v4(mc + i, src[i]);
     } else {
       for (unsigned long long i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
         const uint4 v = src[i];

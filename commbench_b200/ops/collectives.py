@@ -48,6 +48,12 @@ def pick_blocks(nbytes: int, max_blocks: int, grain: int = 1 << 16) -> int:
     return max(1, min(max_blocks, (nbytes + grain - 1) // grain))
 
 
+def _default_cap(cfg, nbytes: int) -> int:
+    """Grid cap of the bandwidth-bound collectives: one wave of 64 CTAs keeps the barrier cheap
+    for small and medium messages; from 16 MB per rank up every SM takes part."""
+    return cfg.coll_max_blocks_large if nbytes >= (16 << 20) else cfg.coll_max_blocks
+
+
 def choose_all_reduce_algo(nbytes: int, world: int, has_multicast: bool) -> str:
     """Measured on 8xB200: the in-switch reduction wins at every size from 4 KB (16 us against
     27-31 us one-shot) to 1 GB (839 GB/s bus against 342 two-shot, 725 NCCL).  With two ranks
@@ -162,7 +168,7 @@ def all_gather(ctx: CommContext, x: torch.Tensor, out: torch.Tensor | None = Non
     if out.numel() * out.element_size() != ctx.world * nbytes:
         raise CommError("all_gather: out has the wrong size")
     cfg = get_config()
-    blocks = pick_blocks(nbytes, max_blocks or cfg.coll_max_blocks)
+    blocks = pick_blocks(nbytes, max_blocks or _default_cap(cfg, nbytes))
     osym = ctx.find_block(out)
     if osym is not None and nbytes % 16 == 0:
         a = _fill_args(ctx.comm, osym[0], osym[1], x.data_ptr(), out.data_ptr(), nbytes)
@@ -191,7 +197,7 @@ def reduce_scatter(ctx: CommContext, x: torch.Tensor, out: torch.Tensor | None =
                           device=x.device)
     _check_local(out, "out")
     cfg = get_config()
-    blocks = pick_blocks(nbytes // ctx.world, max_blocks or cfg.coll_max_blocks)
+    blocks = pick_blocks(nbytes // ctx.world, max_blocks or _default_cap(cfg, nbytes // ctx.world))
     dt = _dtype_code(x)
     sym = ctx.find_block(x)
     want_nvls = ctx.has_multicast if use_nvls is None else (use_nvls and ctx.has_multicast)
@@ -216,7 +222,7 @@ def all_to_all(ctx: CommContext, x: torch.Tensor, out: torch.Tensor | None = Non
     out = torch.empty_like(x) if out is None else out
     _check_local(out, "out")
     cfg = get_config()
-    blocks = pick_blocks(nbytes, max_blocks or cfg.coll_max_blocks)
+    blocks = pick_blocks(nbytes, max_blocks or _default_cap(cfg, nbytes))
     sym = ctx.find_block(x)
     if sym is not None:
         a = _fill_args(ctx.comm, sym[0], 0, x.data_ptr(), out.data_ptr(), nbytes)
@@ -256,7 +262,7 @@ def all_to_all_4d(ctx: CommContext, x: torch.Tensor, to_heads: bool,
     _check_local(out, "out")
     nbytes = x.numel() * x.element_size()
     cfg = get_config()
-    blocks = pick_blocks(nbytes, max_blocks or cfg.coll_max_blocks)
+    blocks = pick_blocks(nbytes, max_blocks or _default_cap(cfg, nbytes))
     geo = (B, Sl, H, D, 1 if to_heads else 0)
     sym = ctx.find_block(x)
     if sym is not None:
@@ -275,7 +281,7 @@ def broadcast(ctx: CommContext, x: torch.Tensor, root: int = 0, max_blocks: int 
     _check_local(x, "x")
     nbytes = x.numel() * x.element_size()
     cfg = get_config()
-    blocks = pick_blocks(nbytes, max_blocks or cfg.coll_max_blocks)
+    blocks = pick_blocks(nbytes, max_blocks or _default_cap(cfg, nbytes))
     st = ctx.named("coll_stage", _pad16(nbytes))
     if ctx.has_multicast and x.data_ptr() % 16 == 0:
         a = _fill_args(ctx.comm, st.peer_ptrs, st.mc_ptr, x.data_ptr(), x.data_ptr(), nbytes,

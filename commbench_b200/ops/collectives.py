@@ -171,7 +171,10 @@ def all_gather(ctx: CommContext, x: torch.Tensor, out: torch.Tensor | None = Non
     blocks = pick_blocks(nbytes, max_blocks or _default_cap(cfg, nbytes))
     osym = ctx.find_block(out)
     if osym is not None and nbytes % 16 == 0:
-        a = _fill_args(ctx.comm, osym[0], osym[1], x.data_ptr(), out.data_ptr(), nbytes)
+        # One multicast store replaces W-1 peer stores; between two ranks it replaces one and
+        # was measured slower than plain stores for large shards.
+        mc = osym[1] if (ctx.world > 2 or nbytes < cfg.ar_nvls_max_bytes_two_ranks) else 0
+        a = _fill_args(ctx.comm, osym[0], mc, x.data_ptr(), out.data_ptr(), nbytes)
         _launch(ctx, N.OP_AG_PUSH, a, blocks, stream)
         return out
     xsym = ctx.find_block(x)
@@ -200,7 +203,12 @@ def reduce_scatter(ctx: CommContext, x: torch.Tensor, out: torch.Tensor | None =
     blocks = pick_blocks(nbytes // ctx.world, max_blocks or _default_cap(cfg, nbytes // ctx.world))
     dt = _dtype_code(x)
     sym = ctx.find_block(x)
-    want_nvls = ctx.has_multicast if use_nvls is None else (use_nvls and ctx.has_multicast)
+    if use_nvls is None:
+        # Between two ranks the switch reduction adds a hop and saves no link bytes: above a few
+        # MB plain peer loads are faster (measured), as for all-reduce.
+        want_nvls = ctx.has_multicast and (ctx.world > 2 or nbytes < cfg.ar_nvls_max_bytes_two_ranks)
+    else:
+        want_nvls = use_nvls and ctx.has_multicast
     if sym is not None:
         a = _fill_args(ctx.comm, sym[0], sym[1] if want_nvls else 0, x.data_ptr(), out.data_ptr(),
                        nbytes, dtype=dt)

@@ -1,0 +1,59 @@
+"""Every shipped generate/build/run task: well-formed description, skeleton and reference that
+build, and - for the tasks that need no GPU - a reference that passes its own check while the
+unfilled skeleton does not."""
+import json
+import os
+import shutil
+
+import pytest
+
+from commbench_b200.harness import compile_run as CR
+
+TASKS = os.path.join(os.path.dirname(CR.__file__), "tasks")
+ALL = sorted(d for d in os.listdir(TASKS) if os.path.exists(os.path.join(TASKS, d, "task.json")))
+CPU = [t for t in ALL if not CR.load_task(os.path.join(TASKS, t))["needs_gpu"]]
+FAMILIES = {"A", "B", "C", "D", "E", "F", "G", "H", "I"}
+
+
+def test_task_set_covers_several_families():
+    fams = {CR.load_task(os.path.join(TASKS, t)).get("family") for t in ALL}
+    assert len(ALL) >= 10 and {"A", "B", "C", "G"} <= fams and fams <= FAMILIES | {None}
+
+
+@pytest.mark.parametrize("task", ALL)
+def test_task_is_well_formed(task):
+    folder = os.path.join(TASKS, task)
+    with open(os.path.join(folder, "task.json")) as f:
+        spec = json.load(f)
+    assert spec["name"] == task and len(spec["description"]) > 80
+    assert spec["launcher"] in ("python", "torchrun", "nvcc") and spec["world"] >= 1
+    assert spec["direction"] in ("lower", "higher") and spec["primary_metric"]
+    empty, ref = CR.find_empty_file(folder), CR.find_ref_file(folder)
+    assert empty and ref and os.path.splitext(empty)[1] == os.path.splitext(ref)[1]
+    assert os.path.basename(empty) == "empty_" + os.path.basename(ref)[len("ref_"):]
+    text = open(empty).read()
+    assert "TODO" in text                                  # the skeleton says what to fill in
+    assert (spec["launcher"] == "nvcc") == ref.endswith(".cu")
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("task", ALL)
+def test_skeleton_and_reference_build(task, tmp_path):
+    folder = os.path.join(TASKS, task)
+    for src in (CR.find_ref_file(folder), CR.find_empty_file(folder)):
+        r = CR.compile_and_run(folder, src, build_only=True, work_dir=str(tmp_path))
+        assert r.compile_success, r.compile_output[-2000:]
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("task", CPU)
+def test_cpu_task_reference_passes_and_skeleton_does_not(task, tmp_path):
+    folder = os.path.join(TASKS, task)
+    r = CR.compile_and_run(folder, CR.find_ref_file(folder), work_dir=str(tmp_path))
+    assert CR.analyze_result(r) == (True, "program reported PASS"), r.output[-2000:]
+    rows = (r.result_json or {}).get("metrics")
+    spec = CR.load_task(folder)
+    assert rows and all(spec["primary_metric"] in row for row in rows)
+    skel = CR.compile_and_run(folder, CR.find_empty_file(folder), work_dir=str(tmp_path))
+    assert not CR.analyze_result(skel)[0]
+    shutil.rmtree(os.path.join(folder, "__pycache__"), ignore_errors=True)

@@ -51,7 +51,33 @@ class ResultStore:
             f.write(json.dumps(rec) + "\n")
 
     def records(self) -> list[dict]:
-        return list(self.done.values())
+        """Measurements only (suite markers are book-keeping)."""
+        return [r for r in self.done.values() if not str(r.get("op", "")).startswith("_")]
+
+
+class SuiteLedger:
+    """Suite-level resume for a multi-rank sweep.
+
+    A suite is collective code: either every rank runs it or none does.  Each rank appends a
+    marker record when it has finished a suite; on a resumed run a suite is skipped only when
+    EVERY rank holds its marker (``agree`` reduces a bool with AND over the ranks), so ranks whose
+    files diverged after an interrupted run still take the same branch.  The marker key covers
+    the arguments that change what a suite measures."""
+
+    def __init__(self, store: ResultStore, world: int, params: dict, agree=None, enabled: bool = True):
+        self.store, self.world, self.enabled = store, world, enabled
+        self.params = json.dumps(params, sort_keys=True)
+        self.agree = agree or (lambda flag: flag)
+
+    def _key(self, suite: str) -> str:
+        return config_key("_suite", suite, {"params": self.params}, "-", self.world)
+
+    def done(self, suite: str) -> bool:
+        mine = self.enabled and self.store.has(self._key(suite))
+        return bool(self.agree(bool(mine)))
+
+    def mark(self, suite: str):
+        self.store.add({"key": self._key(suite), "op": "_suite", "variant": suite, "world": self.world})
 
 
 def finish_record(rec: dict) -> dict:

@@ -37,6 +37,8 @@ def main(argv=None) -> int:
                     help="also time small all-reduces replayed from CUDA graphs (ours and NCCL)")
     ap.add_argument("--scale", type=float, default=1.0,
                     help="shrink the MoE / attention shapes (1.0 = the target configurations)")
+    ap.add_argument("--resume", action="store_true",
+                    help="skip the suites that every rank finished in an earlier run into --out")
     args = ap.parse_args(argv)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -99,6 +101,13 @@ def main(argv=None) -> int:
                               for k, v in rec.items() if k != "key"}), flush=True)
 
     suites = [s.strip() for s in args.suite.split(",") if s.strip()]
+    ledger = report.SuiteLedger(store, world, {"quick": args.quick, "graphs": args.graphs,
+                                               "scale": args.scale, "iters": args.iters},
+                                agree=all_ok, enabled=args.resume)
+    todo = [s for s in suites if not ledger.done(s)]
+    if rank == 0 and len(todo) != len(suites):
+        print(json.dumps({"resumed": True, "skipped": [s for s in suites if s not in todo]}), flush=True)
+    all_suites, suites = suites, todo
 
     # ------------------------------------------------------------- all-reduce sweep
     if "allreduce" in suites:
@@ -161,6 +170,7 @@ def main(argv=None) -> int:
                            time_ms=gms, baseline_ms=gbase, busbw_gbs=f * nbytes / (gms * 1e-3) / 1e9,
                            roofline_frac=roofline.fraction(roofline.roofline_ms(0, link, peaks), gms),
                            roofline_note=f"of {peaks.source}")
+        ledger.mark("allreduce")
 
     # ----------------------------------------------------------- other collectives
     if "coll" in suites and world > 1:
@@ -208,6 +218,7 @@ def main(argv=None) -> int:
                 record(op, variant, tuple(x.shape), "bf16", correct=correct, time_ms=ms,
                        baseline_ms=bms, busbw_gbs=link / (ms * 1e-3) / 1e9,
                        roofline_frac=roofline.fraction(roofline.roofline_ms(0, link, peaks), ms))
+        ledger.mark("coll")
 
     # ------------------------------------------------- point-to-point and barrier probes
     if "p2p" in suites and world > 1:
@@ -233,6 +244,7 @@ def main(argv=None) -> int:
                 record("p2p_copy", mode, (mb << 20,), "u8", correct=True, time_ms=ms, baseline_ms=None,
                        busbw_gbs=t.item(),
                        roofline_frac=t.item() / peaks.nvlink_gbs)
+        ledger.mark("p2p")
 
     # ------------------------------------------------- tensor-parallel fused GEMMs
     if "tp" in suites:
@@ -300,6 +312,7 @@ def main(argv=None) -> int:
                 record("gemm_ar", variant[0], (Md, Nd, Kd), "bf16", correct=all_ok(err < 2e-2),
                        max_err=err, time_ms=ms, baseline_ms=bms, tflops=fl / (ms * 1e-3) / 1e12,
                        roofline_frac=roofline.fraction(roofline.roofline_ms(fl, link, peaks), ms))
+        ledger.mark("tp")
 
     # ----------------------------------------------------------------- MoE layer
     if "moe" in suites:
@@ -330,6 +343,7 @@ def main(argv=None) -> int:
         record("moe_layer", "fp8-dispatch", (T, H, I, E, K), "bf16", correct=all_ok(err < 6e-2),
                max_err=err, time_ms=ms, baseline_ms=bms, tflops=fl / (ms * 1e-3) / 1e12,
                roofline_frac=roofline.fraction(roofline.roofline_ms(fl, link, peaks, True), ms))
+        ledger.mark("moe")
 
     # ------------------------------------------------------- context-parallel attention
     if "cp" in suites:
@@ -381,11 +395,12 @@ def main(argv=None) -> int:
                    time_ms=ms3, baseline_ms=bms, tflops=fl / (ms3 * 1e-3) / 1e12,
                    roofline_frac=roofline.fraction(roofline.roofline_ms(fl, link2, peaks, True), ms3),
                    note="timing only; numerics covered by the multi-rank tests")
+        ledger.mark("cp")
 
     sync_all()
     if rank == 0:
         s = report.write_summary(store.records(), args.out,
-                                 meta={"world": world, "suites": suites, "peaks": peaks.__dict__,
+                                 meta={"world": world, "suites": all_suites, "peaks": peaks.__dict__,
                                        "symmetric_memory": {"mode": ctx.mode,
                                                             "multicast": ctx.has_multicast}})
         print(json.dumps({"summary": os.path.join(args.out, "summary.json"),

@@ -36,6 +36,7 @@ int main() {
     CK(cudaFree(src));
     CK(cudaFree(dst));
   }
+  ok = ok && gbs.size() == sizeof(sizes) / sizeof(sizes[0]);  // nothing measured is not a pass
   printf("{\"Correctness\": \"%s\", \"data_size_unit\": \"MB\", \"latency_unit\": \"us\", "
          "\"throughput_unit\": \"GB/s\", \"metrics\": [", ok ? "PASS" : "FAIL");
   for (size_t i = 0; i < gbs.size(); ++i)

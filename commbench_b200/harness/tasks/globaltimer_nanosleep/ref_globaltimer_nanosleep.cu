@@ -59,6 +59,7 @@ int main() {
   const unsigned requests[] = {100, 1000, 10000, 100000, 1000000};
   unsigned long long* d = nullptr;
   CK(cudaMalloc(&d, 4 * sizeof(unsigned long long)));
+  CK(cudaMemset(d, 0, 4 * sizeof(unsigned long long)));
   bool ok = true;
   unsigned long long h[4] = {0, 0, 0, 0};
   resolution_kernel<<<1, 32>>>(d);

@@ -1,7 +1,7 @@
 """One-sided write and read plus two-sided send/recv between two reliable-connected queue pairs
 of one transport context (loopback device).  Prints one JSON object.
 
-Same exercise as the reference's datasets/example002_rdma_loopback/empty_rdma_loopback.cpp:142-390
+Same exercise as the reference's datasets/example002_rdma_loopback/ib/empty_rdma_loopback.cpp:142-390
 (endpoint set-up, write / read / send / recv, completion polling with a time limit), on the
 package's verbs-style transport instead of raw libibverbs.
 """

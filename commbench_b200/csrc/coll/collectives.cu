@@ -420,23 +420,44 @@ __global__ void __launch_bounds__(kCollThreads)
       }
       for (; i < s1; i += blockDim.x) out[i] = Vec16<DT>::mm_reduce(mc + i);
     } else {
-      for (unsigned long long i = s0 + threadIdx.x; i < s1; i += blockDim.x) {
+      // At least eight 16-byte loads in flight per thread: U vectors x W ranks per iteration.
+      constexpr int U = (W >= 8) ? 1 : 8 / W;
+      auto reduce_one = [&](const uint4(&raw)[W]) {
         float acc[Vec16<DT>::N];
-        uint4 raw[W];
 #pragma unroll
-        for (int p = 0; p < W; ++p) {
-          const int src = (c.rank + p) % W;
-          raw[p] = ld_sys_v4(static_cast<const uint4*>(a.sym[src]) + c0 + i);
-        }
-#pragma unroll
-        for (int r = 0; r < W; ++r) {
+        for (int r = 0; r < W; ++r) {  // always summed in rank order, so every rank rounds alike
           const int p = (r - c.rank + W) % W;
           float f[Vec16<DT>::N];
           Vec16<DT>::unpack(raw[p], f);
 #pragma unroll
           for (int k = 0; k < Vec16<DT>::N; ++k) acc[k] = (r == 0) ? f[k] : acc[k] + f[k];
         }
-        out[i] = Vec16<DT>::pack(acc);
+        return Vec16<DT>::pack(acc);
+      };
+      unsigned long long i = s0 + threadIdx.x;
+      for (; i + static_cast<unsigned long long>(U - 1) * blockDim.x < s1;
+           i += static_cast<unsigned long long>(U) * blockDim.x) {
+        uint4 raw[U][W];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+          for (int p = 0; p < W; ++p) {
+            const int src = (c.rank + p) % W;
+            raw[u][p] = ld_sys_v4(static_cast<const uint4*>(a.sym[src]) + c0 + i +
+                                  static_cast<unsigned long long>(u) * blockDim.x);
+          }
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          out[i + static_cast<unsigned long long>(u) * blockDim.x] = reduce_one(raw[u]);
+      }
+      for (; i < s1; i += blockDim.x) {
+        uint4 raw[W];
+#pragma unroll
+        for (int p = 0; p < W; ++p) {
+          const int src = (c.rank + p) % W;
+          raw[p] = ld_sys_v4(static_cast<const uint4*>(a.sym[src]) + c0 + i);
+        }
+        out[i] = reduce_one(raw);
       }
     }
     ok = rank_barrier_block(c, ch, e + 2, PH_BARRIER_END);

@@ -188,7 +188,15 @@ def main(argv=None) -> int:
             x_sym, ag_out = x_sym_full[:rows], ag_out_full[:rows]
             x_sym.copy_(x)
             sync_all()
-            for op, variant, ours, theirs, link_op, size in (
+            forced = ()
+            if ctx.has_multicast:
+                forced = (
+                    ("reduce_scatter", "symmetric-in-nvls", lambda: coll.reduce_scatter(ctx, x_sym, use_nvls=True),
+                     lambda: base.reduce_scatter(x), "reduce_scatter", nbytes),
+                    ("reduce_scatter", "symmetric-in-plain", lambda: coll.reduce_scatter(ctx, x_sym, use_nvls=False),
+                     lambda: base.reduce_scatter(x), "reduce_scatter", nbytes),
+                )
+            for op, variant, ours, theirs, link_op, size in forced + (
                 ("all_gather", "symmetric-out", lambda: coll.all_gather(ctx, shard, out=ag_out),
                  lambda: base.all_gather(shard), "all_gather", nbytes),
                 ("all_gather", "staged", lambda: coll.all_gather(ctx, shard),

@@ -33,6 +33,7 @@ class Config:
     attn_impl: int = 4                          # flash-attention kernel, 1..5 (4: P kept in TMEM)
     # --- MoE ---------------------------------------------------------------
     moe_expert_alignment: int = 128             # rows per expert padded to a tile multiple
+    moe_fused_swiglu: bool = True               # silu(gate)*up in the up-projection's epilogue
     # --- runtime -----------------------------------------------------------
     heap_bytes: int = 1 << 30
     timeout_s: float = 2.0

@@ -347,6 +347,31 @@ __device__ __forceinline__ void gemm_signal(const P& p, GemmCtl<Cfg::STAGES>* ct
   }
 }
 
+// A policy may declare `static constexpr bool kGated = true`: every BN-wide accumulator tile then
+// holds BN/2 "gate" columns followed by BN/2 "up" columns of the same output columns (the
+// weight rows are interleaved that way by the caller), and the TMA-store epilogue writes
+// silu(gate) * up - BN/2 output columns per tile - instead of the raw accumulator, so the
+// activation never makes a round trip through HBM.
+template <class Policy>
+__host__ __device__ constexpr bool policy_gated() {
+  if constexpr (requires { Policy::kGated; }) {
+    return Policy::kGated;
+  } else {
+    return false;
+  }
+}
+
+// acc[i] <- silu(alpha * acc[i]) * (alpha * up[i]), fp32 in the accumulator's bit pattern.
+__device__ __forceinline__ void epi_gate_32(uint32_t (&acc)[32], const uint32_t (&up)[32],
+                                            float alpha) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const float gv = __uint_as_float(acc[i]) * alpha;
+    const float uv = __uint_as_float(up[i]) * alpha;
+    acc[i] = __float_as_uint(gv / (1.f + __expf(-gv)) * uv);
+  }
+}
+
 template <class Cfg, class Policy, class P>
 __device__ __forceinline__ void gemm_epilogue_tma(const P& p, const GemmShape& g,
                                                   uint8_t* epi_smem, GemmCtl<Cfg::STAGES>* ctl,
@@ -362,14 +387,28 @@ __device__ __forceinline__ void gemm_epilogue_tma(const P& p, const GemmShape& g
     Policy::tile_coord(p, tile, &m_blk, &n_blk);
     if (!mbar_wait(&ctl->tmem_full[acc], acc_phase, &ctl->abort_flag, status, 0x400 + acc)) return;
     tc_fence_after_sync();
+    constexpr bool kGated = policy_gated<Policy>();
+    constexpr int kBoxes = Cfg::BN / Cfg::EPI_COLS / (kGated ? 2 : 1);  // store boxes per tile
 #pragma unroll 1
-    for (int c = 0; c < Cfg::BN / Cfg::EPI_COLS; ++c) {
+    for (int c = 0; c < kBoxes; ++c) {
       const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * Cfg::BN + c * Cfg::EPI_COLS;
       uint32_t r0[32], r1[32];
-      tmem_ld_32x32(taddr, r0);
-      tmem_ld_32x32(taddr + 32u, r1);
-      tmem_wait_ld();
-      if (c == Cfg::BN / Cfg::EPI_COLS - 1) {
+      if constexpr (kGated) {
+        uint32_t up[32];
+        tmem_ld_32x32(taddr, r0);
+        tmem_ld_32x32(taddr + Cfg::BN / 2, up);
+        tmem_wait_ld();
+        epi_gate_32(r0, up, g.alpha);
+        tmem_ld_32x32(taddr + 32u, r1);
+        tmem_ld_32x32(taddr + Cfg::BN / 2 + 32u, up);
+        tmem_wait_ld();
+        epi_gate_32(r1, up, g.alpha);
+      } else {
+        tmem_ld_32x32(taddr, r0);
+        tmem_ld_32x32(taddr + 32u, r1);
+        tmem_wait_ld();
+      }
+      if (c == kBoxes - 1) {
         // Last read of this accumulator: hand it back to the MMA thread.
         tc_fence_before_sync();
         __syncwarp();
@@ -379,7 +418,7 @@ __device__ __forceinline__ void gemm_epilogue_tma(const P& p, const GemmShape& g
       if (lane == 0) bulk_wait_read<1>();
       __syncwarp();
       uint8_t* b = bufs + buf * Cfg::EPI_BUF_BYTES;
-      epi_write_row_swizzled(b, lane, r0, r1, g.alpha);
+      epi_write_row_swizzled(b, lane, r0, r1, kGated ? 1.0f : g.alpha);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {

@@ -1,6 +1,7 @@
 // Grouped (per-expert) tcgen05 GEMMs over the expert-major receive buffer.
 //
 //   up:    H1[rows, 2I] = A[rows, H] * W1[e][2I, H]^T          (TMA-store epilogue, local)
+//          or, gated: S[rows, I] = silu(A * Wgate^T) * (A * Wup^T) in the same epilogue
 //   down:  O[rows, H]   = S[rows, I] * W2[e][H, I]^T, each output row written straight
 //          into the combine buffer of the rank that owns the token (fused combine send)
 //
@@ -40,9 +41,14 @@ struct GroupedParams {
   uint32_t* status;
 };
 
-template <class Cfg, bool kDown>
+// kGatedUp (up projection only): the weight slab of every expert is stored with its rows
+// interleaved per column block - 128 gate rows, then the 128 up rows of the same outputs - and
+// the epilogue writes silu(gate) * up, [rows, N/2], so H1 never exists in memory.
+template <class Cfg, bool kDown, bool kGatedUp = false>
 struct GroupedPolicy {
   using P = GroupedParams;
+  static constexpr bool kGated = kGatedUp;
+  static_assert(!(kDown && kGatedUp), "the gated epilogue belongs to the up projection");
   __device__ static int num_tiles(const P& p) {
     int mb = *reinterpret_cast<const volatile int*>(p.n_mblocks);
     if (mb > p.g.num_m_blocks) mb = p.g.num_m_blocks;
@@ -66,7 +72,8 @@ struct GroupedPolicy {
   static constexpr bool kScatterRows = kDown;
   __device__ static void store_box(const P& p, int m_blk, int n_blk, int row, int col,
                                    const void* smem_box) {
-    tma_store_2d(&p.tm_c, smem_box, n_blk * Cfg::BN + col, m_blk * Cfg::BM + row);
+    tma_store_2d(&p.tm_c, smem_box, n_blk * (kGatedUp ? Cfg::BN / 2 : Cfg::BN) + col,
+                 m_blk * Cfg::BM + row);
   }
   __device__ static void direct_targets(const P&, int, int, DirectTargets* t) {
     t->n = 0;
@@ -84,11 +91,12 @@ struct GroupedPolicy {
   __device__ static void tile_done(const P&, int, int, int) {}
 };
 
-template <class Cfg, bool kDown>
+template <class Cfg, bool kDown, bool kGatedUp>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
     grouped_gemm_kernel(const __grid_constant__ GroupedParams p) {
   extern __shared__ uint8_t smem_raw[];
-  gemm_cta_main<Cfg, GroupedPolicy<Cfg, kDown>>(p, p.g, p.status, blockIdx.x, gridDim.x, smem_raw);
+  gemm_cta_main<Cfg, GroupedPolicy<Cfg, kDown, kGatedUp>>(p, p.g, p.status, blockIdx.x, gridDim.x,
+                                                          smem_raw);
   if constexpr (kDown) {
     // Every CTA releases its rows; the last one tells every owner that this expert rank
     // is done (the owners' combine reduction waits for W such words).
@@ -107,16 +115,16 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1)
   }
 }
 
-template <class Cfg, bool kDown>
+template <class Cfg, bool kDown, bool kGatedUp = false>
 static int launch_grouped(const GroupedParams& p, int ctas, cudaStream_t st) {
-  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<Cfg, kDown>,
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<Cfg, kDown, kGatedUp>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        Cfg::SMEM_BYTES);
   if (e != cudaSuccess) {
     set_last_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
     return -1;
   }
-  grouped_gemm_kernel<Cfg, kDown><<<ctas, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(p);
+  grouped_gemm_kernel<Cfg, kDown, kGatedUp><<<ctas, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_last_error(std::string("grouped gemm launch: ") + cudaGetErrorString(e));
@@ -136,9 +144,10 @@ struct CbGroupedDesc {
   int down;          // 0: up projection (C local), 1: down projection with combine scatter
   int rank, world;
   int ctas;
+  int gated;         // up only: b is gate/up interleaved per 256 rows, c = silu(gate) * up
   const void* a;     // [max_rows, K] bf16
   const void* b;     // [n_local_experts * N, K] bf16
-  void* c;           // [max_rows, N] bf16 (up only)
+  void* c;           // up only: [max_rows, N] bf16, or [max_rows, N / 2] when gated
   const void* mblk_expert;
   const void* n_mblocks;
   const void* recv_meta;
@@ -162,9 +171,14 @@ int cb_moe_grouped_gemm(const CbGroupedDesc* d, void* stream) {
   if (make_tmap_2d(&p.tm_b, d->b, TMAP_BF16, d->K, (unsigned long long)d->n_local_experts * d->N,
                    (unsigned long long)d->K * 2, Cfg::BK, Cfg::BN, true))
     return -1;
+  if (d->gated && d->down) {
+    set_last_error("grouped gemm: the gated epilogue belongs to the up projection");
+    return -1;
+  }
   if (!d->down) {
-    if (make_tmap_2d(&p.tm_c, d->c, TMAP_BF16, d->N, d->max_rows, (unsigned long long)d->N * 2,
-                     Cfg::EPI_COLS, 32, true))
+    const unsigned long long c_cols = d->gated ? d->N / 2 : d->N;
+    if (make_tmap_2d(&p.tm_c, d->c, TMAP_BF16, c_cols, d->max_rows, c_cols * 2, Cfg::EPI_COLS, 32,
+                     true))
       return -1;
   } else {
     p.tm_c = p.tm_a;
@@ -188,7 +202,9 @@ int cb_moe_grouped_gemm(const CbGroupedDesc* d, void* stream) {
   p.world = d->world;
   p.status = static_cast<uint32_t*>(d->status);
   int ctas = d->ctas > 0 ? d->ctas : 148;
-  return d->down ? launch_grouped<Cfg, true>(p, ctas, st) : launch_grouped<Cfg, false>(p, ctas, st);
+  if (d->down) return launch_grouped<Cfg, true>(p, ctas, st);
+  return d->gated ? launch_grouped<Cfg, false, true>(p, ctas, st)
+                  : launch_grouped<Cfg, false, false>(p, ctas, st);
 }
 
 }  // extern "C"

@@ -131,14 +131,15 @@ __global__ void __launch_bounds__(256)
   for (int r = blockIdx.y * warps + warp; r < padded; r += gridDim.y * warps) {
     const long long row = static_cast<long long>(base) + r;
     if (row >= a.max_rows) continue;
-    uint4* out = reinterpret_cast<uint4*>(a.a_out + row * a.H);
+    uint4* __restrict__ out = reinterpret_cast<uint4*>(a.a_out + row * a.H);
     if (r >= expect) {
       for (int v = lane; v < nvec; v += 32) out[v] = make_uint4(0, 0, 0, 0);
       if (lane == 0) a.recv_meta[row] = make_int2(-1, -1);
       continue;
     }
-    const uint2* q = reinterpret_cast<const uint2*>(a.recv_x + row * a.H);
-    const float* sc = a.recv_scale + row * groups;
+    const uint2* __restrict__ q = reinterpret_cast<const uint2*>(a.recv_x + row * a.H);
+    const float* __restrict__ sc = a.recv_scale + row * groups;
+#pragma unroll 4
     for (int v = lane; v < nvec; v += 32) {
       const uint2 raw = __ldcg(q + v);
       const float s = __ldcg(sc + v / 16);

@@ -120,23 +120,44 @@ __global__ void dispatch_layout_kernel(const int* __restrict__ topk_idx, int T, 
 }
 
 // -------------------------------------------------- deterministic slot assignment
-// One warp per expert scans all T*K selections in order: slot[i] = number of
-// earlier selections of the same expert.  Also yields counts[e].  The order is a
-// pure function of topk_idx, so repeated runs place every row identically.
-__global__ void moe_slot_kernel(const int* __restrict__ topk_idx, int n_pairs, int E,
-                                int* __restrict__ slot, int* __restrict__ counts) {
-  const int e = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (e >= E) return;
-  int running = 0;
-  for (int base = 0; base < n_pairs; base += 32) {
+// One CTA per expert: slot[i] = number of earlier selections of the same expert; also yields
+// counts[e].  The T*K selections are cut into one contiguous chunk per warp; a first pass
+// counts each chunk's hits, a prefix over the warps gives every chunk its starting slot, a
+// second pass (the list is cache resident) writes the slots.  The order is a pure function of
+// topk_idx, so repeated runs place every row identically.
+constexpr int kSlotWarps = 16;
+__global__ void __launch_bounds__(kSlotWarps * 32)
+    moe_slot_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, int* __restrict__ slot,
+                    int* __restrict__ counts) {
+  __shared__ int chunk_hits[kSlotWarps];
+  const int e = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per_warp = ((n_pairs + kSlotWarps - 1) / kSlotWarps + 31) / 32 * 32;
+  const int begin = min(warp * per_warp, n_pairs), end = min(begin + per_warp, n_pairs);
+  int hits = 0;
+#pragma unroll 4
+  for (int base = begin; base < end; base += 32) {
     const int i = base + lane;
-    const bool hit = i < n_pairs && topk_idx[i] == e;
+    hits += (i < end && topk_idx[i] == e) ? 1 : 0;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) hits += __shfl_xor_sync(0xffffffffu, hits, o);
+  if (lane == 0) chunk_hits[warp] = hits;
+  __syncthreads();
+  int running = 0;
+  for (int w = 0; w < warp; ++w) running += chunk_hits[w];
+  if (threadIdx.x == 0) {
+    int total = 0;
+    for (int w = 0; w < kSlotWarps; ++w) total += chunk_hits[w];
+    counts[e] = total;
+  }
+  for (int base = begin; base < end; base += 32) {
+    const int i = base + lane;
+    const bool hit = i < end && topk_idx[i] == e;
     const unsigned m = __ballot_sync(0xffffffffu, hit);
     if (hit) slot[i] = running + __popc(m & ((1u << lane) - 1u));
     running += __popc(m);
   }
-  if (lane == 0) counts[e] = running;
 }
 
 // ---------------------------------------------------------------------- plan
@@ -250,9 +271,7 @@ int cb_moe_dispatch_layout(const void* topk_idx, int T, int K, int R, int E, voi
 }
 
 int cb_moe_slots(const void* topk_idx, int n_pairs, int E, void* slot, void* counts, void* stream) {
-  const int threads = 256;
-  const int blocks = (E * 32 + threads - 1) / threads;
-  moe_slot_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+  moe_slot_kernel<<<E, kSlotWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const int*>(topk_idx), n_pairs, E, static_cast<int*>(slot),
       static_cast<int*>(counts));
   return cudaGetLastError() == cudaSuccess ? 0 : -1;

@@ -4,7 +4,8 @@ weighted combine reduction.
 
 Per call and rank the kernels are (all from ``csrc/moe``):
   router_topk, moe_slots, [count all-gather], moe_plan, moe_sort_pairs, dispatch_send,
-  recv_dequant, grouped_gemm(up), swiglu, grouped_gemm(down, scatter), combine_reduce.
+  recv_dequant, grouped_gemm(up; silu(gate) * up in its epilogue unless ``fused_swiglu`` is off,
+  then a separate swiglu kernel), grouped_gemm(down, scatter), combine_reduce.
 No host synchronisation happens between them: the receive side learns the row counts from
 the all-gathered count matrix, never from the CPU (the reference's DeepEP path spins on
 mapped host counters: datasets/example080_deepep_jit_dispatch_payload/nv/
@@ -57,6 +58,7 @@ class _GroupedDesc(C.Structure):
     _fields_ = [
         ("max_rows", C.c_int), ("N", C.c_int), ("K", C.c_int), ("n_local_experts", C.c_int),
         ("down", C.c_int), ("rank", C.c_int), ("world", C.c_int), ("ctas", C.c_int),
+        ("gated", C.c_int),
         ("a", C.c_void_p), ("b", C.c_void_p), ("c", C.c_void_p),
         ("mblk_expert", C.c_void_p), ("n_mblocks", C.c_void_p), ("recv_meta", C.c_void_p),
         ("combine_peer", _P8), ("done_peer", _P8), ("done_ctas", C.c_void_p),
@@ -90,6 +92,20 @@ def dispatch_layout(topk_idx: torch.Tensor, num_ranks: int, num_experts: int):
     return per_e, per_r, in_r
 
 
+def interleave_gate_up(w1: torch.Tensor, block: int = 128) -> torch.Tensor:
+    """[E, 2I, H] with rows (gate | up) -> the same rows ordered per output block:
+    gate rows j*block..(j+1)*block, then the up rows of the same outputs, for j = 0, 1, ...
+    One 2*block-row tile of the product then holds both halves of `block` outputs, which is what
+    the gated epilogue of the grouped GEMM combines into silu(gate) * up."""
+    E, two_i, H = w1.shape
+    I = two_i // 2
+    if I % block:
+        raise CommError(f"intermediate size must divide by {block}")
+    g = w1[:, :I].reshape(E, I // block, 1, block, H)
+    u = w1[:, I:].reshape(E, I // block, 1, block, H)
+    return torch.cat([g, u], dim=2).reshape(E, two_i, H).contiguous()
+
+
 class _RankState:
     """Buffers of one (virtual) rank."""
 
@@ -108,7 +124,8 @@ class _RankState:
         self.n_rows = torch.zeros(1, **i32)
         self.sorted_pair = torch.empty(L.T * L.K, **i32)
         self.a = torch.empty(L.max_rows, L.H, dtype=torch.bfloat16, device=dev)
-        self.h1 = torch.empty(L.max_rows, 2 * L.I, dtype=torch.bfloat16, device=dev)
+        self.h1 = None if L.fused_swiglu else \
+            torch.empty(L.max_rows, 2 * L.I, dtype=torch.bfloat16, device=dev)
         self.s = torch.empty(L.max_rows, L.I, dtype=torch.bfloat16, device=dev)
         self.done_ctas = torch.zeros(4, **i32)
         self.y = torch.empty(L.T, L.H, dtype=torch.bfloat16, device=dev)
@@ -116,14 +133,20 @@ class _RankState:
         # bf16 expert weights N(0, 0.02): gate|up stacked [El, 2I, H] and down [El, H, I]
         self.w1 = (torch.randn(L.El, 2 * L.I, L.H, device=dev, generator=g) * 0.02).bfloat16()
         self.w2 = (torch.randn(L.El, L.H, L.I, device=dev, generator=g) * 0.02).bfloat16()
+        # The gated up projection reads its own row order of the same weights (one more copy of w1).
+        self.w1_gated = interleave_gate_up(self.w1) if L.fused_swiglu else None
 
 
 class MoELayer:
     """Expert-parallel MoE feed-forward over `ctx` (real ranks or virtual ranks)."""
 
     def __init__(self, ctx, tokens: int, hidden: int, intermediate: int, num_experts: int,
-                 topk: int, capacity_factor: float = 2.0, seed: int = 0):
+                 topk: int, capacity_factor: float = 2.0, seed: int = 0,
+                 fused_swiglu: bool | None = None):
         self.ctx, self.lib = ctx, ctx.lib
+        from ..config import get_config
+
+        self.fused_swiglu = get_config().moe_fused_swiglu if fused_swiglu is None else fused_swiglu
         self.emu = isinstance(ctx, EmuContext)
         self.W = ctx.world
         self.T, self.H, self.I, self.E, self.K = tokens, hidden, intermediate, num_experts, topk
@@ -238,7 +261,9 @@ class MoELayer:
             ra.recv_expected, ra.recv_base = st.recv_expected.data_ptr(), st.recv_base.data_ptr()
             ra.H, ra.max_rows = H, self.max_rows
             ra.timeout_ns, ra.status = self.ctx.timeout_ns, self._status(st)
-            N.check(lib.cb_moe_recv_dequant(C.byref(ra), self.El, 4, sp), "cb_moe_recv_dequant")
+            # about two CTAs per SM: the kernel streams max_rows * H bytes in and twice that out
+            slices = max(4, -(-2 * self.sms // self.El))
+            N.check(lib.cb_moe_recv_dequant(C.byref(ra), self.El, slices, sp), "cb_moe_recv_dequant")
             self._local(self.arrived, st)[:self.El * 4].zero_()   # counters ready for the next call
             st.n_rows.copy_(st.n_mblocks * 128)
         self._mark("recv_dequant")
@@ -247,13 +272,18 @@ class MoELayer:
             d = _GroupedDesc()
             d.max_rows, d.N, d.K, d.n_local_experts = self.max_rows, 2 * I, H, self.El
             d.down, d.rank, d.world, d.ctas = 0, st.r, W, self.sms
-            d.a, d.b, d.c = st.a.data_ptr(), st.w1.data_ptr(), st.h1.data_ptr()
+            if self.fused_swiglu:
+                d.gated, d.a, d.b, d.c = 1, st.a.data_ptr(), st.w1_gated.data_ptr(), st.s.data_ptr()
+            else:
+                d.gated, d.a, d.b, d.c = 0, st.a.data_ptr(), st.w1.data_ptr(), st.h1.data_ptr()
             d.mblk_expert, d.n_mblocks = st.mblk_expert.data_ptr(), st.n_mblocks.data_ptr()
             d.status = self._status(st)
             N.check(lib.cb_moe_grouped_gemm(C.byref(d), sp), "grouped gemm (up)")
             self._mark("gemm_up")
-            N.check(lib.cb_moe_swiglu(N.ptr(st.h1), N.ptr(st.s), N.ptr(st.n_rows), I, sp), "swiglu")
-            self._mark("swiglu")
+            if not self.fused_swiglu:
+                N.check(lib.cb_moe_swiglu(N.ptr(st.h1), N.ptr(st.s), N.ptr(st.n_rows), I, sp),
+                        "swiglu")
+                self._mark("swiglu")
             d2 = _GroupedDesc()
             d2.max_rows, d2.N, d2.K, d2.n_local_experts = self.max_rows, H, I, self.El
             d2.down, d2.rank, d2.world, d2.ctas = 1, st.r, W, self.sms
@@ -278,7 +308,9 @@ class MoELayer:
         ys = [st.y for st in self.states]
         return ys if self.emu else ys[0]
 
-    launches_per_call = 11
+    @property
+    def launches_per_call(self) -> int:
+        return 10 if self.fused_swiglu else 11
 
 
 def expert_sort(topk_idx: torch.Tensor, num_experts: int):

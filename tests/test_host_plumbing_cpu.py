@@ -157,3 +157,26 @@ def test_launcher_kills_session_on_timeout(tmp_path):
     r = run_in_new_session([sys.executable, str(script)], timeout=1.0)
     assert r.timed_out
     assert r.seconds < 10
+
+
+def test_gate_up_interleave_puts_both_halves_of_an_output_block_in_one_tile():
+    """Row order the gated up-projection epilogue expects: per block of 128 outputs the gate
+    rows, then the up rows of the same outputs."""
+    from commbench_b200.ops.moe import interleave_gate_up
+
+    E, I, H = 3, 256, 16
+    w1 = torch.arange(E * 2 * I * H, dtype=torch.float32).reshape(E, 2 * I, H)
+    out = interleave_gate_up(w1)
+    assert out.shape == w1.shape and out.is_contiguous()
+    for e in range(E):
+        for j in range(I // 128):
+            tile = out[e, j * 256:(j + 1) * 256]
+            assert torch.equal(tile[:128], w1[e, j * 128:(j + 1) * 128])
+            assert torch.equal(tile[128:], w1[e, I + j * 128:I + (j + 1) * 128])
+    x = torch.randn(5, H)
+    h = x @ w1[1].t()
+    ref = torch.nn.functional.silu(h[:, :I]) * h[:, I:]
+    hg = (x @ out[1].t()).reshape(5, I // 128, 2, 128)
+    assert torch.allclose((torch.nn.functional.silu(hg[:, :, 0]) * hg[:, :, 1]).reshape(5, I), ref)
+    with pytest.raises(Exception):
+        interleave_gate_up(torch.zeros(1, 2 * 96, 8))

@@ -33,6 +33,8 @@ class CbComm(C.Structure):
         ("epoch", C.c_void_p),
         ("status", C.c_void_p),
         ("timeout_ns", C.c_uint64),
+        ("jitter_ns", C.c_uint32),
+        ("reserved", C.c_uint32),
     ]
 
 

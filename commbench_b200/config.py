@@ -38,6 +38,7 @@ class Config:
     heap_bytes: int = 1 << 30
     timeout_s: float = 2.0
     use_nvls: bool = True
+    nvtx: bool = False                          # NVTX range around every op (external profilers)
 
 
 _CONFIG: Config | None = None

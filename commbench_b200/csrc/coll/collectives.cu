@@ -91,7 +91,21 @@ __device__ __forceinline__ void for_each_chunk_slice(unsigned long long nvec,
 
 __device__ __forceinline__ uint32_t begin_epoch(const CbComm& c, uint32_t ch) {
   // Every thread reads the same word; no thread writes it before end_epoch's barrier.
-  return ld_volatile(c.epoch + ch);
+  const uint32_t e = ld_volatile(c.epoch + ch);
+  if (c.jitter_ns != 0u) {  // debug stress: a different, repeatable delay per (rank, CTA, call)
+    uint32_t h = (static_cast<uint32_t>(c.rank) * 0x9e3779b9u) ^ (blockIdx.x * 0x85ebca6bu) ^
+                 (e * 0xc2b2ae35u);
+    h ^= h >> 15;
+    h *= 0x2c1b3c6du;
+    h ^= h >> 12;
+    uint32_t left = h % c.jitter_ns;
+    while (left > 0u) {  // one __nanosleep is capped near a millisecond
+      const uint32_t step = left < 500000u ? left : 500000u;
+      __nanosleep(step);
+      left -= step;
+    }
+  }
+  return e;
 }
 __device__ __forceinline__ void end_epoch(const CbComm& c, uint32_t ch, uint32_t value) {
   __syncthreads();

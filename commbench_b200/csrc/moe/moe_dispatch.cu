@@ -50,9 +50,13 @@ __global__ void __launch_bounds__(256)
     const int token = pair / a.K;
     const long long row = static_cast<long long>(a.send_row_base[e]) + r;
     if (row >= a.max_rows) continue;  // plan kernel already reported the overflow
-    const uint4* src = reinterpret_cast<const uint4*>(a.x + static_cast<size_t>(token) * a.H);
-    uint2* dq = reinterpret_cast<uint2*>(a.recv_x[dst] + row * a.H);
-    float* ds = a.recv_scale[dst] + row * groups;
+    const uint4* __restrict__ src =
+        reinterpret_cast<const uint4*>(a.x + static_cast<size_t>(token) * a.H);
+    uint2* __restrict__ dq = reinterpret_cast<uint2*>(a.recv_x[dst] + row * a.H);
+    float* __restrict__ ds = a.recv_scale[dst] + row * groups;
+    // H is a multiple of 256, so every lane makes the same number of trips (the shuffles below
+    // need the whole warp); four rows of loads in flight per lane.
+#pragma unroll 4
     for (int v = lane; v < nvec; v += 32) {
       const uint4 raw = src[v];
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);

@@ -33,4 +33,9 @@ struct CbComm {
   uint32_t* epoch;      // [CB_PAD_CHANNELS] local device memory
   uint32_t* status;     // one word, host-mapped so the host can read it after a sync
   uint64_t timeout_ns;  // budget of every bounded wait
+  // Debug stress: when non-zero every CTA of a collective kernel sleeps a pseudo-random time
+  // below this many nanoseconds before it starts (a function of rank, CTA and call number), so
+  // ordering assumptions that only hold when all CTAs start together show up in the tests.
+  uint32_t jitter_ns;
+  uint32_t reserved;
 };

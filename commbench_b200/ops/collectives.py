@@ -85,8 +85,18 @@ def _fill_args(comm: N.CbComm, sym_ptrs, mc_ptr, inp_ptr, out_ptr, nbytes, *, co
     return a
 
 
+_OP_NAMES = ("all_reduce.oneshot", "all_reduce.twoshot", "all_reduce.nvls", "all_gather.pull",
+             "all_gather.push", "reduce_scatter", "all_to_all", "all_to_all_4d", "broadcast")
+
+
 def _launch(ctx, op: int, args: N.CollArgs, blocks: int, stream=None):
-    rc = ctx.lib.cb_coll_launch(op, C.byref(args), None, 0, blocks, N.stream_ptr(stream))
+    if get_config().nvtx:
+        from ..utils.tracing import nvtx_range
+
+        with nvtx_range(f"cb200.{_OP_NAMES[op]}[{args.nbytes}B x{blocks}]"):
+            rc = ctx.lib.cb_coll_launch(op, C.byref(args), None, 0, blocks, N.stream_ptr(stream))
+    else:
+        rc = ctx.lib.cb_coll_launch(op, C.byref(args), None, 0, blocks, N.stream_ptr(stream))
     if rc != 0:
         raise CommError(f"collective launch failed (rc={rc}): {N.last_error()}")
 

@@ -22,9 +22,11 @@ from ..config import get_config
 
 from .. import _native as N
 from ..runtime.context import CommContext, CommError, tensor_from_ptr
+from ..utils.tracing import traced
 from . import collectives as coll
 
 
+@traced("cb200.flash_attention")
 def flash_attention(q, k, v, causal: bool = True, q_offset: int = 0, kv_offset: int = 0,
                     scale: float | None = None, out=None, lse=None, status_ptr: int = 0,
                     stream=None, impl: int | None = None):
@@ -126,6 +128,7 @@ class RingAttention:
         a, b = zigzag_chunks(self.W, r)
         return [(0, h, a * h), (h, h, b * h)]
 
+    @traced("cb200.ring_attention")
     def forward(self, q, k, v, causal: bool = True):
         ctx, W = self.ctx, self.W
         main = torch.cuda.current_stream()
@@ -198,6 +201,7 @@ class RingAttention:
         return self.o_acc.to(torch.bfloat16), self.lse_acc
 
 
+@traced("cb200.ulysses_attention")
 def ulysses_attention(ctx: CommContext, q, k, v, causal: bool = True):
     """Sequence-sharded in, sequence-sharded out: all-to-all q/k/v to head-sharded
     full-sequence tensors, local attention, all-to-all back (4 exchanges, as in the

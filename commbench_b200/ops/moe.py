@@ -29,6 +29,7 @@ import torch
 
 from .. import _native as N
 from ..runtime.context import CommError, EmuContext
+from ..utils.tracing import traced
 from . import collectives as coll
 
 _P8 = C.c_void_p * N.MAX_RANKS
@@ -204,6 +205,7 @@ class MoELayer:
         return out
 
     # ------------------------------------------------------------------ forward
+    @traced("cb200.moe.forward")
     def forward(self, xs, topk_idx, topk_w):
         """xs [T, H] bf16, topk_idx [T, K] int32, topk_w [T, K] fp32 (lists in emulation).
         Returns y [T, H] bf16 (list in emulation)."""

@@ -25,6 +25,7 @@ import torch
 from .. import _native as N
 from ..config import get_config
 from ..runtime.context import CommContext, CommError, EmuContext
+from ..utils.tracing import traced
 
 _P8 = C.c_void_p * N.MAX_RANKS
 
@@ -161,6 +162,7 @@ class AgGemm(_FusedBase):
         d.timeout_ns = self.ctx.timeout_ns
         return d
 
+    @traced("cb200.ag_gemm")
     def __call__(self, a_local, b, out=None, alpha: float = 1.0, bn: int = 256,
                  comm_ctas: int | None = None, parts: int | None = None, use_mc: bool = True,
                  stream=None):
@@ -226,6 +228,7 @@ class GemmRs(_FusedBase):
         d.timeout_ns = self.ctx.timeout_ns
         return d
 
+    @traced("cb200.gemm_rs")
     def __call__(self, a, b, out=None, alpha: float = 1.0, bn: int = 256, stream=None):
         a0, b0 = (a[0], b[0]) if self.emu else (a, b)
         M, K = a0.shape
@@ -306,6 +309,7 @@ class GemmAr(_FusedBase):
                 return bn
         return 64
 
+    @traced("cb200.gemm_ar")
     def __call__(self, a, b, out=None, alpha: float = 1.0, bn: int | None = None,
                  oneshot: bool | None = None, stream=None):
         a0, b0 = (a[0], b[0]) if self.emu else (a, b)

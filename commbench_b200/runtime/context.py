@@ -98,6 +98,10 @@ class _ContextBase:
         c.epoch = epoch_ptr
         c.status = status_dev_ptr
         c.timeout_ns = self.timeout_ns
+        # Debug stress (CB200_DEBUG_JITTER_NS): pseudo-random start delay per CTA in the
+        # collective kernels; capped well below the wait budget.
+        c.jitter_ns = min(int(os.environ.get("CB200_DEBUG_JITTER_NS", "0") or 0),
+                          max(self.timeout_ns // 100, 0), 10_000_000)
         return c
 
 

@@ -167,3 +167,31 @@ def test_wait_times_out_and_reports_status(native_lib):
     outs = coll.emu_all_reduce(ctx2, xs)
     ctx2.check_status()
     assert torch.allclose(outs[0].float(), xs[0].float() + xs[1].float(), atol=2e-2)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_collectives_are_bit_stable_under_start_jitter(native_lib, world, monkeypatch):
+    """Debug stress: every CTA starts after its own pseudo-random delay (up to 200 us).  Results
+    must be bit-identical to the run without delays, call after call."""
+    from commbench_b200.ops import collectives as coll
+    from commbench_b200.runtime.context import EmuContext
+
+    xs = _inputs(world, (world * 4096 + world * 8,), torch.bfloat16, seed=11)
+    calm = EmuContext(world)
+    want_ar = coll.emu_all_reduce(calm, xs, algo="twoshot")[0].clone()
+    want_rs = [o.clone() for o in coll.emu_reduce_scatter(calm, xs)]
+    want_a2a = [o.clone() for o in coll.emu_all_to_all(calm, xs)]
+    calm.check_status()
+    monkeypatch.setenv("CB200_DEBUG_JITTER_NS", "200000")
+    ctx = EmuContext(world)
+    assert ctx.comms[0].jitter_ns == 200000
+    for _ in range(3):
+        for o in coll.emu_all_reduce(ctx, xs, algo="twoshot"):
+            assert torch.equal(o, want_ar)
+        for o, w in zip(coll.emu_reduce_scatter(ctx, xs), want_rs):
+            assert torch.equal(o, w)
+        for o, w in zip(coll.emu_all_to_all(ctx, xs), want_a2a):
+            assert torch.equal(o, w)
+        gathered = coll.emu_all_gather(ctx, xs, push=True)
+        assert torch.equal(gathered[world - 1], torch.cat(xs))
+        ctx.check_status()

@@ -57,3 +57,33 @@ def test_cpu_task_reference_passes_and_skeleton_does_not(task, tmp_path):
     skel = CR.compile_and_run(folder, CR.find_empty_file(folder), work_dir=str(tmp_path))
     assert not CR.analyze_result(skel)[0]
     shutil.rmtree(os.path.join(folder, "__pycache__"), ignore_errors=True)
+
+
+def test_skeleton_generator_handles_markers_and_errors():
+    from commbench_b200.harness import make_skeleton as MS
+
+    ref = ('"""Doc.\n\nReference counterpart: somewhere\n(more).\n"""\n'
+           "def f(x):\n    # --- solution: add one\n    #     (to x)\n    return x + 1\n    # --- end solution\n"
+           "\n\ndef g():\n    # --- solution\n    return 2\n    # --- end solution\n")
+    out = MS.skeleton_text(ref)
+    assert "somewhere" not in out and "(more)" not in out and out.startswith('"""Doc.\n"""')
+    assert "    # TODO: add one\n    #       (to x)\n    raise NotImplementedError\n" in out
+    assert "    # TODO: implement\n    raise NotImplementedError\n" in out and "return" not in out
+    cu = "bool w() {\n  // --- solution else: return false;: poll\n  return poll();\n  // --- end solution\n}\n"
+    assert MS.skeleton_text(cu) == "bool w() {\n  // TODO: poll\n  return false;\n}\n"
+    for bad in ("# --- end solution\n", "# --- solution: x\ncode\n",
+                "# --- solution: a\n# --- solution: b\n# --- end solution\n"):
+        with pytest.raises(ValueError):
+            MS.skeleton_text(bad)
+    assert MS.skeleton_path("/t/ref_x.py") == "/t/empty_x.py" and MS.has_markers(ref)
+
+
+@pytest.mark.parametrize("task", ALL)
+def test_marked_references_regenerate_their_committed_skeleton(task):
+    from commbench_b200.harness import make_skeleton as MS
+
+    ref = CR.find_ref_file(os.path.join(TASKS, task))
+    text = open(ref).read()
+    if not MS.has_markers(text):
+        pytest.skip("skeleton of this task is kept by hand")
+    assert open(MS.skeleton_path(ref)).read() == MS.skeleton_text(text)

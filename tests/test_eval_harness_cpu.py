@@ -239,3 +239,46 @@ def test_shipped_gloo_task_reference_passes_its_own_check():
     skel = CR.compile_and_run(folder, CR.find_empty_file(folder), work_dir="/tmp/cb_task_build")
     assert not CR.analyze_result(skel)[0]            # the unfilled skeleton must not pass
     shutil.rmtree("/tmp/cb_task_build", ignore_errors=True)
+
+
+def test_leaderboard_scoring_and_table(tmp_path):
+    from commbench_b200.harness import leaderboard as LB
+
+    def summ(task, model, pass_it, perf, base=None, cand=None, direction="lower"):
+        d = tmp_path / task / "results" / model
+        d.mkdir(parents=True)
+        detail = {"primary_metric": "latency_avg", "direction": direction, "baseline": base, "candidate": cand}
+        (d / "summary.json").write_text(json.dumps(
+            {"task": task, "model": model, "passed": pass_it is not None and perf in ("better", "on_par"),
+             "pass_iteration": pass_it, "performance": perf, "performance_detail": detail}))
+
+    summ("t1", "m-a", 1, "better", 100.0, 50.0)                   # 2x faster (lower is better)
+    summ("t2", "m-a", 2, "degraded", 10.0, 20.0, "lower")         # 0.5x
+    summ("t3", "m-a", None, None)
+    summ("t1", "m-b", 1, "on_par", 4.0, 4.0, "higher")
+    table = LB.score(LB.collect(str(tmp_path)))
+    a, b = table["m-a"], table["m-b"]
+    assert a["tasks"] == 3 and a["correct"] == 2 and abs(a["pass_rate"] - 2 / 3) < 1e-9
+    assert abs(a["pass_good_rate"] - 1 / 3) < 1e-9 and abs(a["gm_speedup"] - 1.0) < 1e-9
+    assert abs(a["pass_x_gm"] - 2 / 3) < 1e-9 and a["mean_rounds_to_pass"] == 1.5
+    assert b["pass_rate"] == 1.0 and b["gm_speedup"] == 1.0
+    md = LB.render_markdown(table)
+    assert md.splitlines()[2].startswith("| m-b |") and "| m-a | 3 | 67 % | 33 % | 1.00 | 0.67 | 1.5 |" in md
+
+
+@pytest.mark.timeout(600)
+def test_leaderboard_self_check_runs_references_as_candidates(tmp_path):
+    """Copies two quick tasks, evaluates each reference as the candidate through the whole
+    build / run / compare path and aggregates the result."""
+    from commbench_b200.harness import leaderboard as LB
+
+    for t in ("rdma_atomics", "rdma_memory_pool"):
+        shutil.copytree(os.path.join(TASKS, t), tmp_path / t, ignore=shutil.ignore_patterns("results", "build"))
+    rows = LB.run_all("reference", str(tmp_path), None, 1, self_check=True, log=lambda *_: None)
+    assert [r["task"] for r in rows] == ["rdma_atomics", "rdma_memory_pool"]
+    assert all(r["rounds"] == 1 and r["performance"] is not None for r in rows), rows
+    table = LB.score(LB.collect(str(tmp_path)))
+    assert table["reference"]["tasks"] == 2 and table["reference"]["correct"] == 2
+    assert 0.2 < table["reference"]["gm_speedup"] < 5.0           # the same program twice
+    assert LB.main(["--tasks-dir", str(tmp_path), "--out", str(tmp_path / "lb.md")]) == 0
+    assert (tmp_path / "lb.json").exists() and "reference" in (tmp_path / "lb.md").read_text()

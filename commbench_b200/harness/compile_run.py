@@ -31,7 +31,9 @@ SOURCE_EXTS = (".py", ".cu", ".cpp", ".cc", ".cxx")
 PKG_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 REPO_ROOT = os.path.dirname(PKG_ROOT)
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++20", "-O3", "-lineinfo",
-              "--expt-relaxed-constexpr"]
+              "--expt-relaxed-constexpr", "-Xptxas=-v,--warn-on-spills"]
+NVCC_DEBUG_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++20", "-O0", "-g", "-G",
+                    "--expt-relaxed-constexpr"]
 
 
 @dataclass
@@ -49,6 +51,7 @@ class CompileRunResult:
     result_json: dict | None = None
     metrics: dict = field(default_factory=dict)
     command: list[str] = field(default_factory=list)
+    ptxas: list = field(default_factory=list)      # per kernel: registers, spills, static smem
 
     def to_dict(self) -> dict:
         return asdict(self)
@@ -164,8 +167,48 @@ def build_command(spec: dict, source: str, binary: str | None) -> list[str]:
     raise ValueError(f"unknown launcher {launcher!r}")
 
 
-def compile_source(source: str, out_dir: str, timeout_s: float = 300.0) -> tuple[bool, int | None, str, str | None]:
-    """(ok, returncode, log, binary).  Python sources are byte-compiled as the syntax check."""
+def ptxas_report(log: str) -> list[dict]:
+    """Per kernel: registers, spill bytes and static shared memory out of a ``ptxas -v`` log."""
+    import re
+
+    out, cur = [], None
+    for line in log.splitlines():
+        m = re.search(r"Compiling entry function '([^']+)'", line)
+        if m:
+            cur = {"kernel": m.group(1), "registers": None, "spill_stores": 0, "spill_loads": 0,
+                   "smem_bytes": 0}
+            out.append(cur)
+            continue
+        if cur is None:
+            continue
+        m = re.search(r"(\d+) bytes spill stores, (\d+) bytes spill loads", line)
+        if m:
+            cur["spill_stores"], cur["spill_loads"] = int(m.group(1)), int(m.group(2))
+        m = re.search(r"Used (\d+) registers", line)
+        if m:
+            cur["registers"] = int(m.group(1))
+            s = re.search(r"(\d+) bytes smem", line)
+            cur["smem_bytes"] = int(s.group(1)) if s else 0
+    return out
+
+
+def _source_digest(source: str, flags: list[str]) -> str:
+    import hashlib
+
+    h = hashlib.sha256(" ".join(flags).encode())
+    with open(source, "rb") as f:
+        h.update(f.read())
+    return h.hexdigest()
+
+
+def compile_source(source: str, out_dir: str, timeout_s: float = 300.0,
+                   debug: bool = False) -> tuple[bool, int | None, str, str | None]:
+    """(ok, returncode, log, binary).  Python sources are byte-compiled as the syntax check.
+    CUDA / C++ sources are built with nvcc for sm_100a; the log carries the ``ptxas -v`` report
+    (registers, spills; ``debug`` builds ``-O0 -g -G`` instead).  A binary whose source text and
+    flags have not changed since it was built in ``out_dir`` is reused (the log is kept beside
+    it), like the reference's mtime binary cache
+    (datasets/example060_thunderkitten_all_reduce_hard/nv/build_and_run.py:227-242)."""
     ext = os.path.splitext(source)[1]
     if ext == ".py":
         r = run_in_new_session([sys.executable, "-m", "py_compile", source], timeout=60,
@@ -176,11 +219,25 @@ def compile_source(source: str, out_dir: str, timeout_s: float = 300.0) -> tuple
         return False, None, "nvcc not found", None
     os.makedirs(out_dir, exist_ok=True)
     binary = os.path.join(out_dir, os.path.splitext(os.path.basename(source))[0])
-    cmd = [nvcc] + NVCC_FLAGS + ["-I", os.path.join(PKG_ROOT, "csrc"), "-x", "cu", source, "-o", binary,
-                                 "-lcuda"]
+    flags = NVCC_DEBUG_FLAGS if debug else NVCC_FLAGS
+    digest, stamp = _source_digest(source, flags), binary + ".build.json"
+    if os.path.exists(binary) and os.path.exists(stamp):
+        try:
+            with open(stamp) as f:
+                old = json.load(f)
+            if old.get("digest") == digest:
+                return True, 0, old.get("log", "") + "\n[build cache hit]", binary
+        except (OSError, json.JSONDecodeError):
+            pass
+    cmd = [nvcc] + flags + ["-I", os.path.join(PKG_ROOT, "csrc"), "-x", "cu", source, "-o", binary,
+                            "-lcuda"]
     r = run_in_new_session(cmd, timeout=timeout_s, env=scrubbed_env())
     ok = r.returncode == 0 and os.path.exists(binary)
-    return ok, r.returncode, (r.stdout + r.stderr), binary if ok else None
+    log = r.stdout + r.stderr
+    if ok:
+        with open(stamp, "w") as f:
+            json.dump({"digest": digest, "log": log}, f)
+    return ok, r.returncode, log, binary if ok else None
 
 
 def compile_and_run(folder: str, source: str, timeout_s: float | None = None,
@@ -189,8 +246,9 @@ def compile_and_run(folder: str, source: str, timeout_s: float | None = None,
     res = CompileRunResult(source=source)
     work_dir = work_dir or os.path.join(folder, "build")
     t0 = time.time()
-    ok, rc, log, binary = compile_source(source, work_dir)
+    ok, rc, log, binary = compile_source(source, work_dir, debug=bool(spec.get("debug")))
     res.compile_success, res.compile_returncode, res.compile_output = ok, rc, log
+    res.ptxas = ptxas_report(log)
     if not ok or build_only:
         res.wall_s = time.time() - t0
         return res

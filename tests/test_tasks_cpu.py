@@ -87,3 +87,34 @@ def test_marked_references_regenerate_their_committed_skeleton(task):
     if not MS.has_markers(text):
         pytest.skip("skeleton of this task is kept by hand")
     assert open(MS.skeleton_path(ref)).read() == MS.skeleton_text(text)
+
+
+@pytest.mark.timeout(600)
+def test_cuda_build_reports_registers_and_is_cached(tmp_path):
+    folder = os.path.join(TASKS, "mbarrier_producer_consumer")
+    src = tmp_path / "ref_copy.cu"
+    shutil.copy(CR.find_ref_file(folder), src)
+    r1 = CR.compile_and_run(folder, str(src), build_only=True, work_dir=str(tmp_path / "b"))
+    assert r1.compile_success and "[build cache hit]" not in r1.compile_output
+    k = [p for p in r1.ptxas if "handoff_kernel" in p["kernel"]]
+    assert k and 8 <= k[0]["registers"] <= 255 and k[0]["spill_stores"] == 0 and k[0]["smem_bytes"] > 0
+    r2 = CR.compile_and_run(folder, str(src), build_only=True, work_dir=str(tmp_path / "b"))
+    assert r2.compile_success and "[build cache hit]" in r2.compile_output and r2.ptxas == r1.ptxas
+    src.write_text(src.read_text() + "\n// changed\n")
+    r3 = CR.compile_and_run(folder, str(src), build_only=True, work_dir=str(tmp_path / "b"))
+    assert r3.compile_success and "[build cache hit]" not in r3.compile_output
+    ok, _, log, _ = CR.compile_source(str(src), str(tmp_path / "dbg"), debug=True)
+    assert ok and "[build cache hit]" not in log
+
+
+def test_ptxas_report_parser():
+    log = ("ptxas info    : Compiling entry function '_Z1kPf' for 'sm_100a'\n"
+           "ptxas info    : Function properties for _Z1kPf\n"
+           "    16 bytes stack frame, 8 bytes spill stores, 12 bytes spill loads\n"
+           "ptxas info    : Used 40 registers, used 1 barriers, 4096 bytes smem\n"
+           "ptxas info    : Compiling entry function '_Z1jv' for 'sm_100a'\n"
+           "    0 bytes stack frame, 0 bytes spill stores, 0 bytes spill loads\n"
+           "ptxas info    : Used 12 registers, used 0 barriers\n")
+    assert CR.ptxas_report(log) == [
+        {"kernel": "_Z1kPf", "registers": 40, "spill_stores": 8, "spill_loads": 12, "smem_bytes": 4096},
+        {"kernel": "_Z1jv", "registers": 12, "spill_stores": 0, "spill_loads": 0, "smem_bytes": 0}]

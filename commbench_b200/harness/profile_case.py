@@ -4,6 +4,7 @@
     python -m commbench_b200.harness.profile_case gemm_fp8
     python -m commbench_b200.harness.profile_case attn   [--seq 8192 --heads 16]
     python -m commbench_b200.harness.profile_case quant
+    python -m commbench_b200.harness.profile_case moe    [--tokens 4096]   # per-stage event times
 
 Each case allocates inputs larger than the 126 MB L2 but well under a few GB, runs two warm-up
 launches and ``--launches`` measured ones (default 3), prints the CUDA-event time and exits.
@@ -35,7 +36,8 @@ def _time(fn, launches: int) -> float:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "gemm_fp8", "attn", "quant"])
+    ap.add_argument("case", choices=["gemm", "gemm_fp8", "attn", "quant", "moe"])
+    ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=4096)
@@ -80,6 +82,30 @@ def main(argv=None) -> int:
         nbytes = x.numel() * 3
         out.update(rows=32768, cols=7168, quant_ms=ms_q, dequant_ms=ms_d,
                    quant_gbs=nbytes / ms_q / 1e6, dequant_gbs=nbytes / ms_d / 1e6)
+    elif a.case == "moe":
+        # One rank's share of the 256-expert layer on one GPU (all traffic local): 4096 tokens,
+        # top-8 over the rank's 32 experts = 32,768 expert rows, with per-stage CUDA events.
+        from ..ops.moe import MoELayer, router_topk
+        from ..runtime.context import EmuContext
+
+        T, H, I, E, K = a.tokens, 7168, 2048, 32, 8
+        for fused in (False, True):
+            ctx = EmuContext(1)
+            layer = MoELayer(ctx, T, H, I, E, K, capacity_factor=1.5, fused_swiglu=fused)
+            gg = torch.Generator(device=dev).manual_seed(7)
+            x = torch.randn(T, H, device=dev, generator=gg).bfloat16()
+            idx, w = router_topk(torch.randn(T, E, device=dev, generator=gg), K)
+            for _ in range(3):
+                layer.forward([x], [idx], [w])
+            torch.cuda.synchronize()
+            layer.enable_stage_timing()
+            ms = _time(lambda: layer.forward([x], [idx], [w]), a.launches)
+            n = a.launches + 2
+            stages = {k: round(v / n, 3) for k, v in layer.stage_ms().items()}
+            ctx.check_status()
+            out["fused_swiglu" if fused else "separate_swiglu"] = {"ms": round(ms, 3), "stages_ms": stages}
+            del layer, ctx
+            torch.cuda.empty_cache()
     print(json.dumps(out))
     return 0
 

@@ -42,15 +42,20 @@ def skeleton_text(ref_text: str, drop_containing: tuple[str, ...] = ()) -> str:
                 raise ValueError(f"line {i + 1}: end marker without a solution marker")
             if line.strip().lstrip("/# ").startswith("Reference counterpart:"):
                 # the paragraph that says where the exercise comes from stays in the solution only
+                tok = next((t for t in ("//", "#") if line.strip().startswith(t)), None)
                 while i < len(lines) and lines[i].strip() not in ("", "//", "#") \
-                        and not lines[i].strip().startswith('"""'):
-                    i += 1
+                        and not lines[i].strip().startswith('"""') \
+                        and (tok is None or lines[i].strip().startswith(tok + " ")):
+                    i += 1                      # a comment paragraph ends where the comment ends
                 if out and out[-1].strip() in ("", "//", "#") and i < len(lines) \
                         and lines[i].strip() in ("", "//", "#"):
                     i += 1                      # do not leave two blank lines behind
                 elif out and out[-1].strip() == "" and i < len(lines) \
                         and lines[i].strip().startswith('"""'):
                     out.pop()                   # nor a blank line before the closing quotes
+                elif tok and out and out[-1].strip() == tok and \
+                        (i == len(lines) or not lines[i].strip().startswith(tok)):
+                    out.pop()                   # nor an empty comment line at the end of the block
                 continue
             if not any(d in line for d in drop_containing):
                 out.append(line)

@@ -42,6 +42,7 @@ namespace {
 class Verbs : public TransportBackend {
  public:
   ~Verbs() override {
+    for (ibv_ah* ah : ahs_) ibv_destroy_ah(ah);
     for (auto& kv : qps_) ibv_destroy_qp(kv.second);
     for (auto& kv : srqs_) ibv_destroy_srq(kv.second);
     for (auto& kv : cqs_) ibv_destroy_cq(kv.second);

@@ -315,3 +315,27 @@ def test_two_rank_allreduce_over_put_and_signal(ctx):
     lonely.start(np.ones(8, dtype=np.float32))
     with pytest.raises(T.TransportError, match="signal never arrived"):
         lonely.finish(timeout_s=0.3)                    # nobody answers: bounded wait, no hang
+
+
+def test_verbs_backend_type_checks_against_the_public_interface():
+    """No RDMA stack here: the libibverbs backend is at least compiled (syntax and types only)
+    against a declarations-only copy of the public interface it uses."""
+    import os
+    import shutil
+    import subprocess
+
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("no host compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    util = os.path.join(root, "commbench_b200", "csrc", "util")
+    r = subprocess.run([gxx, "-std=c++17", "-fsyntax-only", "-Wall", "-Werror",
+                        "-I", os.path.join(root, "tests", "stubs"), "-I", util,
+                        "-I", os.path.join(root, "commbench_b200", "csrc"),
+                        os.path.join(util, "transport_verbs.cc")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
+    # and without the header the file must fall back to the "not built" stub
+    r = subprocess.run([gxx, "-std=c++17", "-fsyntax-only", "-Wall", "-Werror", "-I", util,
+                        "-I", os.path.join(root, "commbench_b200", "csrc"),
+                        os.path.join(util, "transport_verbs.cc")], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]

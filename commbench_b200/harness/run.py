@@ -30,7 +30,7 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--suite", default="allreduce,tp")
     ap.add_argument("--out", default="results/harness")
-    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--quick", action="store_true", help="coarser sweeps (every 4th size)")
     ap.add_argument("--graphs", action="store_true",

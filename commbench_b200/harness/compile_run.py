@@ -330,8 +330,24 @@ def compare_save_results(folder: str, ref_source: str, gen_source: str, results_
         entry = registry.entry(spec["op"])
     v = V.compute_verdict(entry if entry is not None else "info_only", ref_m, gen_m)
     gen_ok, gen_why = analyze_result(gen)
+    units = {k: (gen.result_json or ref.result_json or {}).get(k)
+             for k in ("data_size_unit", "latency_unit", "throughput_unit")}
+
+    def side(r: CompileRunResult) -> dict:
+        regs = [p["registers"] for p in r.ptxas if p.get("registers") is not None]
+        return {"compile_success": r.compile_success, "run_success": r.run_success,
+                "timed_out": r.timed_out, "wall_s": round(r.wall_s, 3),
+                "max_registers": max(regs) if regs else None,
+                "spill_bytes": sum(p["spill_stores"] + p["spill_loads"] for p in r.ptxas)}
+
     summary = {
         "task": spec["name"],
+        "ref_source": os.path.basename(ref_source),
+        "generated_source": os.path.basename(gen_source),
+        **units,
+        "build_and_run": {"reference": side(ref), "generated": side(gen)},
+        "verdict_scheme": {"better_pct": V.BETTER_PCT, "on_par_lower_pct": V.ON_PAR_LOWER_PCT,
+                           "degraded_lower_pct": V.DEGRADED_LOWER_PCT},
         "correctness": {"reference": analyze_result(ref)[0], "generated": gen_ok, "reason": gen_why},
         "metrics_comparison": {k: {"reference": ref_m.get(k), "generated": gen_m.get(k)}
                                for k in sorted(set(ref_m) | set(gen_m))},

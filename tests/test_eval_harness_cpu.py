@@ -282,3 +282,21 @@ def test_leaderboard_self_check_runs_references_as_candidates(tmp_path):
     assert 0.2 < table["reference"]["gm_speedup"] < 5.0           # the same program twice
     assert LB.main(["--tasks-dir", str(tmp_path), "--out", str(tmp_path / "lb.md")]) == 0
     assert (tmp_path / "lb.json").exists() and "reference" in (tmp_path / "lb.md").read_text()
+
+
+@pytest.mark.timeout(300)
+def test_comparison_summary_has_the_documented_layout(tmp_path):
+    """A real reference-vs-candidate comparison writes exactly the keys of the shipped template."""
+    folder = os.path.join(TASKS, "rdma_memory_pool")
+    ref = CR.find_ref_file(folder)
+    s = CR.compare_save_results(folder, ref, ref, str(tmp_path / "cmp"))
+    with open(os.path.join(os.path.dirname(CR.__file__), "summary_template.json")) as f:
+        tmpl = json.load(f)
+    assert set(s) == set(tmpl)
+    assert set(s["build_and_run"]["generated"]) == set(tmpl["build_and_run"]["generated"])
+    assert set(s["performance_detail"]) >= {"primary_metric", "direction", "baseline", "candidate",
+                                            "improvement_pct"}
+    assert s["latency_unit"] == "us" and s["ref_source"] == "ref_rdma_memory_pool.py"
+    assert s["correctness"] == {"reference": True, "generated": True, "reason": "program reported PASS"}
+    with open(tmp_path / "cmp" / "summary.json") as f:
+        assert json.load(f)["task"] == "rdma_memory_pool"

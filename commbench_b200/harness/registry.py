@@ -59,8 +59,8 @@ OPS: dict = {
     "copy_widths": {**BW, "family": "utility", "examples": ["example075", "example077"]},
     "tma_stream": {**BW, "family": "utility", "examples": ["example094"]},
     "mbarrier": {**TIME, "family": "utility", "examples": ["example072"]},
-    "nanosleep": "info_only",
-    "gpu_attributes": "info_only",
+    "nanosleep": {"info_only": True, "family": "utility", "examples": ["example076"]},
+    "gpu_attributes": {"info_only": True, "family": "utility", "examples": ["example010"]},
     "rdma_transport": {**TIME, "family": "rdma",
                        "examples": ["example002", "example004", "example006", "example007",
                                     "example008", "example009", "example011", "example013",
@@ -73,8 +73,10 @@ OPS: dict = {
 def entry(op: str):
     """Registry entry of an op, or None when the op is unknown."""
     e = OPS.get(op)
-    if e is None or e == "info_only":
-        return e
+    if e is None:
+        return None
+    if e == "info_only" or (isinstance(e, dict) and e.get("info_only")):
+        return "info_only"
     return {"primary": e["primary"], "direction": e["direction"]}
 
 
@@ -84,3 +86,84 @@ def examples_covered() -> set[str]:
         if isinstance(e, dict):
             out.update(e["examples"])
     return out
+
+
+# Where each op lives in this package (what a user of the reference's example calls instead) and,
+# where one is shipped, the generate/build/run task that poses the same exercise.
+API: dict = {
+    "all_reduce": ("ops.collectives.all_reduce (one-shot / two-shot / NVLS by size)",
+                   "gloo_allreduce, oneshot_allreduce_virtual_ranks"),
+    "internode_all_reduce": ("ops.transport.PutSignalAllReduce", None),
+    "all_gather": ("ops.collectives.all_gather (pull / push / multimem)", None),
+    "reduce_scatter": ("ops.collectives.reduce_scatter (pull / multimem.ld_reduce)", None),
+    "all_to_all": ("ops.collectives.all_to_all, all_to_all_4d; ops.p2p.ulysses_all_to_all_nccl",
+                   "ulysses_all_to_all"),
+    "broadcast": ("ops.collectives.broadcast; ops.p2p.WeightBroadcaster", "weight_broadcast"),
+    "barrier": ("ops.collectives.barrier (flag matrix / multimem.red)", None),
+    "ag_gemm": ("ops.tp.AgGemm; parallel.tp.ColumnParallelLinear", None),
+    "gemm_rs": ("ops.tp.GemmRs; parallel.tp.RowParallelLinear", None),
+    "gemm_ar": ("ops.tp.GemmAr", None),
+    "tp_qknorm": ("ops.fused.TPQKNorm", None),
+    "gemm": ("ops.gemm.gemm, gemm_fp8_blockscaled", None),
+    "moe_layer": ("ops.moe.MoELayer; parallel.ep.ExpertParallelMoE; ops.p2p.all_gatherv / reduce_scatterv",
+                  "moe_agrs_dispatch"),
+    "moe_dispatch_layout": ("ops.moe.dispatch_layout, router_topk, expert_sort", "moe_dispatch_layout"),
+    "eplb_rebalance": ("ops.p2p.rearrange_expert_weights_inplace", "eplb_rebalance"),
+    "ring_attention": ("ops.cp.RingAttention; parallel.cp.ContextParallelAttention", None),
+    "ulysses_attention": ("ops.cp.ulysses_attention", None),
+    "flash_attention": ("ops.cp.flash_attention", None),
+    "p2p_copy": ("ops.util.peer_copy_bandwidth, memcpy_bandwidth, ipc_export / ipc_import", "d2d_copy_kernel"),
+    "p2p_pingpong": ("ops.util.pingpong_latency", None),
+    "put_signal": ("ops.shmem.put_signal", None),
+    "get": ("ops.shmem.wait_get", None),
+    "atomic_fetch_inc": ("ops.shmem.atomic_fetch_inc", "atomic_ticket_counter"),
+    "tile_produce_consume": ("ops.shmem.tile_put, tile_consume", None),
+    "pp_tensor_dict": ("ops.p2p.send_tensor_dict / recv_tensor_dict; parallel.pp.PipelineStage",
+                       "tensor_dict_handoff"),
+    "ipc_weight_handoff": ("ops.util.ipc_export / ipc_import", None),
+    "d2h_fifo": ("ops.util.D2HFifo", None),
+    "h2d_fifo": ("ops.util.H2DFifo", None),
+    "shm_broadcast": ("ops.util.ShmBroadcast", "shm_object_broadcast"),
+    "copy_widths": ("ops.util.copy_bandwidth", "d2d_copy_kernel"),
+    "tma_stream": ("ops.util.tma_stream_bandwidth", "tma_bulk_copy_ring"),
+    "mbarrier": ("ops.util.mbarrier_round_trip", "mbarrier_producer_consumer"),
+    "nanosleep": ("ops.util.nanosleep_probe", "globaltimer_nanosleep"),
+    "gpu_attributes": ("ops.util.device_attributes; harness.platform_detect", None),
+    "rdma_transport": ("ops.transport (Context, Endpoint, MemoryRegion, MemoryPool, exchange_metadata)", None),
+}
+
+# Finer than per op where one op stands for many examples.
+EXAMPLE_TASK: dict = {
+    "example002": "rdma_rc_write_read", "example009": "rdma_rc_write_read",
+    "example006": "rdma_tcp_exchange",
+    "example008": "rdma_srq_write_imm", "example011": "rdma_srq_write_imm", "example013": "rdma_srq_write_imm",
+    "example014": "rdma_inline_sgl", "example019": "rdma_inline_sgl",
+    "example015": "rdma_memory_pool", "example016": "rdma_ud_datagram",
+    "example024": "rdma_atomics", "example025": "rdma_atomics",
+    "example026": "rdma_cq_overflow_event", "example027": "rdma_memory_window",
+    "example022": "gloo_allreduce", "example105": "oneshot_allreduce_virtual_ranks",
+    "example109": "oneshot_allreduce_virtual_ranks", "example020": "ulysses_all_to_all",
+    "example058": "ulysses_all_to_all", "example087": "weight_broadcast", "example084": "moe_agrs_dispatch",
+    "example042": "moe_dispatch_layout", "example074": "d2d_copy_kernel", "example077": "d2d_copy_kernel",
+}
+EXAMPLE_API: dict = {
+    "example004": "ops.transport.Context.device_info", "example029": "ops.transport.Context.device_info",
+    "example028": "ops.transport.Context.clock_ns", "example007": "ops.transport (UC queue pairs, CUDA tensors as buffers)",
+    "example015": "ops.transport.MemoryPool", "example006": "ops.transport.exchange_metadata",
+}
+
+
+def migration_table() -> str:
+    """Markdown table: reference example -> op -> where it is in this package -> shipped task."""
+    rows = []
+    for op, e in OPS.items():
+        api, task = API.get(op, ("", None))
+        for ex in (e.get("examples", []) if isinstance(e, dict) else []):
+            rows.append((ex, op, EXAMPLE_API.get(ex, api), EXAMPLE_TASK.get(ex, task) or "-"))
+    lines = ["| reference example | op | in this package | shipped task |", "|---|---|---|---|"]
+    lines += [f"| {ex} | {op} | `{api}` | {task} |" for ex, op, api, task in sorted(rows)]
+    return "\n".join(lines) + "\n"
+
+
+if __name__ == "__main__":
+    print(migration_table(), end="")

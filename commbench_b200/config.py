@@ -26,13 +26,11 @@ class Config:
     ar_chunk_grain_bytes: int = 64 * 1024       # message bytes per CTA, two-shot / NVLS
     # --- fused GEMMs -------------------------------------------------------
     ag_gemm_comm_ctas: int = 8                  # CTAs reserved for pushing the local A shard
-    gemm_rs_reduce_ctas: int = 0                # 0: reduction runs on all CTAs after their tiles
     gemm_ar_oneshot_max_m: int = 0              # rows at or below use the one-shot epilogue (0: never)
     fused_poll_ns: int = 300                    # pause between polls of a peer-written flag
     # --- attention -------------------------------------------------------
     attn_impl: int = 4                          # flash-attention kernel, 1..5 (4: P kept in TMEM)
     # --- MoE ---------------------------------------------------------------
-    moe_expert_alignment: int = 128             # rows per expert padded to a tile multiple
     moe_fused_swiglu: bool = True               # silu(gate)*up in the up-projection's epilogue
     # --- runtime -----------------------------------------------------------
     heap_bytes: int = 1 << 30

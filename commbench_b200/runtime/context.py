@@ -75,13 +75,6 @@ class SymmBlock:
         return self.local[:nb].view(dtype).view(*shape)
 
 
-def _env_int(name: str, default: int) -> int:
-    try:
-        return int(os.environ.get(name, default))
-    except ValueError:
-        return default
-
-
 class _ContextBase:
     rank: int
     world: int
@@ -126,11 +119,13 @@ class CommContext(_ContextBase):
         self.group = group
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         torch.cuda.set_device(self.device)
-        self.timeout_ns = int((timeout_s if timeout_s is not None
-                               else float(os.environ.get("CB200_TIMEOUT_S", "2.0"))) * 1e9)
-        self.heap_bytes = heap_bytes or _env_int("CB200_HEAP_BYTES", 1 << 30)
-        if use_multicast is None:
-            use_multicast = os.environ.get("CB200_NVLS", "1") != "0"
+        from ..config import get_config
+
+        cfg = get_config()          # CB200_TIMEOUT_S, CB200_HEAP_BYTES, CB200_USE_NVLS
+        self.timeout_ns = int((timeout_s if timeout_s is not None else cfg.timeout_s) * 1e9)
+        self.heap_bytes = heap_bytes or int(cfg.heap_bytes)
+        if use_multicast is None:   # CB200_NVLS=0 is the older spelling of CB200_USE_NVLS=0
+            use_multicast = bool(cfg.use_nvls) and os.environ.get("CB200_NVLS", "1") != "0"
         self._ctrl = None
         if self.world > 1:
             # CPU control plane for object exchange (the NCCL group moves tensors only).

@@ -1,9 +1,11 @@
 """Prompts for the generate -> build -> run -> repair loop, and extraction of code from replies.
 
-Four prompt kinds: *completion* (fill in the skeleton of a task), *fix* (the last attempt failed
-to build / run / verify: show earlier attempts as capped diffs plus capped error text),
-*performance fix* (it works but the verdict against the reference is below par: show the
-comparison summary) and *explanation* (describe what a source file does).
+Prompt kinds: *completion* (fill in the skeleton of a task; a *detailed* variant adds the
+machine and hints), *fix* (the last attempt failed to build / run / verify: show earlier attempts
+as capped diffs plus capped error text), *performance fix* (it works but the verdict against the
+reference is below par: show the comparison summary), *optimisation* (make a working program
+faster, with or without its measured metrics) and *explanation* (describe what a source file
+does).
 
 Counterpart of the reference's ``prompt_llm/prompt.py``: completion prompt with C++/CUDA and
 Python variants (:167-247), code extraction from fenced or truncated replies (:104-164), fix
@@ -109,6 +111,47 @@ def generate_perf_fix_prompt_from_code(skeleton_path: str, current_code: str, su
             "barriers, peer stores instead of staged copies.\n\n"
             f"{_RULES_PYTHON if lang == 'python' else _RULES_NATIVE}\n\n"
             f"Current program:\n```{lang}\n{current_code}\n```\n")
+
+
+def generate_completion_prompt_detailed(skeleton_path: str, task_description: str | None = None,
+                                        hardware: dict | None = None, hints: list[str] | None = None) -> str:
+    """Completion prompt with the machine it will run on and optional hints spelled out
+    (the reference keeps such a variant beside the plain one: prompt_llm/prompt.py, "detailed")."""
+    hw = hardware or {"gpu": "NVIDIA B200 (sm_100a), 148 SMs, 180 GB HBM3e", "gpus_per_node": 8,
+                      "interconnect": "NVLink 5 through NVSwitch, 900 GB/s per direction per GPU, "
+                                      "in-switch reduction (multimem) available"}
+    lines = [generate_completion_prompt(skeleton_path, task_description).rstrip("\n"), "",
+             "Machine:"] + [f"- {k}: {v}" for k, v in hw.items()]
+    if hints:
+        lines += ["", "Hints:"] + [f"- {h}" for h in hints]
+    return "\n".join(lines) + "\n"
+
+
+def generate_optimization_prompt(source_path: str, goal: str = "lower latency at every size") -> str:
+    """Asks for a faster version of a working program without a measured comparison at hand."""
+    lang = language_of(source_path)
+    return (f"The {lang} program below works. Rewrite it for {goal} on one NVIDIA B200 node without changing "
+            "what it computes, checks or prints.\n\n"
+            f"{_RULES_PYTHON if lang == 'python' else _RULES_NATIVE}\n\n"
+            f"Program ({os.path.basename(source_path)}):\n```{lang}\n{_read(source_path)}\n```\n")
+
+
+def generate_performance_optimization_prompt(source_path: str, metrics: dict,
+                                             roofline: dict | None = None) -> str:
+    """Optimisation prompt that carries the program's own measured metrics and, when known, how far
+    they are from the machine's limits (fraction of link bandwidth or of the GEMM peak)."""
+    lang = language_of(source_path)
+    text = (f"The {lang} program below works. Its measured results:\n```json\n"
+            f"{_cap(json.dumps(metrics, indent=1), 3000, keep_tail=False)}\n```\n")
+    if roofline:
+        text += ("Against the machine's limits:\n```json\n"
+                 f"{_cap(json.dumps(roofline, indent=1), 1500, keep_tail=False)}\n```\n")
+    text += ("\nName the bottleneck these numbers point to (launch latency, synchronisation, link bandwidth, "
+             "memory bandwidth, tensor throughput), then rewrite the program to remove it without changing what "
+             "it computes, checks or prints.\n\n"
+             f"{_RULES_PYTHON if lang == 'python' else _RULES_NATIVE}\n\n"
+             f"Program ({os.path.basename(source_path)}):\n```{lang}\n{_read(source_path)}\n```\n")
+    return text
 
 
 def generate_explanation_prompt(source_path: str) -> str:

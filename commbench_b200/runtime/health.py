@@ -10,7 +10,10 @@ missing peer from being *launched against* in the first place:
 * ``Watchdog.check()`` - called between steps, before the next kernel launch - raises
   ``RankFailure`` naming the ranks whose counter stopped or whose process is gone;
 * ``rerendezvous()`` builds a fresh ``torch.distributed`` group (new store, ranks renumbered)
-  from the survivors, after which symmetric buffers are re-created on the new group.
+  from the survivors, after which symmetric buffers are re-created on the new group;
+* ``ElasticRunner`` packages the three into a step loop: a membership barrier on the board
+  before every step, re-rendezvous when somebody is missing, a hook for the caller to rebuild
+  what hangs on the group.
 
 The reference has per-wait device time-outs and host-side process containment but neither
 heart-beats nor recovery (DeepEP's ``timeout_while`` and ``gpu_barrier`` time-outs,
@@ -62,7 +65,8 @@ class HeartbeatBoard:
     def __init__(self, name: str, rank: int, world: int, interval_s: float = 0.05, create: bool | None = None):
         self.name, self.rank, self.world, self.interval = name, rank, world, interval_s
         self.path = os.path.join("/dev/shm", name)
-        size = _HEADER + world * _SLOT.size
+        self._steps_at = _HEADER + world * _SLOT.size          # one u64 "next step" word per rank
+        size = self._steps_at + world * 8
         if create is None:
             create = rank == 0
         if create:
@@ -117,9 +121,17 @@ class HeartbeatBoard:
             except FileNotFoundError:
                 pass
 
+    def announce_step(self, step: int):
+        """Publishes "this rank is about to run step ``step``" (see ``ElasticRunner``)."""
+        struct.pack_into("<Q", self.mm, self._steps_at + self.rank * 8, step + 1)
+
     # ------------------------------------------------------------------ peers
     def read(self, r: int) -> tuple[int, int, int, int]:
         return _SLOT.unpack_from(self.mm, _HEADER + r * _SLOT.size)
+
+    def step_of(self, r: int) -> int:
+        """The step rank ``r`` last announced, -1 before its first announcement."""
+        return struct.unpack_from("<Q", self.mm, self._steps_at + r * 8)[0] - 1
 
     def wait_all_present(self, timeout_s: float = 30.0):
         deadline = time.time() + timeout_s
@@ -138,12 +150,13 @@ class Watchdog:
         self.board, self.timeout = board, timeout_s
         now = time.monotonic()
         self._seen = {r: (board.read(r)[0], now) for r in range(board.world)}
+        self.ignored: set[int] = set()      # ranks already dealt with (left out of later answers)
 
     def dead_ranks(self) -> list[int]:
         now = time.monotonic()
         dead = []
         for r in range(self.board.world):
-            if r == self.board.rank:
+            if r == self.board.rank or r in self.ignored:
                 continue
             count, pid, state, _ = self.board.read(r)
             last_count, last_t = self._seen[r]
@@ -197,3 +210,93 @@ def rerendezvous(store_dir: str, old_rank: int, survivors: list[int], generation
     dist.init_process_group(backend, store=store, rank=new_rank, world_size=new_world,
                             timeout=datetime.timedelta(seconds=timeout_s))
     return new_rank, new_world
+
+
+class ElasticRunner:
+    """A step loop that survives ranks leaving between steps.
+
+    Before every step the members meet at a *membership barrier* on the heart-beat board: each
+    announces the step it is about to run and waits until every other member has announced the
+    same step - or has left, died or stopped beating.  Nobody therefore enters a collective with
+    a rank that is not coming; when somebody is missing, the survivors tear the process group
+    down, re-rendezvous under new rank numbers (``on_reconfigure(runner)`` lets the caller
+    rebuild what hangs on the group: symmetric buffers, sharded state) and run the step as the
+    smaller group.  The barrier costs a few shared-memory reads per step; nothing is in flight
+    on a GPU while it runs.
+
+        runner = ElasticRunner("job42", rank, world, "/tmp/job42/store").start()
+        runner.run(lambda step, r: train_step(step, r.rank, r.world), steps=1000)
+    """
+
+    def __init__(self, name: str, rank: int, world: int, store_dir: str, backend: str = "gloo",
+                 beat_s: float = 0.05, dead_after_s: float = 1.0, group_timeout_s: float = 30.0,
+                 on_reconfigure=None):
+        self.name, self.store_dir, self.backend = name, store_dir, backend
+        self.first_rank, self.first_world = rank, world        # numbering on the board never changes
+        self.rank, self.world = rank, world                    # numbering of the current group
+        self.members = list(range(world))                      # board ranks still in the job
+        self.generation = 0
+        self.beat_s, self.dead_after_s, self.group_timeout_s = beat_s, dead_after_s, group_timeout_s
+        self.on_reconfigure = on_reconfigure
+        self.board: HeartbeatBoard | None = None
+        self.watchdog: Watchdog | None = None
+        self.history: list[dict] = []                          # one entry per reconfiguration
+
+    def start(self) -> "ElasticRunner":
+        self.board = HeartbeatBoard(self.name, self.first_rank, self.first_world, self.beat_s)
+        self.board.wait_all_present()
+        self.watchdog = Watchdog(self.board, self.dead_after_s)
+        self.rank, self.world = rerendezvous(self.store_dir, self.first_rank, self.members, 0,
+                                             self.backend, self.group_timeout_s)
+        return self
+
+    def membership_barrier(self, step: int, timeout_s: float = 60.0) -> list[int]:
+        """Returns the members (board ranks) that will NOT take part in ``step``."""
+        self.board.announce_step(step)
+        deadline = time.monotonic() + timeout_s
+        while True:
+            dead = [r for r in self.watchdog.dead_ranks() if r in self.members]
+            waiting = [r for r in self.members
+                       if r != self.first_rank and r not in dead and self.board.step_of(r) < step]
+            if not waiting:
+                return dead
+            if time.monotonic() > deadline:
+                raise RankFailure(waiting, f"alive but never reached step {step}")
+            time.sleep(min(self.beat_s, 0.005))
+
+    def _reconfigure(self, dead: list[int], step: int):
+        self.members = [r for r in self.members if r not in dead]
+        self.watchdog.ignored.update(dead)
+        self.generation += 1
+        self.rank, self.world = rerendezvous(self.store_dir, self.first_rank, self.members,
+                                             self.generation, self.backend, self.group_timeout_s)
+        self.history.append({"step": step, "dead": list(dead), "world": self.world, "rank": self.rank})
+        if self.on_reconfigure is not None:
+            self.on_reconfigure(self)
+
+    LEAVE = "leave"
+
+    def run(self, step_fn, steps: int, first_step: int = 0):
+        """Calls ``step_fn(step, runner)`` for every step; returns the number of steps run.  A
+        ``step_fn`` that returns ``ElasticRunner.LEAVE`` has finished its last step: the rank
+        announces its departure and the loop ends (a rank may only go between steps)."""
+        for step in range(first_step, first_step + steps):
+            dead = self.membership_barrier(step)
+            if dead:
+                self._reconfigure(dead, step)
+            if step_fn(step, self) == self.LEAVE:
+                self.leave()
+                return step - first_step + 1
+        return steps
+
+    def leave(self, failed: bool = False):
+        """Leaves the job between steps (nothing in flight): the others see it at their next
+        membership barrier.  The process group is left as it is: the survivors abandon it."""
+        self.board.leave(failed=failed)
+
+    def close(self):
+        import torch.distributed as dist
+
+        if dist.is_initialized():
+            dist.destroy_process_group()
+        self.board.close(unlink=(self.first_rank == min(self.members)))

@@ -103,9 +103,47 @@ def gpu_leave(rank, world, scratch):
     os._exit(0)
 
 
+def cpu_runner(rank, world, scratch, silent_exit):
+    """Four gloo ranks run eight all-reduce steps under ``ElasticRunner``; rank 3 leaves before
+    step 3 and rank 1 before step 6 (announced, or by just exiting).  Every step's sum must be
+    the number of members that took part in it."""
+    import torch
+    import torch.distributed as dist
+
+    from commbench_b200.runtime import health as H
+
+    seen = []
+    runner = H.ElasticRunner(f"cb_runner_{os.path.basename(scratch)}", rank, world,
+                             os.path.join(scratch, "store"), beat_s=0.02, dead_after_s=0.5,
+                             on_reconfigure=lambda r: seen.append((r.generation, r.rank, r.world)))
+    runner.start()
+    sums = []
+
+    def step_fn(step, r):
+        x = torch.ones(8)
+        dist.all_reduce(x)
+        sums.append(int(x[0].item()))
+        if (rank == 3 and step == 2) or (rank == 1 and step == 5):     # last step of this rank
+            _report(scratch, rank, sums=sums, left_after=step)
+            if silent_exit:
+                os._exit(0)                    # no announcement at all: the beat just stops
+            return r.LEAVE
+
+    ran = runner.run(step_fn, steps=8)
+    if ran < 8:
+        os._exit(0)                            # left on purpose; the survivors keep the board
+    _report(scratch, rank, sums=sums, reconfigured=seen, history=runner.history,
+            members=runner.members, final=(runner.rank, runner.world))
+    runner.close()
+
+
 if __name__ == "__main__":
     case, rank, world, scratch = sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), sys.argv[4]
-    if case == "cpu_elastic":
+    if case == "cpu_runner":
+        cpu_runner(rank, world, scratch, silent_exit=False)
+    elif case == "cpu_runner_silent":
+        cpu_runner(rank, world, scratch, silent_exit=True)
+    elif case == "cpu_elastic":
         cpu_elastic(rank, world, scratch, silent_exit=False)
     elif case == "cpu_elastic_silent":
         cpu_elastic(rank, world, scratch, silent_exit=True)

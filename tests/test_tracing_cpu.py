@@ -69,3 +69,16 @@ def test_span_recorder_nests_and_exports_a_chrome_trace(tmp_path):
     merged = TR.merge_chrome_traces([p, p2], str(tmp_path / "all.json"))
     with open(merged) as f:
         assert {e["pid"] for e in json.load(f)["traceEvents"]} == {3, 4}
+
+
+def test_latency_stats_are_nearest_rank_percentiles():
+    from commbench_b200.utils.timing import latency_stats
+
+    s = latency_stats(range(1, 101))                  # 1 .. 100
+    assert (s["count"], s["min"], s["max"], s["avg"]) == (100, 1.0, 100.0, 50.5)
+    assert (s["p50"], s["p90"], s["p99"]) == (50.0, 90.0, 99.0)
+    one = latency_stats([7.5])
+    assert one["p50"] == one["p99"] == one["min"] == one["max"] == 7.5
+    few = latency_stats([3.0, 1.0, 2.0])
+    assert few["p50"] == 2.0 and few["p99"] == 3.0 and few["p90"] == 3.0
+    assert latency_stats([])["count"] == 0 and latency_stats([])["p99"] is None

@@ -141,6 +141,7 @@ EXAMPLE_TASK: dict = {
     "example015": "rdma_memory_pool", "example016": "rdma_ud_datagram",
     "example024": "rdma_atomics", "example025": "rdma_atomics",
     "example026": "rdma_cq_overflow_event", "example027": "rdma_memory_window",
+    "example021": "all_gather_last_dim", "example023": "reduce_scatter_blocks",
     "example022": "gloo_allreduce", "example105": "oneshot_allreduce_virtual_ranks",
     "example109": "oneshot_allreduce_virtual_ranks", "example020": "ulysses_all_to_all",
     "example058": "ulysses_all_to_all", "example087": "weight_broadcast", "example084": "moe_agrs_dispatch",

@@ -242,9 +242,12 @@ def compile_source(source: str, out_dir: str, timeout_s: float = 300.0,
 
 def compile_and_run(folder: str, source: str, timeout_s: float | None = None,
                     build_only: bool = False, work_dir: str | None = None) -> CompileRunResult:
+    # The program runs with the task folder as its working directory: relative paths given by the
+    # caller must not be re-interpreted there.
+    folder, source = os.path.abspath(folder), os.path.abspath(source)
     spec = load_task(folder)
     res = CompileRunResult(source=source)
-    work_dir = work_dir or os.path.join(folder, "build")
+    work_dir = os.path.abspath(work_dir) if work_dir else os.path.join(folder, "build")
     t0 = time.time()
     ok, rc, log, binary = compile_source(source, work_dir, debug=bool(spec.get("debug")))
     res.compile_success, res.compile_returncode, res.compile_output = ok, rc, log

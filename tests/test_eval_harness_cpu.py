@@ -300,3 +300,20 @@ def test_comparison_summary_has_the_documented_layout(tmp_path):
     assert s["correctness"] == {"reference": True, "generated": True, "reason": "program reported PASS"}
     with open(tmp_path / "cmp" / "summary.json") as f:
         assert json.load(f)["task"] == "rdma_memory_pool"
+
+
+@pytest.mark.timeout(300)
+def test_relative_paths_survive_the_change_of_working_directory(tmp_path, monkeypatch):
+    """Programs run with the task folder as their working directory; a relative task folder,
+    source or build directory given by the caller must still mean what it meant for the caller."""
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    monkeypatch.chdir(repo)
+    rel_task = os.path.relpath(os.path.join(TASKS, "rdma_atomics"), repo)
+    rel_src = os.path.join(rel_task, "ref_rdma_atomics.py")
+    work = os.path.relpath(str(tmp_path / "b"), repo)
+    r = CR.compile_and_run(rel_task, rel_src, work_dir=work)
+    assert CR.analyze_result(r) == (True, "program reported PASS"), r.output[-1500:]
+    assert os.path.isabs(r.source)
+    out = tmp_path / "tr"
+    rc = TR.main(["--task", rel_task, "--compare", rel_src, rel_src, "--results-dir", str(out), "--plot"])
+    assert rc == 0 and (out / "summary.json").exists() and (out / "latency.svg").exists()

@@ -102,7 +102,12 @@ def main(argv=None) -> int:
     ap.add_argument("--drop-line-containing", action="append", default=[])
     args = ap.parse_args(argv)
     with open(args.reference) as f:
-        text = skeleton_text(f.read(), tuple(args.drop_line_containing))
+        ref_text = f.read()
+    if not has_markers(ref_text):
+        # Without markers the "skeleton" would be the whole solution: never write that.
+        print(f"no solution markers in {args.reference}: its skeleton is kept by hand", file=sys.stderr)
+        return 2
+    text = skeleton_text(ref_text, tuple(args.drop_line_containing))
     path = skeleton_path(args.reference)
     if args.check:
         with open(path) as f:

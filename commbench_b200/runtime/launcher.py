@@ -45,11 +45,40 @@ def _kill_group(pgid: int):
         time.sleep(0.5)
 
 
+def die_with_parent(sig: int = signal.SIGKILL) -> bool:
+    """Asks the kernel to send ``sig`` to THIS process when its parent dies
+    (``prctl(PR_SET_PDEATHSIG)``): a rank worker then cannot outlive a launcher that was killed
+    before it could clean up.  Returns False where the call is not available."""
+    prctl = _prctl()
+    return prctl is not None and prctl(1, int(sig), 0, 0, 0) == 0     # 1 = PR_SET_PDEATHSIG
+
+
+_PRCTL = None
+
+
+def _prctl():
+    """libc's prctl, looked up once in the parent: the child of a fork must not import anything
+    (another thread may have held the import lock at the time of the fork)."""
+    global _PRCTL
+    if _PRCTL is None:
+        try:
+            import ctypes
+
+            _PRCTL = ctypes.CDLL(None, use_errno=True).prctl
+        except (OSError, AttributeError):
+            _PRCTL = False
+    return _PRCTL or None
+
+
 def run_in_new_session(cmd: list[str], timeout: float, env: dict | None = None,
-                       cwd: str | None = None) -> RunResult:
+                       cwd: str | None = None, pdeathsig: bool = True) -> RunResult:
+    """Runs ``cmd`` in a new session; the whole session group is killed on time-out and after a
+    normal exit.  With ``pdeathsig`` the child is also killed when this process dies first."""
     t0 = time.time()
+    use_pd = pdeathsig and _prctl() is not None
     p = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
-                         start_new_session=True, env=env, cwd=cwd)
+                         start_new_session=True, env=env, cwd=cwd,
+                         preexec_fn=die_with_parent if use_pd else None)
     timed_out = False
     try:
         out, err = p.communicate(timeout=timeout)

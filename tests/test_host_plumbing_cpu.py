@@ -159,6 +159,46 @@ def test_launcher_kills_session_on_timeout(tmp_path):
     assert r.seconds < 10
 
 
+def test_rank_worker_dies_with_a_launcher_that_was_killed(tmp_path):
+    """A launcher killed with SIGKILL cannot clean up; its worker asked the kernel to be killed
+    when the parent dies, so nothing is left behind."""
+    import signal
+    import subprocess
+    import time
+
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    pidfile = tmp_path / "worker.pid"
+    worker = tmp_path / "worker.py"
+    worker.write_text(f"import os, time\nopen({str(pidfile)!r}, 'w').write(str(os.getpid()))\ntime.sleep(120)\n")
+    launcher = tmp_path / "launcher.py"
+    launcher.write_text(
+        f"import sys\nsys.path.insert(0, {repo!r})\n"
+        "from commbench_b200.runtime.launcher import run_in_new_session\n"
+        f"run_in_new_session([sys.executable, {str(worker)!r}], timeout=100)\n")
+    p = subprocess.Popen([sys.executable, str(launcher)])
+    deadline = time.time() + 30
+    while not (pidfile.exists() and pidfile.read_text().strip()) and time.time() < deadline:
+        time.sleep(0.05)
+    wpid = int(pidfile.read_text())
+    os.kill(p.pid, signal.SIGKILL)                     # exactly the launcher we started
+    p.wait(10)
+
+    def alive(pid):
+        try:
+            with open(f"/proc/{pid}/stat") as f:
+                return f.read().rsplit(")", 1)[1].split()[0] != "Z"
+        except OSError:
+            return False
+
+    deadline = time.time() + 10
+    while alive(wpid) and time.time() < deadline:
+        time.sleep(0.05)
+    gone = not alive(wpid)
+    if not gone:
+        os.kill(wpid, signal.SIGKILL)                  # do not leave it behind if the check fails
+    assert gone
+
+
 def test_gate_up_interleave_puts_both_halves_of_an_output_block_in_one_tile():
     """Row order the gated up-projection epilogue expects: per block of 128 outputs the gate
     rows, then the up rows of the same outputs."""

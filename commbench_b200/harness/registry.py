@@ -142,6 +142,9 @@ EXAMPLE_TASK: dict = {
     "example024": "rdma_atomics", "example025": "rdma_atomics",
     "example026": "rdma_cq_overflow_event", "example027": "rdma_memory_window",
     "example021": "all_gather_last_dim", "example023": "reduce_scatter_blocks",
+    "example038": "put_signal_virtual_ranks", "example096": "put_signal_virtual_ranks",
+    "example039": "put_signal_virtual_ranks", "example090": "put_signal_virtual_ranks",
+    "example032": "atomic_ticket_counter",
     "example022": "gloo_allreduce", "example105": "oneshot_allreduce_virtual_ranks",
     "example109": "oneshot_allreduce_virtual_ranks", "example020": "ulysses_all_to_all",
     "example058": "ulysses_all_to_all", "example087": "weight_broadcast", "example084": "moe_agrs_dispatch",

@@ -9,10 +9,11 @@ from commbench_b200.harness import compile_run as CR
 pytestmark = pytest.mark.gpu
 
 TASKS = os.path.join(os.path.dirname(CR.__file__), "tasks")
-GPU1 = sorted(d for d in os.listdir(TASKS)
-              if os.path.exists(os.path.join(TASKS, d, "task.json"))
-              and CR.load_task(os.path.join(TASKS, d))["needs_gpu"]
-              and CR.load_task(os.path.join(TASKS, d))["world"] == 1)
+GPU1 = sorted((d for d in os.listdir(TASKS)
+               if os.path.exists(os.path.join(TASKS, d, "task.json"))
+               and CR.load_task(os.path.join(TASKS, d))["needs_gpu"]
+               and CR.load_task(os.path.join(TASKS, d))["world"] == 1),
+              key=lambda d: (CR.load_task(os.path.join(TASKS, d)).get("added", 0), d))   # oldest tasks first
 
 
 @pytest.mark.timeout(600)

@@ -91,18 +91,43 @@ def load_task(folder: str) -> dict:
     return spec
 
 
-def _find(folder: str, prefix: str) -> str | None:
-    hits = sorted(f for f in os.listdir(folder)
-                  if f.startswith(prefix) and f.endswith(SOURCE_EXTS))
-    return os.path.join(folder, hits[0]) if hits else None
+PLATFORM_SUBDIRS = ("nv", "ib", "roce", "efa")
 
 
-def find_empty_file(folder: str) -> str | None:
-    return _find(folder, "empty_")
+def platform_subdir_order(platform: str | None = None) -> list[str]:
+    """Where a task keeps its files: the folder itself, or a per-platform sub-folder
+    (``nv`` for the GPU vendor, then the fabric this machine has: ``ib`` / ``roce`` / ``efa``; a
+    machine without a NIC still finds the ``ib`` variants, which run on the loopback transport).
+    The reference resolves ``amd_nv -> amd / nv -> ib, roce / efa``
+    (run_eval/compile_run.py:274-333); there is one GPU vendor here."""
+    order = ["", "nv"]
+    p = (platform or "").upper()
+    for net in ("ib", "roce", "efa"):
+        if net.upper() in p:
+            order.append(net)
+    for net in ("ib", "roce", "efa"):
+        if net not in order:
+            order.append(net)
+    return order
 
 
-def find_ref_file(folder: str) -> str | None:
-    return _find(folder, "ref_")
+def _find(folder: str, prefix: str, platform: str | None = None) -> str | None:
+    for sub in platform_subdir_order(platform):
+        d = os.path.join(folder, sub) if sub else folder
+        if not os.path.isdir(d):
+            continue
+        hits = sorted(f for f in os.listdir(d) if f.startswith(prefix) and f.endswith(SOURCE_EXTS))
+        if hits:
+            return os.path.join(d, hits[0])
+    return None
+
+
+def find_empty_file(folder: str, platform: str | None = None) -> str | None:
+    return _find(folder, "empty_", platform)
+
+
+def find_ref_file(folder: str, platform: str | None = None) -> str | None:
+    return _find(folder, "ref_", platform)
 
 
 def first_json_object(text: str) -> dict | None:

@@ -317,3 +317,24 @@ def test_relative_paths_survive_the_change_of_working_directory(tmp_path, monkey
     out = tmp_path / "tr"
     rc = TR.main(["--task", rel_task, "--compare", rel_src, rel_src, "--results-dir", str(out), "--plot"])
     assert rc == 0 and (out / "summary.json").exists() and (out / "latency.svg").exists()
+
+
+def test_task_files_are_found_in_platform_subfolders(tmp_path):
+    assert CR.platform_subdir_order("NV_ROCE")[:3] == ["", "nv", "roce"]
+    assert CR.platform_subdir_order("CPU") == ["", "nv", "ib", "roce", "efa"]
+    t = tmp_path / "task"
+    (t / "nv").mkdir(parents=True)
+    (t / "efa").mkdir()
+    (t / "ib").mkdir()
+    (t / "efa" / "empty_x.py").write_text("# efa\n")
+    (t / "ib" / "empty_x.py").write_text("# ib\n")
+    (t / "ib" / "ref_x.py").write_text("# ib\n")
+    assert CR.find_empty_file(str(t), "NV_EFA").endswith(os.path.join("efa", "empty_x.py"))
+    assert CR.find_empty_file(str(t), "NV_IB").endswith(os.path.join("ib", "empty_x.py"))
+    assert CR.find_empty_file(str(t)).endswith(os.path.join("ib", "empty_x.py"))      # no NIC: ib first
+    assert CR.find_ref_file(str(t), "NV_EFA").endswith(os.path.join("ib", "ref_x.py"))
+    (t / "nv" / "empty_x.cu").write_text("// nv\n")
+    assert CR.find_empty_file(str(t), "NV_EFA").endswith(os.path.join("nv", "empty_x.cu"))
+    (t / "empty_x.py").write_text("# top\n")
+    assert CR.find_empty_file(str(t), "NV_EFA") == str(t / "empty_x.py")              # the folder itself wins
+    assert CR.find_ref_file(str(tmp_path)) is None

@@ -92,3 +92,66 @@ def geometric_mean_speedup(pairs) -> float:
 
     logs = [math.log(b / c) for b, c in pairs if b > 0 and c > 0]
     return math.exp(sum(logs) / len(logs)) if logs else float("nan")
+
+
+def infer_task_name(path: str) -> str | None:
+    """Name of the task a file or results folder belongs to: the nearest ancestor folder that
+    holds a ``task.json`` (the reference walks up to ``exampleNNN_*``:
+    run_eval/perf_verdict.py:256-269)."""
+    import os
+
+    d = os.path.abspath(path)
+    if not os.path.isdir(d):
+        d = os.path.dirname(d)
+    while True:
+        if os.path.exists(os.path.join(d, "task.json")):
+            return os.path.basename(d)
+        parent = os.path.dirname(d)
+        if parent == d:
+            return None
+        d = parent
+
+
+def override_summary_verdict(summary_path: str, entry=None) -> dict:
+    """Re-judges a comparison ``summary.json`` written by an older or foreign tool with the
+    unified scheme: recomputes ``performance`` / ``performance_detail`` from its
+    ``metrics_comparison`` (either ``{metric: {reference, generated}}`` or the reference's
+    ``{ref: {...}, generated: {...}}`` layout), keeps what was there as ``performance_legacy`` and
+    records the thresholds used.  ``entry`` = ``{"primary", "direction"}`` or ``"info_only"``;
+    by default the task's own ``task.json`` decides
+    (run_eval/perf_verdict.py:400-452)."""
+    import json
+    import os
+
+    with open(summary_path) as f:
+        s = json.load(f)
+    if entry is None:
+        d = os.path.dirname(os.path.abspath(summary_path))
+        spec = None
+        while True:
+            p = os.path.join(d, "task.json")
+            if os.path.exists(p):
+                with open(p) as f:
+                    spec = json.load(f)
+                break
+            if os.path.dirname(d) == d:
+                break
+            d = os.path.dirname(d)
+        entry = {"primary": spec["primary_metric"], "direction": spec.get("direction", "lower")} \
+            if spec and spec.get("primary_metric") else INFO_ONLY
+    mc = s.get("metrics_comparison") or {}
+    if "ref" in mc and "generated" in mc and isinstance(mc["ref"], dict):
+        base, cand = mc["ref"], mc["generated"]
+    else:
+        base = {k: v.get("reference") for k, v in mc.items() if isinstance(v, dict)}
+        cand = {k: v.get("generated") for k, v in mc.items() if isinstance(v, dict)}
+    v = compute_verdict(entry, {k: x for k, x in base.items() if x is not None},
+                        {k: x for k, x in cand.items() if x is not None})
+    if "performance" in s and "performance_legacy" not in s:
+        s["performance_legacy"] = s["performance"]
+    s["performance"], s["performance_detail"] = v.verdict, v.detail
+    s["verdict_scheme"] = {"better_pct": BETTER_PCT, "on_par_lower_pct": ON_PAR_LOWER_PCT,
+                           "degraded_lower_pct": DEGRADED_LOWER_PCT}
+    with open(summary_path, "w") as f:
+        json.dump(s, f, indent=1)
+    return s

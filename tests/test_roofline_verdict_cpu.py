@@ -59,3 +59,31 @@ def test_verdict_tiers_and_guards():
         V.improvement_pct(1.0, 1.0, "sideways")
     assert V.geometric_mean_speedup([(2.0, 1.0), (1.0, 2.0)]) == pytest.approx(1.0)
     assert V.geometric_mean_speedup([(3.0, 1.0)]) == pytest.approx(3.0)
+
+
+def test_old_summaries_are_rejudged_and_keep_their_first_verdict(tmp_path):
+    task = tmp_path / "some_task"
+    res = task / "results" / "m" / "round1"
+    res.mkdir(parents=True)
+    (task / "task.json").write_text(json.dumps({"name": "some_task", "primary_metric": "throughput",
+                                                "direction": "higher"}))
+    # the older layout: two flat dicts and a two-word verdict
+    p = res / "summary.json"
+    p.write_text(json.dumps({"metrics_comparison": {"ref": {"throughput": 40.0, "latency_avg": 9.0},
+                                                    "generated": {"throughput": 52.0, "latency_avg": 7.0}},
+                             "performance": "same"}))
+    assert V.infer_task_name(str(p)) == "some_task" and V.infer_task_name(str(res)) == "some_task"
+    assert V.infer_task_name(str(tmp_path)) is None
+    s = V.override_summary_verdict(str(p))
+    assert s["performance"] == "better" and s["performance_legacy"] == "same"
+    assert s["performance_detail"]["primary_metric"] == "throughput" and s["verdict_scheme"]["better_pct"] == 20.0
+    again = V.override_summary_verdict(str(p), {"primary": "latency_avg", "direction": "lower"})
+    assert again["performance"] == "better" and again["performance_legacy"] == "same"   # first verdict kept
+    assert again["performance_detail"]["improvement_pct"] == pytest.approx(22.222, abs=1e-3)
+    # the current layout, and a task without a metric of its own
+    q = res / "s2.json"
+    q.write_text(json.dumps({"metrics_comparison": {"latency_avg": {"reference": 10.0, "generated": 20.0}}}))
+    assert V.override_summary_verdict(str(q), {"primary": "latency_avg", "direction": "lower"})["performance"] == \
+        "severely_degraded"
+    (task / "task.json").write_text(json.dumps({"name": "some_task"}))
+    assert V.override_summary_verdict(str(q))["performance"] == "info_only"

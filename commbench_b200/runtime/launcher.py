@@ -75,7 +75,11 @@ def run_in_new_session(cmd: list[str], timeout: float, env: dict | None = None,
     """Runs ``cmd`` in a new session; the whole session group is killed on time-out and after a
     normal exit.  With ``pdeathsig`` the child is also killed when this process dies first."""
     t0 = time.time()
-    use_pd = pdeathsig and _prctl() is not None
+    # Python code between fork and exec is kept out of parents that hold a CUDA context (many
+    # driver threads): there the session-group kill below is the containment.
+    torch_mod = sys.modules.get("torch")
+    cuda_live = bool(torch_mod is not None and torch_mod.cuda.is_initialized())
+    use_pd = pdeathsig and not cuda_live and _prctl() is not None
     p = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
                          start_new_session=True, env=env, cwd=cwd,
                          preexec_fn=die_with_parent if use_pd else None)

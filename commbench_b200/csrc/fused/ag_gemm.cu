@@ -18,6 +18,7 @@
 
 #include <string>
 
+#include "../gemm/launch.h"
 #include "../gemm/tmap_host.h"
 #include "../symm/driver_api.h"
 
@@ -32,7 +33,7 @@ struct AgGemmParams {
   CUtensorMap tm_c;
   GemmShape g;
   int rank, world;
-  int blocks_per_rank;  // 128-row blocks of A owned by each rank
+  int blocks_per_rank;  // row blocks (one tile height each) of A owned by each rank
   int parts;            // independent pieces a row block is pushed in
   int num_comm_ctas;
   int raster_group;
@@ -220,16 +221,15 @@ static int launch_ag(const AgGemmParams& p, const AgGemmParams* emu, int emu_wor
     set_last_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
     return -1;
   }
-  if (emu != nullptr) {
-    void* params[] = {const_cast<AgGemmParams*>(&p), &emu, &ctas_per_rank};
-    e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(ag_gemm_kernel<Cfg>),
-                                    dim3(ctas_per_rank * emu_world), dim3(Cfg::THREADS), params,
-                                    Cfg::SMEM_BYTES, st);
-  } else {
-    ag_gemm_kernel<Cfg><<<ctas_per_rank, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(p, nullptr,
-                                                                              ctas_per_rank);
-    e = cudaGetLastError();
+  if (ctas_per_rank % Cfg::PAIR != 0 || p.num_comm_ctas % Cfg::PAIR != 0) {
+    set_last_error("ag_gemm: CTA counts must be even for CTA-pair tiles");
+    return -1;
   }
+  // Emulated ranks wait on one another inside the launch: cooperative, so that all their
+  // CTAs are resident together.
+  const int grid = emu != nullptr ? ctas_per_rank * emu_world : ctas_per_rank;
+  e = launch_gemm_kernel(ag_gemm_kernel<Cfg>, grid, Cfg::THREADS, Cfg::SMEM_BYTES, st, Cfg::PAIR,
+                         emu != nullptr, p, emu, ctas_per_rank);
   if (e != cudaSuccess) {
     set_last_error(std::string("ag_gemm launch: ") + cudaGetErrorString(e));
     return -1;
@@ -249,9 +249,9 @@ struct CbAgGemmDesc {
   int M, N, K;            // M = rows of the gathered A (all ranks), N = local columns
   int fp8;                // 0 bf16, 1 fp8 e4m3 (inputs); output is bf16
   float alpha;
-  int bn;                 // 256 or 128
+  int bn;                 // 256 or 128: one CTA per 128 x bn tile; 512: a CTA pair per 256 x 256
   int num_comm_ctas;      // 0 when world == 1
-  int parts;              // pieces a 128-row block is pushed in (0 < parts <= 1024)
+  int parts;              // pieces a row block is pushed in (0 < parts <= 1024)
   int ctas_per_rank;      // CTAs this rank's launch (or grid slice) uses
   const void* a_local;    // [M/world, K]
   const void* b;          // [N, K]
@@ -269,15 +269,18 @@ static int build_ag_params(const CbAgGemmDesc& d, AgGemmParams* p) {
   const int esz = d.fp8 ? 1 : 2;
   const int BK = d.fp8 ? 128 : 64;
   const TmapDtype dt = d.fp8 ? TMAP_U8 : TMAP_BF16;
-  if (d.world < 1 || d.M % (d.world * 128) != 0) {
-    set_last_error("ag_gemm: M must be a multiple of world * 128");
+  const int pair = d.bn == 512 ? 2 : 1;
+  const int bm = 128 * pair;                 // tile height = rows per flag
+  const int tile_n = d.bn == 512 ? 256 : d.bn;
+  if (d.world < 1 || d.M % (d.world * bm) != 0) {
+    set_last_error("ag_gemm: M must be a multiple of world * tile height (128, or 256 for bn 512)");
     return -1;
   }
   if (d.K % 16 != 0 || d.N % 8 != 0) {
     set_last_error("ag_gemm: K % 16 == 0 and N % 8 == 0 required");
     return -1;
   }
-  if (d.M / 128 > kAgMaxRowBlocks) {
+  if (d.M / bm > kAgMaxRowBlocks) {
     set_last_error("ag_gemm: too many row blocks");
     return -1;
   }
@@ -299,24 +302,25 @@ static int build_ag_params(const CbAgGemmDesc& d, AgGemmParams* p) {
       p->tm_a_full[par] = p->tm_a_local;
     }
   }
-  if (make_tmap_2d(&p->tm_b, d.b, dt, d.K, d.N, (unsigned long long)d.K * esz, BK, d.bn, true))
+  if (make_tmap_2d(&p->tm_b, d.b, dt, d.K, d.N, (unsigned long long)d.K * esz, BK, tile_n / pair,
+                   true))
     return -1;
   if (make_tmap_2d(&p->tm_c, d.c, TMAP_BF16, d.N, d.M, (unsigned long long)d.N * 2, 64, 32, true))
     return -1;
   p->g.M = d.M;
   p->g.N = d.N;
   p->g.K = d.K;
-  p->g.num_m_blocks = d.M / 128;
-  p->g.num_n_blocks = (d.N + d.bn - 1) / d.bn;
+  p->g.num_m_blocks = d.M / bm;
+  p->g.num_n_blocks = (d.N + tile_n - 1) / tile_n;
   p->g.num_k_blocks = (d.K + BK - 1) / BK;
   p->g.alpha = d.alpha;
   p->rank = d.rank;
   p->world = d.world;
-  p->blocks_per_rank = Ml / 128;
+  p->blocks_per_rank = Ml / bm;
   p->parts = d.parts;
   p->num_comm_ctas = d.world > 1 ? d.num_comm_ctas : 0;
   p->raster_group = p->blocks_per_rank < 8 ? p->blocks_per_rank : 8;
-  p->row_block_bytes = 128ull * d.K * esz;
+  p->row_block_bytes = static_cast<unsigned long long>(bm) * d.K * esz;
   p->a_local = static_cast<const uint8_t*>(d.a_local);
   for (int par = 0; par < 2; ++par) {
     for (int r = 0; r < CB_MAX_RANKS; ++r)
@@ -370,13 +374,17 @@ int cb_ag_gemm(const CbAgGemmDesc* descs, int n, void* emu_table, void* stream) 
   }
   const CbAgGemmDesc& d = descs[0];
   if (d.fp8) {
+    if (d.bn == 512)
+      return launch_ag<GemmCfg<256, 6, true, 2>>(hp[0], emu, n, d.ctas_per_rank, st);
     if (d.bn == 256) return launch_ag<GemmCfg<256, 4, true>>(hp[0], emu, n, d.ctas_per_rank, st);
     if (d.bn == 128) return launch_ag<GemmCfg<128, 6, true>>(hp[0], emu, n, d.ctas_per_rank, st);
   } else {
+    if (d.bn == 512)
+      return launch_ag<GemmCfg<256, 6, false, 2>>(hp[0], emu, n, d.ctas_per_rank, st);
     if (d.bn == 256) return launch_ag<GemmCfg<256, 4, false>>(hp[0], emu, n, d.ctas_per_rank, st);
     if (d.bn == 128) return launch_ag<GemmCfg<128, 6, false>>(hp[0], emu, n, d.ctas_per_rank, st);
   }
-  set_last_error("ag_gemm: bn must be 128 or 256");
+  set_last_error("ag_gemm: bn must be 128, 256 or 512");
   return -1;
 }
 

@@ -3,12 +3,15 @@
 //
 // ONE kernel per rank.  The tcgen05 GEMM walks the output row blocks owner by
 // owner, starting with the next rank (so at any moment the W ranks write to W
-// different owners); the epilogue writes each bf16 partial tile straight into
-// the OWNER's staging slot for this source rank (row-contiguous 16-byte stores
-// over NVLink) and bumps a per-tile arrival counter there.  When a CTA has finished its GEMM tiles it turns to the
-// reduction of this rank's own output tiles: wait until all W partials of a
-// tile arrived, add them in fp32, write bf16.  The transfer of tile i overlaps
-// the math of tile i+1; the result is deterministic (fixed summation order).
+// different owners) and ending with its OWN rows.  For another rank's rows the
+// epilogue writes the bf16 partial tile straight into the owner's staging slot
+// for this source rank (row-contiguous 16-byte stores over NVLink) and bumps a
+// per-tile arrival counter there.  For its own rows - by then the other ranks'
+// partials have had a whole owner-chunk of time to arrive - the epilogue waits
+// for the tile's W-1 arrivals, adds the staged partials to its accumulator in
+// fp32 in rank order and writes the final bf16 rows: the reduction runs under
+// the main loop of the next tile, the local partial never goes through memory,
+// and there is no reduction phase after the GEMM.  Deterministic (fixed order).
 //
 // The reference fuses the same pair with in-flight `store_add` into the
 // owner's C (datasets/example054_thunderkitten_gemm_rs_easy/nv/
@@ -20,6 +23,7 @@
 
 #include <string>
 
+#include "../gemm/launch.h"
 #include "../gemm/tmap_host.h"
 #include "../symm/driver_api.h"
 
@@ -33,7 +37,7 @@ struct GemmRsParams {
   uint8_t* stage_peer[2][CB_MAX_RANKS];  // [parity][owner]: owner's staging (all source slots)
   GemmShape g;
   int rank, world;
-  int blocks_per_rank;  // 128-row blocks of the output owned by each rank
+  int blocks_per_rank;  // row blocks (one tile height each) of the output owned by each rank
   int raster_group;
   const uint8_t* stage_local[2];  // my staging: [W sources][M/W][N] bf16
   uint32_t* flags_peer[CB_MAX_RANKS];  // [2][kRsMaxTiles] on each rank
@@ -73,7 +77,42 @@ struct RsPolicy {
   static constexpr bool kDirect = true;
   static constexpr bool kSignalPerTile = true;
   static constexpr bool kScatterRows = false;
+  static constexpr bool kReduceLocal = true;
   __device__ static int b_row(const RsRt&, int, int n_blk) { return n_blk * Cfg::BN; }
+  __device__ static bool tile_is_local(const RsRt& r, int m_blk) {
+    return m_blk / r.p->blocks_per_rank == r.p->rank;
+  }
+  // Arrival counter of the rows that CTA `sub` of a pair produces / consumes for local tile
+  // (lm, n_blk).
+  __device__ static int flag_index(const GemmRsParams& p, int lm, int n_blk, int sub) {
+    return (lm * p.g.num_n_blocks + n_blk) * Cfg::PAIR + sub;
+  }
+  __device__ static bool wait_local_ready(const RsRt& r, int m_blk, int n_blk, int sub) {
+    const GemmRsParams& p = *r.p;
+    const int lm = m_blk - p.rank * p.blocks_per_rank;
+    const uint32_t* f = p.flags_local + r.parity * kRsMaxTiles + flag_index(p, lm, n_blk, sub);
+    return wait_flag_ge_sys_paced(f, static_cast<uint32_t>(p.world - 1), p.timeout_ns, p.status,
+                                  PH_RS_TILE, lm * p.g.num_n_blocks + n_blk, kPacedPollNs);
+  }
+  __device__ static void local_reduce(const RsRt& r, int m_blk, int n_blk, LocalReduce* t) {
+    const GemmRsParams& p = *r.p;
+    const int lm = m_blk - p.rank * p.blocks_per_rank;
+    const long long Ml = p.g.M / p.world;
+    const long long ld = static_cast<long long>(p.g.N) * 2;
+    const long long tile_off =
+        (static_cast<long long>(lm) * Cfg::BM * p.g.N + static_cast<long long>(n_blk) * Cfg::BN) *
+        2;
+    // Copies in rank order (own rank left out): the sum does not depend on timing.
+    t->nsrc = p.world - 1;
+#pragma unroll
+    for (int i = 0; i < 7; ++i) {
+      const int s = i + (i >= p.rank ? 1 : 0);
+      t->src[i] = p.stage_local[r.parity] + static_cast<long long>(s) * Ml * ld + tile_off;
+    }
+    t->src_ld = ld;
+    t->out = static_cast<uint8_t*>(p.out) + tile_off;
+    t->out_ld = ld;
+  }
   __device__ static void direct_targets(const RsRt& r, int m_blk, int n_blk, DirectTargets* t) {
     const GemmRsParams& p = *r.p;
     const int owner = m_blk / p.blocks_per_rank;
@@ -89,56 +128,15 @@ struct RsPolicy {
     t->cols = left < Cfg::BN ? left : Cfg::BN;
   }
   // Signal thread, after its release fence covered the tile's stores.
-  __device__ static void tile_done(const RsRt& r, int m_blk, int n_blk, int) {
+  __device__ static void tile_done(const RsRt& r, int m_blk, int n_blk, int quadrant) {
     const GemmRsParams& p = *r.p;
     const int owner = m_blk / p.blocks_per_rank;
     const int lm = m_blk - owner * p.blocks_per_rank;
     red_relaxed_sys_add(
-        p.flags_peer[owner] + r.parity * kRsMaxTiles + lm * p.g.num_n_blocks + n_blk, 1u);
+        p.flags_peer[owner] + r.parity * kRsMaxTiles + flag_index(p, lm, n_blk, quadrant >> 2),
+        1u);
   }
 };
-
-// Reduction of this rank's output tiles; all threads of the CTA take part.
-template <class Cfg>
-__device__ __forceinline__ void rs_reduce_phase(const GemmRsParams& p, uint32_t parity, int cta,
-                                                int num_ctas) {
-  const int Ml = p.g.M / p.world;
-  const int ntiles = p.blocks_per_rank * p.g.num_n_blocks;
-  constexpr int VPR = Cfg::BN / 8;  // 16-byte vectors per tile row
-  const uint4* stage = reinterpret_cast<const uint4*>(p.stage_local[parity]);
-  uint4* out = static_cast<uint4*>(p.out);
-  const unsigned long long row_vecs = static_cast<unsigned long long>(p.g.N) / 8ull;
-  for (int t = cta; t < ntiles; t += num_ctas) {
-    const int lm = t / p.g.num_n_blocks;
-    const int n_blk = t - lm * p.g.num_n_blocks;
-    uint32_t* flag = p.flags_local + parity * kRsMaxTiles + t;
-    bool ok = true;
-    if (threadIdx.x == 0)
-      ok = wait_flag_ge_sys(flag, static_cast<uint32_t>(p.world), p.timeout_ns, p.status,
-                            PH_RS_TILE, t);
-    if (__syncthreads_and(ok ? 1 : 0) == 0) return;
-    auto src = [&](int s, int v) -> const uint4* {
-      const unsigned long long row = static_cast<unsigned long long>(lm) * Cfg::BM + v / VPR;
-      return stage + (static_cast<unsigned long long>(s) * Ml + row) * row_vecs + n_blk * VPR +
-             v % VPR;
-    };
-    auto dst = [&](int v, uint4 x) {
-      const unsigned long long row = static_cast<unsigned long long>(lm) * Cfg::BM + v / VPR;
-      out[row * row_vecs + n_blk * VPR + v % VPR] = x;
-    };
-    auto valid = [&](int v) -> bool {
-      return static_cast<unsigned long long>(n_blk * VPR + v % VPR) < row_vecs;
-    };
-    switch (p.world) {
-      case 1: reduce_tile_copies<1, Cfg::BM * VPR>(src, dst, valid); break;
-      case 2: reduce_tile_copies<2, Cfg::BM * VPR>(src, dst, valid); break;
-      case 4: reduce_tile_copies<4, Cfg::BM * VPR>(src, dst, valid); break;
-      default: reduce_tile_copies<8, Cfg::BM * VPR>(src, dst, valid); break;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) *flag = 0u;  // ready for the call after next
-  }
-}
 
 template <class Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
@@ -151,9 +149,26 @@ __global__ void __launch_bounds__(Cfg::THREADS, 1)
   const uint32_t parity = fused_begin(p.seq);
   RsRt rt{&p, parity};
   gemm_cta_main<Cfg, RsPolicy<Cfg>>(rt, p.g, p.status, cta, ctas_per_rank, smem_raw);
+  // Last CTA out clears this parity's arrival counters (every wait of this call is over by
+  // then; the peers' next additions to them belong to the call after next).
   __syncthreads();
-  rs_reduce_phase<Cfg>(p, parity, cta, ctas_per_rank);
-  fused_end(p.seq, static_cast<uint32_t>(ctas_per_rank));
+  __shared__ int last_cta;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    last_cta = atomicAdd(p.seq.done_ctas, 1u) == static_cast<uint32_t>(ctas_per_rank) - 1u;
+  }
+  __syncthreads();
+  if (last_cta) {
+    const int nflags = p.blocks_per_rank * p.g.num_n_blocks * Cfg::PAIR;
+    for (int i = threadIdx.x; i < nflags; i += blockDim.x)
+      p.flags_local[parity * kRsMaxTiles + i] = 0u;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      *p.seq.done_ctas = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(p.seq.seq) = ld_volatile(p.seq.seq) + 1u;
+    }
+  }
 }
 
 template <class Cfg>
@@ -166,16 +181,13 @@ static int launch_rs(const GemmRsParams& p, const GemmRsParams* emu, int emu_wor
     set_last_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
     return -1;
   }
-  if (emu != nullptr) {
-    void* params[] = {const_cast<GemmRsParams*>(&p), &emu, &ctas_per_rank};
-    e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(gemm_rs_kernel<Cfg>),
-                                    dim3(ctas_per_rank * emu_world), dim3(Cfg::THREADS), params,
-                                    Cfg::SMEM_BYTES, st);
-  } else {
-    gemm_rs_kernel<Cfg><<<ctas_per_rank, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(p, nullptr,
-                                                                              ctas_per_rank);
-    e = cudaGetLastError();
+  if (ctas_per_rank % Cfg::PAIR != 0) {
+    set_last_error("gemm_rs: the CTA count must be even for CTA-pair tiles");
+    return -1;
   }
+  const int grid = emu != nullptr ? ctas_per_rank * emu_world : ctas_per_rank;
+  e = launch_gemm_kernel(gemm_rs_kernel<Cfg>, grid, Cfg::THREADS, Cfg::SMEM_BYTES, st, Cfg::PAIR,
+                         emu != nullptr, p, emu, ctas_per_rank);
   if (e != cudaSuccess) {
     set_last_error(std::string("gemm_rs launch: ") + cudaGetErrorString(e));
     return -1;
@@ -194,7 +206,7 @@ struct CbGemmRsDesc {
   int M, N, K;            // K = local K shard
   int fp8;
   float alpha;
-  int bn;                 // 256 or 128
+  int bn;                 // 256 or 128: one CTA per 128 x bn tile; 512: a CTA pair per 256 x 256
   int ctas_per_rank;
   const void* a;          // [M, K]
   const void* b;          // [N, K]
@@ -210,8 +222,11 @@ static int build_rs_params(const CbGemmRsDesc& d, GemmRsParams* p) {
   const int esz = d.fp8 ? 1 : 2;
   const int BK = d.fp8 ? 128 : 64;
   const TmapDtype dt = d.fp8 ? TMAP_U8 : TMAP_BF16;
-  if (d.world < 1 || d.M % (d.world * 128) != 0) {
-    set_last_error("gemm_rs: M must be a multiple of world * 128");
+  const int pair = d.bn == 512 ? 2 : 1;
+  const int bm = 128 * pair;
+  const int tile_n = d.bn == 512 ? 256 : d.bn;
+  if (d.world < 1 || d.M % (d.world * bm) != 0) {
+    set_last_error("gemm_rs: M must be a multiple of world * tile height (128, or 256 for bn 512)");
     return -1;
   }
   if (d.K % 16 != 0 || d.N % 8 != 0) {
@@ -219,14 +234,15 @@ static int build_rs_params(const CbGemmRsDesc& d, GemmRsParams* p) {
     return -1;
   }
   const int Ml = d.M / d.world;
-  const int num_n = (d.N + d.bn - 1) / d.bn;
-  if ((Ml / 128) * num_n > kRsMaxTiles) {
+  const int num_n = (d.N + tile_n - 1) / tile_n;
+  if ((Ml / bm) * num_n * pair > kRsMaxTiles) {
     set_last_error("gemm_rs: too many output tiles per rank");
     return -1;
   }
   if (make_tmap_2d(&p->tm_a, d.a, dt, d.K, d.M, (unsigned long long)d.K * esz, BK, 128, true))
     return -1;
-  if (make_tmap_2d(&p->tm_b, d.b, dt, d.K, d.N, (unsigned long long)d.K * esz, BK, d.bn, true))
+  if (make_tmap_2d(&p->tm_b, d.b, dt, d.K, d.N, (unsigned long long)d.K * esz, BK, tile_n / pair,
+                   true))
     return -1;
   for (int par = 0; par < 2; ++par) {
     for (int o = 0; o < CB_MAX_RANKS; ++o)
@@ -236,13 +252,13 @@ static int build_rs_params(const CbGemmRsDesc& d, GemmRsParams* p) {
   p->g.M = d.M;
   p->g.N = d.N;
   p->g.K = d.K;
-  p->g.num_m_blocks = d.M / 128;
+  p->g.num_m_blocks = d.M / bm;
   p->g.num_n_blocks = num_n;
   p->g.num_k_blocks = (d.K + BK - 1) / BK;
   p->g.alpha = d.alpha;
   p->rank = d.rank;
   p->world = d.world;
-  p->blocks_per_rank = Ml / 128;
+  p->blocks_per_rank = Ml / bm;
   p->raster_group = p->blocks_per_rank < 8 ? p->blocks_per_rank : 8;
   for (int r = 0; r < CB_MAX_RANKS; ++r) p->flags_peer[r] = static_cast<uint32_t*>(d.flags_peer[r]);
   p->flags_local = static_cast<uint32_t*>(d.flags_peer[d.rank]);
@@ -259,7 +275,7 @@ int cb_sizeof_gemm_rs_params() { return static_cast<int>(sizeof(GemmRsParams)); 
 int cb_gemm_rs(const CbGemmRsDesc* descs, int n, void* emu_table, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (n < 1 || n > CB_MAX_RANKS) return -1;
-  static GemmRsParams hp[CB_MAX_RANKS];
+  GemmRsParams hp[CB_MAX_RANKS];
   for (int i = 0; i < n; ++i)
     if (build_rs_params(descs[i], &hp[i]) != 0) return -1;
   const GemmRsParams* emu = nullptr;
@@ -279,13 +295,17 @@ int cb_gemm_rs(const CbGemmRsDesc* descs, int n, void* emu_table, void* stream) 
   }
   const CbGemmRsDesc& d = descs[0];
   if (d.fp8) {
+    if (d.bn == 512)
+      return launch_rs<GemmCfg<256, 6, true, 2>>(hp[0], emu, n, d.ctas_per_rank, st);
     if (d.bn == 256) return launch_rs<GemmCfg<256, 4, true>>(hp[0], emu, n, d.ctas_per_rank, st);
     if (d.bn == 128) return launch_rs<GemmCfg<128, 6, true>>(hp[0], emu, n, d.ctas_per_rank, st);
   } else {
+    if (d.bn == 512)
+      return launch_rs<GemmCfg<256, 6, false, 2>>(hp[0], emu, n, d.ctas_per_rank, st);
     if (d.bn == 256) return launch_rs<GemmCfg<256, 4, false>>(hp[0], emu, n, d.ctas_per_rank, st);
     if (d.bn == 128) return launch_rs<GemmCfg<128, 6, false>>(hp[0], emu, n, d.ctas_per_rank, st);
   }
-  set_last_error("gemm_rs: bn must be 128 or 256");
+  set_last_error("gemm_rs: bn must be 128, 256 or 512");
   return -1;
 }
 

@@ -10,6 +10,7 @@
 #include <string>
 
 #include "../symm/driver_api.h"
+#include "launch.h"
 #include "tmap_host.h"
 
 namespace cb {
@@ -106,13 +107,14 @@ static int sm_count() {
 
 template <class Cfg>
 static int launch_plain(const void* a, const void* b, void* c, int M, int N, int K, float alpha,
-                        uint32_t* status, int max_ctas, cudaStream_t st) {
+                        uint32_t* status, int max_ctas, cudaStream_t st,
+                        unsigned long long* trace = nullptr) {
   PlainParams p;
   const TmapDtype dt = Cfg::FP8 ? TMAP_U8 : TMAP_BF16;
   const unsigned esz = Cfg::FP8 ? 1 : 2;
-  if (make_tmap_2d(&p.tm_a, a, dt, K, M, (unsigned long long)K * esz, Cfg::BK, Cfg::BM, true))
+  if (make_tmap_2d(&p.tm_a, a, dt, K, M, (unsigned long long)K * esz, Cfg::BK, Cfg::CTA_M, true))
     return -1;
-  if (make_tmap_2d(&p.tm_b, b, dt, K, N, (unsigned long long)K * esz, Cfg::BK, Cfg::BN, true))
+  if (make_tmap_2d(&p.tm_b, b, dt, K, N, (unsigned long long)K * esz, Cfg::BK, Cfg::B_ROWS, true))
     return -1;
   if (make_tmap_2d(&p.tm_c, c, TMAP_BF16, N, M, (unsigned long long)N * 2, Cfg::EPI_COLS, 32,
                    true))
@@ -124,8 +126,17 @@ static int launch_plain(const void* a, const void* b, void* c, int M, int N, int
   p.g.num_n_blocks = (N + Cfg::BN - 1) / Cfg::BN;
   p.g.num_k_blocks = (K + Cfg::BK - 1) / Cfg::BK;
   p.g.alpha = alpha;
+  p.g.trace = trace;
   p.status = status;
-  p.raster_group = 8;
+  // Row blocks per raster panel: the panel's A rows (panel x K) stay in L2 while the B
+  // tiles stream past them, so keep the panel near 32 MB.
+  {
+    const long long panel_rows = (32ll << 20) / (static_cast<long long>(K) * esz);
+    int grp = static_cast<int>(panel_rows / Cfg::BM);
+    if (grp < 2) grp = 2;
+    if (grp > 16) grp = 16;
+    p.raster_group = grp;
+  }
   {
     cudaError_t e = cudaFuncSetAttribute(gemm_plain_kernel<Cfg>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -138,10 +149,11 @@ static int launch_plain(const void* a, const void* b, void* c, int M, int N, int
   int tiles = p.g.num_m_blocks * p.g.num_n_blocks;
   int ctas = sm_count();
   if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
-  if (tiles < ctas) ctas = tiles;
-  if (ctas < 1) return 0;
-  gemm_plain_kernel<Cfg><<<ctas, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(p);
-  cudaError_t e = cudaGetLastError();
+  if (tiles * Cfg::PAIR < ctas) ctas = tiles * Cfg::PAIR;
+  ctas -= ctas % Cfg::PAIR;
+  if (ctas < Cfg::PAIR) return 0;
+  cudaError_t e = launch_gemm_kernel(gemm_plain_kernel<Cfg>, ctas, Cfg::THREADS, Cfg::SMEM_BYTES,
+                                     st, Cfg::PAIR, false, p);
   if (e != cudaSuccess) {
     set_last_error(std::string("gemm launch: ") + cudaGetErrorString(e));
     return -1;
@@ -156,7 +168,8 @@ using namespace cb;
 extern "C" {
 
 // bf16: A [M,K], B [N,K], C [M,N], all row-major and 16-byte aligned; K % 8 == 0, N % 8 == 0.
-// `bn` picks the tile width (256, 128 or 64; 0 = choose from the shape).
+// `bn` picks the tile: 256, 128 or 64 = one CTA per 128 x bn tile; 512 = a CTA pair per
+// 256 x 256 tile, 384 = a pair per 256 x 128 tile; 0 = choose from the shape.
 // `status` may be null.  Returns 0 or -1 (cb_last_error()).
 int cb_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, float alpha, int bn,
                  int max_ctas, void* status, void* stream) {
@@ -167,13 +180,19 @@ int cb_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, flo
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint32_t* s = static_cast<uint32_t*>(status);
   if (bn == 0) {
-    // Fill the machine: wide tiles when there are plenty, narrow ones for skinny problems.
+    // Fill the machine: pairs on 256 x 256 tiles when there are plenty of them, narrower
+    // tiles for skinny problems.
     const long long m_blocks = (M + 127) / 128;
-    if (m_blocks * ((N + 255) / 256) >= sm_count()) bn = 256;
+    if (((M + 255) / 256) * ((N + 255) / 256) * 2 >= sm_count()) bn = 512;
+    else if (m_blocks * ((N + 255) / 256) >= sm_count()) bn = 256;
     else if (m_blocks * ((N + 127) / 128) >= sm_count()) bn = 128;
     else bn = 64;
   }
   switch (bn) {
+    case 512:
+      return launch_plain<GemmCfg<256, 6, false, 2>>(a, b, c, M, N, K, alpha, s, max_ctas, st);
+    case 384:
+      return launch_plain<GemmCfg<128, 8, false, 2>>(a, b, c, M, N, K, alpha, s, max_ctas, st);
     case 256:
       return launch_plain<GemmCfg<256, 4, false>>(a, b, c, M, N, K, alpha, s, max_ctas, st);
     case 128:
@@ -181,9 +200,27 @@ int cb_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, flo
     case 64:
       return launch_plain<GemmCfg<64, 8, false>>(a, b, c, M, N, K, alpha, s, max_ctas, st);
     default:
-      set_last_error("cb_gemm_bf16: bn must be 0, 64, 128 or 256");
+      set_last_error("cb_gemm_bf16: bn must be 0, 64, 128, 256, 384 or 512");
       return -1;
   }
+}
+
+// cb_gemm_bf16 with the role trace switched on: `trace` = 8 x (number of SMs) 64-bit words
+// of device memory (see GemmShape::trace for what each CTA writes).  bn: 512 or 256.
+int cb_gemm_bf16_traced(const void* a, const void* b, void* c, int M, int N, int K, float alpha,
+                        int bn, void* trace, void* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 8) != 0 || (N % 8) != 0 || trace == nullptr) {
+    set_last_error("cb_gemm_bf16_traced: need M,N,K > 0, K % 8 == 0, N % 8 == 0, a trace buffer");
+    return -1;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint32_t* s = static_cast<uint32_t*>(status);
+  unsigned long long* t = static_cast<unsigned long long*>(trace);
+  if (bn == 512)
+    return launch_plain<GemmCfg<256, 6, false, 2>>(a, b, c, M, N, K, alpha, s, 0, st, t);
+  if (bn == 256) return launch_plain<GemmCfg<256, 4, false>>(a, b, c, M, N, K, alpha, s, 0, st, t);
+  set_last_error("cb_gemm_bf16_traced: bn must be 256 or 512");
+  return -1;
 }
 
 // fp8 e4m3 inputs with ONE scale per tensor folded into alpha; K % 16 == 0.
@@ -197,11 +234,14 @@ int cb_gemm_fp8(const void* a, const void* b, void* c, int M, int N, int K, floa
   uint32_t* s = static_cast<uint32_t*>(status);
   if (bn == 0) {
     const long long m_blocks = (M + 127) / 128;
-    if (m_blocks * ((N + 255) / 256) >= sm_count()) bn = 256;
+    if (((M + 255) / 256) * ((N + 255) / 256) * 2 >= sm_count()) bn = 512;
+    else if (m_blocks * ((N + 255) / 256) >= sm_count()) bn = 256;
     else if (m_blocks * ((N + 127) / 128) >= sm_count()) bn = 128;
     else bn = 64;
   }
   switch (bn) {
+    case 512:
+      return launch_plain<GemmCfg<256, 6, true, 2>>(a, b, c, M, N, K, alpha, s, max_ctas, st);
     case 256:
       return launch_plain<GemmCfg<256, 4, true>>(a, b, c, M, N, K, alpha, s, max_ctas, st);
     case 128:
@@ -209,7 +249,7 @@ int cb_gemm_fp8(const void* a, const void* b, void* c, int M, int N, int K, floa
     case 64:
       return launch_plain<GemmCfg<64, 8, true>>(a, b, c, M, N, K, alpha, s, max_ctas, st);
     default:
-      set_last_error("cb_gemm_fp8: bn must be 0, 64, 128 or 256");
+      set_last_error("cb_gemm_fp8: bn must be 0, 64, 128, 256 or 512");
       return -1;
   }
 }

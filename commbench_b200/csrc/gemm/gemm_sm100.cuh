@@ -8,9 +8,9 @@
 // datasets/example051_thunderkitten_ag_gemm_easy/nv/empty_thunderkitten_ag_gemm.cu:152-238,
 // datasets/example053_thunderkitten_gemm_ar_easy/nv/empty_thunderkitten_gemm_ar.cu:84-191),
 // written directly in PTX:
-//   warp 0      : one elected thread issues TMA loads of A (128 x 128 B) and B (BN x 128 B)
+//   warp 0      : one elected lane issues TMA loads of A (128 x 128 B) and B (BN x 128 B)
 //                 tiles into a STAGES-deep shared-memory ring (128-byte swizzle);
-//   warp 1      : allocates TMEM; one elected thread issues tcgen05.mma (M=128, N=BN,
+//   warp 1      : allocates TMEM; one elected lane issues tcgen05.mma (M=128, N=BN,
 //                 K=32 bytes per instruction) and commits completion to mbarriers;
 //   warp 6      : signal warp (fused kernels only): system-scope fence + flag per tile;
 //   warps 2..5  : epilogue: tcgen05.ld the accumulator (warp w owns TMEM lanes
@@ -20,29 +20,46 @@
 // GEMM+collective kernels: tile order, a readiness wait before a tile's A rows are
 // loaded, where a finished sub-tile is stored and what is signalled afterwards.
 //
+//
+// CTA pairs (`PAIR_ = 2`, launched as clusters of two): the two CTAs share one
+// 256 x BN tile the way the reference's `CLUSTER_SIZE = 2` GEMMs do
+// (datasets/example051_thunderkitten_ag_gemm_easy/nv/empty_thunderkitten_ag_gemm.cu:73,86-99).
+// CTA r of the pair loads rows 128r.. of the A tile and rows (BN/2)r.. of the B
+// tile with its own plain TMA loads, whose bytes are counted on the even CTA's
+// mbarrier; the even CTA's MMA thread issues `tcgen05.mma.cta_group::2`
+// (M = 256), which makes each tensor core read its own A half and both B
+// halves, so the B traffic out of shared memory halves and the ring gets
+// deeper; completion is committed to the barriers of both CTAs; each CTA drains
+// its own 128 accumulator rows.  `Cfg::BM` is the height of a tile (128 or 256)
+// and is what policies count row blocks in.
+//
 // No load in this file is a cluster-multicast load.  Every wait is bounded: on a
-// time-out the CTA raises its abort word, every role leaves its loop, in-flight
-// copies get a grace period, TMEM is freed and the kernel returns with the
-// status word set.
+// time-out the CTA raises its abort word (and its partner's), every role leaves
+// its loop, in-flight copies get a grace period, TMEM is freed and the kernel
+// returns with the status word set.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include "../prim/cluster.cuh"
 #include "../prim/tcgen05.cuh"
 #include "../prim/tma.cuh"
 
 namespace cb {
 
-template <int BN_, int STAGES_, bool FP8_>
+template <int BN_, int STAGES_, bool FP8_, int PAIR_ = 1>
 struct GemmCfg {
-  static constexpr int BM = 128;
+  static constexpr int PAIR = PAIR_;          // CTAs that share a tile (1, or 2 = a cluster)
+  static constexpr int CTA_M = 128;           // accumulator rows per CTA
+  static constexpr int BM = CTA_M * PAIR_;    // tile height
   static constexpr int BN = BN_;
+  static constexpr int B_ROWS = BN_ / PAIR_;  // B rows each CTA loads
   static constexpr bool FP8 = FP8_;
   static constexpr int BK = FP8_ ? 128 : 64;  // elements per 128-byte row
   static constexpr int MMAS_PER_STAGE = 4;    // 128 B / 32 B per instruction
   static constexpr int STAGES = STAGES_;
-  static constexpr int A_BYTES = BM * 128;
-  static constexpr int B_BYTES = BN * 128;
+  static constexpr int A_BYTES = CTA_M * 128;
+  static constexpr int B_BYTES = B_ROWS * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_COLS = 64;                 // bf16 columns per store box (128 B)
   static constexpr int EPI_BUF_BYTES = 32 * 128;      // 32 rows x 128 B per warp and buffer
@@ -50,6 +67,7 @@ struct GemmCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024;
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int THREADS = 224;  // producer, MMA, 4 epilogue warps, signal warp
+  static_assert(PAIR_ == 1 || PAIR_ == 2, "one CTA or a pair per tile");
   static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN in {64,128,192,256}");
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS >= 32 && TMEM_COLS <= 512,
                 "TMEM columns must be a power of two");
@@ -60,7 +78,32 @@ struct GemmShape {
   int M, N, K;
   int num_m_blocks, num_n_blocks, num_k_blocks;
   float alpha;
+  // Optional role trace, 8 words per CTA of the launch (null = off): SM clock cycles the
+  // MMA thread spent waiting for operands [0] and for a free accumulator [1] and its total
+  // [2]; the producer's wait for free ring slots [3] and total [4]; the first epilogue
+  // warp's wait for finished accumulators [5] and total [6].
+  unsigned long long* trace = nullptr;
 };
+
+// Warp-collective mbar_wait: every lane of a converged warp calls it and all of them get the
+// same answer (a lane that saw the barrier flip at the last moment must not go on alone to a
+// `.sync.aligned` instruction or an election while its neighbours give up).  With tracing on,
+// the waiting time is added to `*acc_cycles`.
+__device__ __forceinline__ bool mbar_wait_traced(uint64_t* bar, uint32_t parity,
+                                                 volatile int* abort_flag, uint32_t* status,
+                                                 uint32_t detail, bool tracing,
+                                                 long long* acc_cycles) {
+  bool ok;
+  if (!tracing) {
+    ok = mbar_wait(bar, parity, abort_flag, status, detail);
+  } else {
+    // The whole call is timed: a try_wait may itself block for a while before it answers.
+    const long long t0 = clock64();
+    ok = mbar_wait(bar, parity, abort_flag, status, detail);
+    *acc_cycles += clock64() - t0;
+  }
+  return __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+}
 
 // Grouped rasterisation: consecutive tiles share a panel of up to `group` row
 // blocks so the CTAs that run together reuse A and B tiles out of L2.
@@ -106,33 +149,72 @@ struct GemmCtl {
 //   direct policies also: kSignalPerTile (signal warp raises a flag per tile) and
 //   kScatterRows (+ uint8_t* row_base(const P&, int m_blk, int row): per-row destinations)
 //   void tile_done(const P&, int m_blk, int n_blk, int quadrant)  after the quadrant's boxes
-//                                              were issued (one lane)
+//                                              were issued (one lane); quadrant = 4 * (CTA of
+//                                              the pair) + epilogue warp, or 4 * CTA from the
+//                                              signal warp of a direct policy
+// Producer and MMA roles are executed by a whole, converged warp: every lane follows the loop
+// and the waits, one elected lane issues the TMA loads / MMAs / commits.  Measured on B200
+// with back-to-back MMAs of 32 pipe cycles each: 43-49 cycles per instruction issued this way
+// against 61 (one CTA) / 82 (pair) from inside an `if (lane == 0)` branch, where the operands
+// of every asynchronous instruction have to be moved out of a diverged thread's registers.
+// At 4 MMAs + commits per 512 pipe cycles the branch form kept the tensor pipe idle a fifth
+// of the time although the MMA thread never waited on a barrier.
 template <class Cfg, class Policy, class P>
 __device__ __forceinline__ void gemm_producer(const P& p, const GemmShape& g, uint8_t* ring,
                                               GemmCtl<Cfg::STAGES>* ctl, uint32_t* status,
-                                              int cta, int num_ctas) {
+                                              int cta, int num_ctas, int sub) {
   uint32_t stage = 0, phase = 0;
   const int ntiles = Policy::num_tiles(p);
+  const bool tracing = g.trace != nullptr;
+  long long w_empty = 0;
+  const long long t_begin = tracing ? clock64() : 0;
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t ring_addr = smem_u32(ring);
+  const uint32_t full0 = smem_u32(&ctl->full[0]);
+  // Pair: both CTAs' bytes are counted on the even CTA's barrier, the one its MMA warp waits on.
+  const uint32_t full0_leader = Cfg::PAIR == 2 ? map_to_cta(full0, 0) : full0;
   for (int tile = cta; tile < ntiles; tile += num_ctas) {
     int m_blk, n_blk;
     Policy::tile_coord(p, tile, &m_blk, &n_blk);
-    if (!Policy::wait_a_ready(p, m_blk, &ctl->abort_flag)) return;
+    // The readiness wait polls a word that peers write: one lane only.
+    int ready = 1;
+    if (lane == 0) ready = Policy::wait_a_ready(p, m_blk, &ctl->abort_flag) ? 1 : 0;
+    if (__shfl_sync(0xffffffffu, ready, 0) == 0) return;
     const CUtensorMap* ma = Policy::map_a(p, m_blk);
     const CUtensorMap* mb = Policy::map_b(p);
-    const int arow = Policy::a_row(p, m_blk);
+    const int arow = Policy::a_row(p, m_blk) + sub * Cfg::CTA_M;
+    const int brow = Policy::b_row(p, m_blk, n_blk) + sub * Cfg::B_ROWS;
     for (int kb = 0; kb < g.num_k_blocks; ++kb) {
-      if (!mbar_wait(&ctl->empty[stage], phase ^ 1u, &ctl->abort_flag, status, 0x100 + stage))
+      if (!mbar_wait_traced(&ctl->empty[stage], phase ^ 1u, &ctl->abort_flag, status,
+                            0x100 + stage, tracing, &w_empty))
         return;
-      uint8_t* sa = ring + stage * Cfg::STAGE_BYTES;
-      uint8_t* sb = sa + Cfg::A_BYTES;
-      mbar_arrive_expect_tx(&ctl->full[stage], Cfg::STAGE_BYTES);
-      tma_load_2d(sa, ma, kb * Cfg::BK, arow, &ctl->full[stage]);
-      tma_load_2d(sb, mb, kb * Cfg::BK, Policy::b_row(p, m_blk, n_blk), &ctl->full[stage]);
+      if (elect_one()) {
+        const uint32_t sa = ring_addr + stage * Cfg::STAGE_BYTES;
+        const uint32_t sb = sa + Cfg::A_BYTES;
+        if constexpr (Cfg::PAIR == 2) {
+          // The partner's bytes may land before this expect_tx: the transaction count is
+          // allowed to run negative within a phase.
+          if (sub == 0) mbar_arrive_expect_tx_addr(full0 + stage * 8u, 2 * Cfg::STAGE_BYTES);
+          const uint32_t bar = full0_leader + stage * 8u;
+          tma_load_2d_pair(sa, ma, kb * Cfg::BK, arow, bar);
+          tma_load_2d_pair(sb, mb, kb * Cfg::BK, brow, bar);
+        } else {
+          const uint32_t bar = full0 + stage * 8u;
+          mbar_arrive_expect_tx_addr(bar, Cfg::STAGE_BYTES);
+          tma_load_2d_addr(sa, ma, kb * Cfg::BK, arow, bar);
+          tma_load_2d_addr(sb, mb, kb * Cfg::BK, brow, bar);
+        }
+      }
+      __syncwarp();
       if (++stage == Cfg::STAGES) {
         stage = 0;
         phase ^= 1u;
       }
     }
+  }
+  if (tracing && lane == 0) {
+    g.trace[blockIdx.x * 8 + 3] = static_cast<unsigned long long>(w_empty);
+    g.trace[blockIdx.x * 8 + 4] = static_cast<unsigned long long>(clock64() - t_begin);
   }
 }
 
@@ -140,39 +222,97 @@ template <class Cfg, class Policy, class P>
 __device__ __forceinline__ void gemm_mma(const P& p, const GemmShape& g, uint8_t* ring,
                                          GemmCtl<Cfg::STAGES>* ctl, uint32_t* status, int cta,
                                          int num_ctas, uint32_t tmem_base) {
-  constexpr uint32_t idesc = make_idesc(Cfg::BM, Cfg::BN, Cfg::FP8 ? 0u : 1u);
+  constexpr uint32_t idesc = make_idesc(Cfg::BM, Cfg::BN, Cfg::FP8 ? 0u : 1u);  // M = 256 for a pair
   uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
   const int ntiles = Policy::num_tiles(p);
+  const bool tracing = g.trace != nullptr;
+  long long w_full = 0, w_acc = 0;
+  const long long t_begin = tracing ? clock64() : 0;
+  const uint32_t lane = threadIdx.x & 31u;
+  // Descriptors and barrier addresses of stage 0; a stage further is a constant step.
+  const uint64_t a_desc0 = make_sw128_kmajor_desc(smem_u32(ring));
+  constexpr uint64_t kStageStep = static_cast<uint64_t>(Cfg::STAGE_BYTES >> 4);
+  constexpr uint64_t kBStep = static_cast<uint64_t>(Cfg::A_BYTES >> 4);
+  const uint32_t empty0 = smem_u32(&ctl->empty[0]);
+  const uint32_t tfull0 = smem_u32(&ctl->tmem_full[0]);
+  const uint32_t empty0_peer = Cfg::PAIR == 2 ? map_to_cta(empty0, 1) : 0u;
+  const uint32_t tfull0_peer = Cfg::PAIR == 2 ? map_to_cta(tfull0, 1) : 0u;
   for (int tile = cta; tile < ntiles; tile += num_ctas) {
-    if (!mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1u, &ctl->abort_flag, status, 0x200 + acc))
+    if (!mbar_wait_traced(&ctl->tmem_empty[acc], acc_phase ^ 1u, &ctl->abort_flag, status,
+                          0x200 + acc, tracing, &w_acc))
       return;
     tc_fence_after_sync();
     const uint32_t d_tmem = tmem_base + acc * Cfg::BN;
     for (int kb = 0; kb < g.num_k_blocks; ++kb) {
-      if (!mbar_wait(&ctl->full[stage], phase, &ctl->abort_flag, status, 0x300 + stage)) return;
+      if (!mbar_wait_traced(&ctl->full[stage], phase, &ctl->abort_flag, status, 0x300 + stage,
+                            tracing, &w_full))
+        return;
       tc_fence_after_sync();
-      const uint32_t sa = smem_u32(ring + stage * Cfg::STAGE_BYTES);
-      const uint64_t a_desc = make_sw128_kmajor_desc(sa);
-      const uint64_t b_desc = make_sw128_kmajor_desc(sa + Cfg::A_BYTES);
+      if (elect_one()) {
+        const uint64_t a_desc = a_desc0 + stage * kStageStep;
+        const uint64_t b_desc = a_desc + kBStep;
 #pragma unroll
-      for (int k = 0; k < Cfg::MMAS_PER_STAGE; ++k) {
-        // 32 bytes along K per instruction: +2 in the descriptor's 16-byte address units.
-        const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
-        if constexpr (Cfg::FP8)
-          mma_fp8_ss(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
-        else
-          mma_bf16_ss(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
+        for (int k = 0; k < Cfg::MMAS_PER_STAGE; ++k) {
+          // 32 bytes along K per instruction: +2 in the descriptor's 16-byte address units.
+          const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+          if constexpr (Cfg::PAIR == 2) {
+            if constexpr (Cfg::FP8)
+              mma_fp8_ss_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
+            else
+              mma_bf16_ss_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
+          } else {
+            if constexpr (Cfg::FP8)
+              mma_fp8_ss(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
+            else
+              mma_bf16_ss(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
+          }
+        }
+        // The ring slot is free once these MMAs have read it (in both CTAs of a pair).
+        if constexpr (Cfg::PAIR == 2) {
+          mma_commit_pair(empty0 + stage * 8u);
+          mma_commit_pair(empty0_peer + stage * 8u);
+        } else {
+          mma_commit_addr(empty0 + stage * 8u);
+        }
       }
-      mma_commit(&ctl->empty[stage]);  // ring slot is free once these MMAs have read it
+      __syncwarp();
       if (++stage == Cfg::STAGES) {
         stage = 0;
         phase ^= 1u;
       }
     }
-    mma_commit(&ctl->tmem_full[acc]);  // accumulator complete
+    // Accumulator complete.
+    if (elect_one()) {
+      if constexpr (Cfg::PAIR == 2) {
+        mma_commit_pair(tfull0 + acc * 8u);
+        mma_commit_pair(tfull0_peer + acc * 8u);
+      } else {
+        mma_commit_addr(tfull0 + acc * 8u);
+      }
+    }
+    __syncwarp();
     acc ^= 1u;
     if (acc == 0u) acc_phase ^= 1u;
   }
+  if (tracing && lane == 0) {
+    g.trace[blockIdx.x * 8 + 0] = static_cast<unsigned long long>(w_full);
+    g.trace[blockIdx.x * 8 + 1] = static_cast<unsigned long long>(w_acc);
+    g.trace[blockIdx.x * 8 + 2] = static_cast<unsigned long long>(clock64() - t_begin);
+  }
+}
+
+// One epilogue warp has read accumulator `acc` for the last time: tell the MMA thread (which
+// lives in the even CTA of a pair).
+template <class Cfg>
+__device__ __forceinline__ void release_accumulator(GemmCtl<Cfg::STAGES>* ctl, uint32_t acc,
+                                                    int sub) {
+  if constexpr (Cfg::PAIR == 2) {
+    if (sub != 0) {
+      mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->tmem_empty[acc]), 0));
+      return;
+    }
+  }
+  mbar_arrive(&ctl->tmem_empty[acc]);
 }
 
 // fp32 accumulator row (64 columns) -> bf16, written into a [32 rows][128 B]
@@ -231,6 +371,41 @@ __device__ __forceinline__ void epi_write_row_256(uint8_t* buf, uint32_t lane, i
   }
 }
 
+// A direct policy may declare `static constexpr bool kReduceLocal = true`: tiles for which
+// `tile_is_local(p, m_blk)` holds are then not sent anywhere; the epilogue adds the staged
+// partial tiles that other ranks sent for them (fp32, fixed order) to its own accumulator
+// and writes the final rows, so the reduction of a reduce-scatter overlaps the main loop of
+// the next tile and the local partial never travels through memory.
+//   bool tile_is_local(const P&, int m_blk)
+//   bool wait_local_ready(const P&, int m_blk, int n_blk, int sub)   (one lane per warp)
+//   void local_reduce(const P&, int m_blk, int n_blk, LocalReduce*)
+struct LocalReduce {
+  int nsrc;               // staged copies to add (0..7)
+  const uint8_t* src[7];  // address of (tile row 0, tile column 0) in each copy
+  long long src_ld;       // row pitch of the copies, bytes
+  uint8_t* out;           // address of (tile row 0, tile column 0) of the result
+  long long out_ld;
+};
+template <class Policy>
+__host__ __device__ constexpr bool policy_reduce_local() {
+  if constexpr (requires { Policy::kReduceLocal; }) {
+    return Policy::kReduceLocal;
+  } else {
+    return false;
+  }
+}
+
+// bf16x8 (+)= bf16x8 in fp32.
+__device__ __forceinline__ void acc_bf16x8(float (&a)[8], const uint4& v) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 t = __bfloat1622float2(h[k]);
+    a[2 * k] += t.x;
+    a[2 * k + 1] += t.y;
+  }
+}
+
 // Epilogue for policies with `kDirect`: accumulator -> bf16 -> shared memory
 // (transposition) -> row-contiguous 16-byte global stores, 256 bytes per row and
 // half-warp.  Used where the destination is another GPU: load/store traffic
@@ -240,7 +415,7 @@ __device__ __forceinline__ void gemm_epilogue_direct(const P& p, const GemmShape
                                                      uint8_t* epi_smem,
                                                      GemmCtl<Cfg::STAGES>* ctl, uint32_t* status,
                                                      int cta, int num_ctas, uint32_t tmem_base,
-                                                     uint32_t warp, uint32_t lane) {
+                                                     uint32_t warp, uint32_t lane, int sub) {
   const uint32_t q = warp & 3u;
   uint8_t* buf = epi_smem + q * (2 * Cfg::EPI_BUF_BYTES);  // 8 KB: 32 rows x 256 B
   uint32_t acc = 0, acc_phase = 0, seq = 0;
@@ -251,8 +426,25 @@ __device__ __forceinline__ void gemm_epilogue_direct(const P& p, const GemmShape
     Policy::tile_coord(p, tile, &m_blk, &n_blk);
     DirectTargets tg;
     Policy::direct_targets(p, m_blk, n_blk, &tg);
-    if (!mbar_wait(&ctl->tmem_full[acc], acc_phase, &ctl->abort_flag, status, 0x400 + acc)) return;
+    if (!mbar_wait_traced(&ctl->tmem_full[acc], acc_phase, &ctl->abort_flag, status, 0x400 + acc,
+                          false, nullptr))
+      return;
     tc_fence_after_sync();
+    constexpr bool kReduce = policy_reduce_local<Policy>();
+    bool local_tile = false;
+    LocalReduce lr;
+    if constexpr (kReduce) {
+      local_tile = Policy::tile_is_local(p, m_blk);
+      if (local_tile) {
+        Policy::local_reduce(p, m_blk, n_blk, &lr);
+        int ok = 1;
+        if (lane == 0 && lr.nsrc > 0) ok = Policy::wait_local_ready(p, m_blk, n_blk, sub) ? 1 : 0;
+        if (__shfl_sync(0xffffffffu, ok, 0) == 0) {
+          ctl->abort_flag = 1;
+          return;
+        }
+      }
+    }
 #pragma unroll 1
     for (int h = 0; h < HALVES; ++h) {
       constexpr int CH = Cfg::BN >= 128 ? 2 : 1;  // 64-column chunks per half
@@ -267,7 +459,7 @@ __device__ __forceinline__ void gemm_epilogue_direct(const P& p, const GemmShape
         if (h == HALVES - 1 && cc == CH - 1) {
           tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&ctl->tmem_empty[acc]);
+          if (lane == 0) release_accumulator<Cfg>(ctl, acc, sub);
         }
         epi_write_row_256(buf, lane, cc, r0, r1, g.alpha);
       }
@@ -276,10 +468,53 @@ __device__ __forceinline__ void gemm_epilogue_direct(const P& p, const GemmShape
       const uint32_t idx = lane & 15u;
       const int col = h * 128 + static_cast<int>(idx) * 8;
       const bool col_ok = (static_cast<int>(idx) < CH * 8) && col < tg.cols;
+      if constexpr (kReduce) {
+        if (local_tile) {
+          // Two rows per lane and step, every staged copy of both loaded before the sums.
+#pragma unroll 1
+          for (int i0 = 0; i0 < 16; i0 += 2) {
+            uint4 parts[2][7];
+            bool okr[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const uint32_t r = 2u * (i0 + u) + (lane >> 4);
+              const int row = sub * Cfg::CTA_M + static_cast<int>(q * 32u + r);
+              okr[u] = col_ok && row < tg.rows;
+              const long long off = row * lr.src_ld + col * 2ll;
+#pragma unroll
+              for (int sidx = 0; sidx < 7; ++sidx)
+                if (okr[u] && sidx < lr.nsrc)
+                  parts[u][sidx] = __ldcg(reinterpret_cast<const uint4*>(lr.src[sidx] + off));
+            }
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              if (!okr[u]) continue;
+              const uint32_t r = 2u * (i0 + u) + (lane >> 4);
+              const int row = sub * Cfg::CTA_M + static_cast<int>(q * 32u + r);
+              const uint4 own =
+                  *reinterpret_cast<const uint4*>(buf + r * 256u + ((idx ^ (r & 7u)) * 16u));
+              float a[8];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) a[k] = 0.f;
+              acc_bf16x8(a, own);
+#pragma unroll
+              for (int sidx = 0; sidx < 7; ++sidx)
+                if (sidx < lr.nsrc) acc_bf16x8(a, parts[u][sidx]);
+              uint4 o;
+              __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(a[2 * k], a[2 * k + 1]);
+              st_v4(lr.out + row * lr.out_ld + col * 2ll, o);
+            }
+          }
+          __syncwarp();
+          continue;
+        }
+      }
 #pragma unroll 4
       for (int i = 0; i < 16; ++i) {
         const uint32_t r = 2u * i + (lane >> 4);
-        const int row = static_cast<int>(q * 32u + r);
+        const int row = sub * Cfg::CTA_M + static_cast<int>(q * 32u + r);
         const uint4 v = *reinterpret_cast<const uint4*>(buf + r * 256u + ((idx ^ (r & 7u)) * 16u));
         if constexpr (Policy::kScatterRows) {
           // Every output row has its own destination (MoE combine): look it up.
@@ -295,14 +530,16 @@ __device__ __forceinline__ void gemm_epilogue_direct(const P& p, const GemmShape
     // Hand the tile to the signal warp: it runs the (slow, ~20 us under store traffic)
     // system-scope fence and raises the flag while these warps go on with the next tile.
     __syncwarp();
-    if (Policy::kSignalPerTile && lane == 0) {
-      const uint32_t slot = seq & 7u;
-      if (!mbar_wait(&ctl->sig_empty[slot], ((seq >> 3) & 1u) ^ 1u, &ctl->abort_flag, status,
-                     0x800 + slot))
-        return;
-      mbar_arrive(&ctl->sig_full[slot]);
+    if (Policy::kSignalPerTile && !local_tile) {
+      if (lane == 0) {
+        const uint32_t slot = seq & 7u;
+        if (!mbar_wait(&ctl->sig_empty[slot], ((seq >> 3) & 1u) ^ 1u, &ctl->abort_flag, status,
+                       0x800 + slot))
+          return;
+        mbar_arrive(&ctl->sig_full[slot]);
+      }
+      ++seq;  // sequence of signalled tiles only
     }
-    ++seq;
     acc ^= 1u;
     if (acc == 0u) acc_phase ^= 1u;
   }
@@ -317,13 +554,24 @@ __device__ __forceinline__ void gemm_epilogue_direct(const P& p, const GemmShape
 // lane, which synchronised with this thread through the mbarrier.
 template <class Cfg, class Policy, class P>
 __device__ __forceinline__ void gemm_signal(const P& p, GemmCtl<Cfg::STAGES>* ctl,
-                                            uint32_t* status, int cta, int num_ctas) {
+                                            uint32_t* status, int cta, int num_ctas, int sub) {
   uint32_t seq = 0;
   const int ntiles = Policy::num_tiles(p);
   int pend_m[4], pend_n[4];
   int npend = 0;
   int tile = cta;
   while (tile < ntiles || npend > 0) {
+    if constexpr (policy_reduce_local<Policy>()) {
+      // Tiles that are reduced in place are not signalled to anybody.
+      if (tile < ntiles) {
+        int m_blk, n_blk;
+        Policy::tile_coord(p, tile, &m_blk, &n_blk);
+        if (Policy::tile_is_local(p, m_blk)) {
+          tile += num_ctas;
+          continue;
+        }
+      }
+    }
     if (tile < ntiles && npend < 4) {
       const uint32_t slot = seq & 7u;
       const uint32_t par = (seq >> 3) & 1u;
@@ -342,7 +590,7 @@ __device__ __forceinline__ void gemm_signal(const P& p, GemmCtl<Cfg::STAGES>* ct
       }
     }
     fence_acq_rel_sys();  // release; a sequentially-consistent fence costs far more here
-    for (int i = 0; i < npend; ++i) Policy::tile_done(p, pend_m[i], pend_n[i], 0);
+    for (int i = 0; i < npend; ++i) Policy::tile_done(p, pend_m[i], pend_n[i], sub * 4);
     npend = 0;
   }
 }
@@ -377,15 +625,20 @@ __device__ __forceinline__ void gemm_epilogue_tma(const P& p, const GemmShape& g
                                                   uint8_t* epi_smem, GemmCtl<Cfg::STAGES>* ctl,
                                                   uint32_t* status, int cta, int num_ctas,
                                                   uint32_t tmem_base, uint32_t warp,
-                                                  uint32_t lane) {
+                                                  uint32_t lane, int sub) {
   const uint32_t q = warp & 3u;  // TMEM lane quadrant this warp may read
   uint8_t* bufs = epi_smem + q * (2 * Cfg::EPI_BUF_BYTES);
   uint32_t acc = 0, acc_phase = 0, buf = 0;
   const int ntiles = Policy::num_tiles(p);
+  const bool tracing = g.trace != nullptr && q == 0 && lane == 0;
+  long long w_tfull = 0;
+  const long long t_begin = tracing ? clock64() : 0;
   for (int tile = cta; tile < ntiles; tile += num_ctas) {
     int m_blk, n_blk;
     Policy::tile_coord(p, tile, &m_blk, &n_blk);
-    if (!mbar_wait(&ctl->tmem_full[acc], acc_phase, &ctl->abort_flag, status, 0x400 + acc)) return;
+    if (!mbar_wait_traced(&ctl->tmem_full[acc], acc_phase, &ctl->abort_flag, status, 0x400 + acc,
+                          tracing, &w_tfull))
+      return;
     tc_fence_after_sync();
     constexpr bool kGated = policy_gated<Policy>();
     constexpr int kBoxes = Cfg::BN / Cfg::EPI_COLS / (kGated ? 2 : 1);  // store boxes per tile
@@ -412,7 +665,7 @@ __device__ __forceinline__ void gemm_epilogue_tma(const P& p, const GemmShape& g
         // Last read of this accumulator: hand it back to the MMA thread.
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl->tmem_empty[acc]);
+        if (lane == 0) release_accumulator<Cfg>(ctl, acc, sub);
       }
       // The buffer we are about to fill was read by the store issued two boxes ago.
       if (lane == 0) bulk_wait_read<1>();
@@ -422,29 +675,34 @@ __device__ __forceinline__ void gemm_epilogue_tma(const P& p, const GemmShape& g
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        Policy::store_box(p, m_blk, n_blk, static_cast<int>(q * 32u), c * Cfg::EPI_COLS, b);
+        Policy::store_box(p, m_blk, n_blk, sub * Cfg::CTA_M + static_cast<int>(q * 32u),
+                          c * Cfg::EPI_COLS, b);
         bulk_commit();
       }
       buf ^= 1u;
     }
-    if (lane == 0) Policy::tile_done(p, m_blk, n_blk, static_cast<int>(q));
+    if (lane == 0) Policy::tile_done(p, m_blk, n_blk, sub * 4 + static_cast<int>(q));
     acc ^= 1u;
     if (acc == 0u) acc_phase ^= 1u;
   }
   if (lane == 0) bulk_wait_all<0>();
+  if (tracing) {
+    g.trace[blockIdx.x * 8 + 5] = static_cast<unsigned long long>(w_tfull);
+    g.trace[blockIdx.x * 8 + 6] = static_cast<unsigned long long>(clock64() - t_begin);
+  }
 }
 
 template <class Cfg, class Policy, class P>
 __device__ __forceinline__ void gemm_epilogue(const P& p, const GemmShape& g, uint8_t* epi_smem,
                                               GemmCtl<Cfg::STAGES>* ctl, uint32_t* status,
                                               int cta, int num_ctas, uint32_t tmem_base,
-                                              uint32_t warp, uint32_t lane) {
+                                              uint32_t warp, uint32_t lane, int sub) {
   if constexpr (Policy::kDirect) {
     gemm_epilogue_direct<Cfg, Policy>(p, g, epi_smem, ctl, status, cta, num_ctas, tmem_base, warp,
-                                      lane);
+                                      lane, sub);
   } else {
     gemm_epilogue_tma<Cfg, Policy>(p, g, epi_smem, ctl, status, cta, num_ctas, tmem_base, warp,
-                                   lane);
+                                   lane, sub);
   }
 }
 
@@ -463,7 +721,7 @@ __device__ __forceinline__ uint32_t gemm_setup(GemmCtl<Cfg::STAGES>* ctl, uint32
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&ctl->tmem_full[a], 1);
-      mbar_init(&ctl->tmem_empty[a], 4);  // one arrival per epilogue warp
+      mbar_init(&ctl->tmem_empty[a], 4 * Cfg::PAIR);  // one arrival per epilogue warp (of the pair)
     }
     for (int i = 0; i < 8; ++i) {
       mbar_init(&ctl->sig_full[i], 4);
@@ -473,11 +731,21 @@ __device__ __forceinline__ uint32_t gemm_setup(GemmCtl<Cfg::STAGES>* ctl, uint32
     fence_mbar_init();
   }
   if (warp == 1) {
-    tmem_alloc(&ctl->tmem_base, Cfg::TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (Cfg::PAIR == 2) {
+      tmem_alloc_pair(&ctl->tmem_base, Cfg::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&ctl->tmem_base, Cfg::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (Cfg::PAIR == 2) {
+    // The partner arrives on this CTA's barriers: they must be initialised before it starts.
+    cluster_sync_all();
+  } else {
+    __syncthreads();
+  }
   tc_fence_after_sync();
   return *reinterpret_cast<volatile uint32_t*>(&ctl->tmem_base);
 }
@@ -486,17 +754,29 @@ template <class Cfg>
 __device__ __forceinline__ void gemm_teardown(GemmCtl<Cfg::STAGES>* ctl, uint32_t warp,
                                               uint32_t tmem_base) {
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (Cfg::PAIR == 2) {
+    // A role that gave up tells the partner CTA, whose roles may still be waiting for it.
+    __syncwarp();
+    if ((threadIdx.x & 31u) == 0 && *reinterpret_cast<volatile int*>(&ctl->abort_flag) != 0)
+      st_cluster_u32(map_to_cta(smem_u32(&ctl->abort_flag), cluster_ctarank() ^ 1u), 1u);
+    // Nobody leaves while the partner may still arrive on this CTA's barriers or while the
+    // even CTA's MMAs may still read this CTA's operand ring.
+    cluster_sync_all();
+  } else {
+    __syncthreads();
+  }
   if (*reinterpret_cast<volatile int*>(&ctl->abort_flag) != 0) {
     // Some wait gave up: loads may still be landing in this CTA's shared memory.
     // Give them a bounded grace period before the CTA (and its memory) goes away.
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
-    __syncthreads();
+    if constexpr (Cfg::PAIR == 2) cluster_sync_all();
+    else __syncthreads();
   }
   if (warp == 1) {
     __syncwarp();
-    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    if constexpr (Cfg::PAIR == 2) tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
+    else tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
 
@@ -517,15 +797,19 @@ __device__ __forceinline__ void gemm_cta_main(const P& p, const GemmShape& g, ui
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t tmem_base = gemm_setup<Cfg>(&ctl, warp);
+  // A pair walks the tile list as one worker; `sub` is this CTA's half of every tile.
+  const int sub = Cfg::PAIR == 2 ? static_cast<int>(cluster_ctarank()) : 0;
+  const int worker = cta / Cfg::PAIR, num_workers = num_ctas / Cfg::PAIR;
   if (warp == 0) {
-    if (lane == 0) gemm_producer<Cfg, Policy>(p, g, ring, &ctl, status, cta, num_ctas);
+    gemm_producer<Cfg, Policy>(p, g, ring, &ctl, status, worker, num_workers, sub);
   } else if (warp == 1) {
-    if (lane == 0) gemm_mma<Cfg, Policy>(p, g, ring, &ctl, status, cta, num_ctas, tmem_base);
+    if (sub == 0) gemm_mma<Cfg, Policy>(p, g, ring, &ctl, status, worker, num_workers, tmem_base);
   } else if (warp < 6) {
-    gemm_epilogue<Cfg, Policy>(p, g, epi, &ctl, status, cta, num_ctas, tmem_base, warp, lane);
+    gemm_epilogue<Cfg, Policy>(p, g, epi, &ctl, status, worker, num_workers, tmem_base, warp,
+                               lane, sub);
   } else {
     if constexpr (Policy::kDirect && Policy::kSignalPerTile) {
-      if (lane == 0) gemm_signal<Cfg, Policy>(p, &ctl, status, cta, num_ctas);
+      if (lane == 0) gemm_signal<Cfg, Policy>(p, &ctl, status, worker, num_workers, sub);
     }
   }
   __syncwarp();

@@ -118,6 +118,65 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
                : "memory");
 }
 
+__device__ __forceinline__ void mma_commit_addr(uint32_t bar_addr) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar_addr)
+               : "memory");
+}
+
+// ------------------------------------------------- CTA pairs (cta_group::2)
+// A pair is the two CTAs of a cluster of 2.  Both CTAs run the allocation and
+// the free (same warp index, same shared-memory word), the even CTA issues the
+// MMAs: one instruction drives both tensor cores, CTA r computes rows
+// 128r..128r+127 of the 256-row tile into its own TMEM from its own A half and
+// BOTH CTAs' B halves (B rows N/2 * r .. of the tile live in CTA r).
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(smem_result)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void mma_bf16_ss_pair(uint32_t d_tmem, uint64_t a_desc,
+                                                 uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_fp8_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Completion of every MMA issued so far by this thread -> one arrival on the
+// mbarrier at `cluster_addr` (a shared::cluster address: this CTA's or the
+// partner's).  Two commits in a row track the same MMAs, which is how both
+// CTAs of a pair are told without a multicast form.
+__device__ __forceinline__ void mma_commit_pair(uint32_t cluster_addr) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+          cluster_addr)
+      : "memory");
+}
+
 // ------------------------------------------------------------------ TMEM load
 // 32 lanes x 32 consecutive fp32 columns: thread t of the warp receives row
 // (lane base + t), columns col .. col+31.  taddr = (lane << 16) | column.

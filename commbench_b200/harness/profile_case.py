@@ -44,6 +44,8 @@ def main(argv=None) -> int:
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--launches", type=int, default=3)
+    ap.add_argument("--bn", type=int, default=0,
+                    help="gemm tile selector (0 = chosen from the shape; 512 = CTA pair, 256x256)")
     a = ap.parse_args(argv)
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -60,8 +62,8 @@ def main(argv=None) -> int:
         else:
             A, B = A.bfloat16(), B.bfloat16()
         C = torch.empty(a.m, a.n, dtype=torch.bfloat16, device=dev)
-        ms = _time(lambda: gemm(A, B, out=C), a.launches)
-        out.update(shape=[a.m, a.n, a.k], ms=ms, tflops=2.0 * a.m * a.n * a.k / ms / 1e9)
+        ms = _time(lambda: gemm(A, B, out=C, bn=a.bn), a.launches)
+        out.update(shape=[a.m, a.n, a.k], bn=a.bn, ms=ms, tflops=2.0 * a.m * a.n * a.k / ms / 1e9)
     elif a.case == "attn":
         from ..ops.cp import flash_attention
 

@@ -52,6 +52,37 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, alph
     return out
 
 
+def gemm_role_trace(a: torch.Tensor, b: torch.Tensor, bn: int = 512) -> dict:
+    """Runs one bf16 GEMM with the kernel's role trace on and returns, per role, the mean
+    share of its time spent waiting (SM clock cycles, averaged over the CTAs that had work):
+    ``mma_wait_operands``, ``mma_wait_accumulator``, ``producer_wait_slots``,
+    ``epilogue_wait_accumulator``, plus ``mma_cycles`` (mean total of the MMA thread)."""
+    lib = N.load()
+    _check(a, "a")
+    _check(b, "b")
+    M, K = a.shape
+    Nn = b.shape[0]
+    out = torch.empty((M, Nn), dtype=torch.bfloat16, device=a.device)
+    nsm = torch.cuda.get_device_properties(a.device).multi_processor_count
+    trace = torch.zeros(nsm * 8, dtype=torch.int64, device=a.device)
+    rc = lib.cb_gemm_bf16_traced(N.ptr(a), N.ptr(b), N.ptr(out), M, Nn, K, C.c_float(1.0), bn,
+                                 N.ptr(trace), C.c_void_p(0), N.stream_ptr())
+    if rc != 0:
+        raise GemmError(f"gemm launch failed: {N.last_error()}")
+    torch.cuda.synchronize()
+    t = trace.view(nsm, 8).double().cpu()
+    mma = t[t[:, 2] > 0]
+    prod = t[t[:, 4] > 0]
+    epi = t[t[:, 6] > 0]
+    return {
+        "mma_cycles": float(mma[:, 2].mean()) if len(mma) else 0.0,
+        "mma_wait_operands": float((mma[:, 0] / mma[:, 2]).mean()) if len(mma) else 0.0,
+        "mma_wait_accumulator": float((mma[:, 1] / mma[:, 2]).mean()) if len(mma) else 0.0,
+        "producer_wait_slots": float((prod[:, 3] / prod[:, 4]).mean()) if len(prod) else 0.0,
+        "epilogue_wait_accumulator": float((epi[:, 5] / epi[:, 6]).mean()) if len(epi) else 0.0,
+    }
+
+
 # ------------------------------------------------------------- block-scaled fp8 operands
 def quantize_blockscaled(x: torch.Tensor, row_block: int = 1):
     """bf16 [rows, K] -> (e4m3 [rows, K], fp32 scales).  ``row_block=1``: one scale per row and

@@ -121,7 +121,16 @@ class _FusedBase:
 
     def _ctas(self) -> int:
         sms = _sm_count(self.ctx.device)
-        return sms // self.world if self.emu else sms
+        n = sms // self.world if self.emu else sms
+        return n - n % 2      # CTA-pair tiles run as clusters of two
+
+    def _pick_bn(self, M: int, Nn: int) -> int:
+        """512 = a CTA pair (`tcgen05.mma.cta_group::2`) per 256 x 256 tile, the fastest form,
+        whenever every rank owns whole 256-row blocks and there is at least one wave of such
+        tiles; otherwise one CTA per 128 x 256 tile."""
+        if M % (self.world * 256) == 0 and (M // 256) * ((Nn + 255) // 256) * 2 >= self._ctas():
+            return 512
+        return 256
 
     def _sync_init(self):
         torch.cuda.synchronize(self.ctx.device)
@@ -163,7 +172,7 @@ class AgGemm(_FusedBase):
         return d
 
     @traced("cb200.ag_gemm")
-    def __call__(self, a_local, b, out=None, alpha: float = 1.0, bn: int = 256,
+    def __call__(self, a_local, b, out=None, alpha: float = 1.0, bn: int | None = None,
                  comm_ctas: int | None = None, parts: int | None = None, use_mc: bool = True,
                  stream=None):
         cfg = get_config()
@@ -171,6 +180,7 @@ class AgGemm(_FusedBase):
             comm_ctas = cfg.ag_gemm_comm_ctas if self.world > 1 else 0
         if self.emu:
             comm_ctas = min(comm_ctas, 4) if self.world > 1 else 0
+        comm_ctas += comm_ctas % 2
         if parts is None:
             parts = max(comm_ctas, 1)   # every comm CTA works on the same row block
         if self.emu:
@@ -182,6 +192,8 @@ class AgGemm(_FusedBase):
         M = Ml * self.world
         if M > self.max_m or K != self.k:
             raise CommError(f"AgGemm built for M<={self.max_m}, K={self.k}; got M={M}, K={K}")
+        if bn is None:
+            bn = self._pick_bn(M, Nn)
         if self.emu:
             outs = out or [torch.empty((M, Nn), dtype=torch.bfloat16, device=a0.device)
                            for _ in range(self.world)]
@@ -229,12 +241,14 @@ class GemmRs(_FusedBase):
         return d
 
     @traced("cb200.gemm_rs")
-    def __call__(self, a, b, out=None, alpha: float = 1.0, bn: int = 256, stream=None):
+    def __call__(self, a, b, out=None, alpha: float = 1.0, bn: int | None = None, stream=None):
         a0, b0 = (a[0], b[0]) if self.emu else (a, b)
         M, K = a0.shape
         Nn = b0.shape[0]
         if M > self.max_m or Nn > self.max_n:
             raise CommError(f"GemmRs built for M<={self.max_m}, N<={self.max_n}")
+        if bn is None:
+            bn = self._pick_bn(M, Nn)
         fp8 = a0.dtype == torch.float8_e4m3fn
         Ml = M // self.world
         if self.emu:

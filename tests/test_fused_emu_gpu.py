@@ -17,8 +17,9 @@ def _close(out, ref, tol=1.5e-2):
     assert err / scale < tol, f"max abs err {err} vs scale {scale}"
 
 
+# bn 512 = a CTA pair (cluster of two) per 256 x 256 tile.
 @pytest.mark.parametrize("world", [2, 4])
-@pytest.mark.parametrize("bn", [256, 128])
+@pytest.mark.parametrize("bn", [512, 256, 128])
 def test_emu_ag_gemm(native_lib, world, bn):
     from commbench_b200.ops.tp import AgGemm
     from commbench_b200.runtime.context import EmuContext
@@ -48,8 +49,30 @@ def test_emu_gemm_rs(native_lib, world):
     b = [_rand((Nn, K), 200 + r) for r in range(world)]
     total = sum(a[r].float() @ b[r].float().t() for r in range(world))
     Ml = M // world
-    for it in range(3):
-        outs = op(a, b, bn=128 if it == 1 else 256)
+    for it in range(4):
+        outs = op(a, b, bn=(256, 128, 512, 512)[it])
+        ctx.check_status()
+        for r in range(world):
+            _close(outs[r], total[r * Ml:(r + 1) * Ml])
+
+
+@pytest.mark.parametrize("bn", [512, 256])
+def test_emu_gemm_rs_many_tiles_per_owner(native_lib, bn):
+    """Several row and column blocks per owner, so that remote partials of a tile arrive
+    while other tiles are in flight, over six calls (both parities, counters cleared)."""
+    from commbench_b200.ops.tp import GemmRs
+    from commbench_b200.runtime.context import EmuContext
+
+    world = 2
+    M, K, Nn = 1024 * world, 192, 1024 + 64
+    ctx = EmuContext(world)
+    op = GemmRs(ctx, max_m=M, max_n=Nn)
+    a = [_rand((M, K), 500 + r) for r in range(world)]
+    b = [_rand((Nn, K), 600 + r) for r in range(world)]
+    total = sum(a[r].float() @ b[r].float().t() for r in range(world))
+    Ml = M // world
+    for it in range(6):
+        outs = op(a, b, bn=bn)
         ctx.check_status()
         for r in range(world):
             _close(outs[r], total[r * Ml:(r + 1) * Ml])

@@ -15,7 +15,9 @@ def _check(out, ref, tol):
     assert err / scale < tol, f"max abs err {err} vs scale {scale}"
 
 
-@pytest.mark.parametrize("bn", [256, 128, 64])
+# bn 512 / 384 = a CTA pair (cluster of two, `tcgen05.mma.cta_group::2`) per 256 x 256 /
+# 256 x 128 tile; the others one CTA per 128 x bn tile.
+@pytest.mark.parametrize("bn", [512, 384, 256, 128, 64])
 @pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (384, 768, 1024),
                                    (1000, 1304, 520), (16, 8192, 1024)])
 def test_gemm_bf16_matches_fp32_reference(native_lib, shape, bn):
@@ -25,9 +27,25 @@ def test_gemm_bf16_matches_fp32_reference(native_lib, shape, bn):
     g = torch.Generator(device="cuda").manual_seed(1234 + M + N + K)
     a = torch.randn(M, K, device="cuda", generator=g).mul_(0.5).bfloat16()
     b = torch.randn(N, K, device="cuda", generator=g).mul_(0.5).bfloat16()
-    out = gemm(a, b, bn=bn)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    out = gemm(a, b, bn=bn, status_ptr=status.data_ptr())
     torch.cuda.synchronize()
+    assert int(status[0].item()) == 0, hex(int(status[0].item()) & 0xffffffff)
     _check(out, _ref(a, b), 1e-2)
+
+
+def test_gemm_pair_every_element_exact_on_small_ints(native_lib):
+    """CTA-pair tiles: integer-valued inputs make fp32 accumulation exact, so a row or column
+    half that lands in the wrong place shows up as a mismatch, not as noise."""
+    from commbench_b200.ops.gemm import gemm
+
+    M, N, K = 768, 1024, 320
+    g = torch.Generator(device="cuda").manual_seed(11)
+    a = torch.randint(-3, 4, (M, K), device="cuda", generator=g).bfloat16()
+    b = torch.randint(-3, 4, (N, K), device="cuda", generator=g).bfloat16()
+    for bn in (512, 384):
+        out = gemm(a, b, bn=bn)
+        assert torch.equal(out.float(), _ref(a, b).bfloat16().float()), bn
 
 
 def test_gemm_bf16_full_tensor_exact_on_small_ints(native_lib):
@@ -64,6 +82,8 @@ def test_gemm_fp8_matches_fp32_reference(native_lib, shape):
     b = torch.randn(N, K, device="cuda", generator=g).to(torch.float8_e4m3fn)
     out = gemm(a, b, alpha=0.25, bn=128)
     _check(out, _ref(a, b, 0.25), 1e-2)
+    out2 = gemm(a, b, alpha=0.25, bn=512)  # CTA pair
+    _check(out2, _ref(a, b, 0.25), 1e-2)
 
 
 def test_blockscaled_fp8_roundtrip_and_gemm(native_lib):

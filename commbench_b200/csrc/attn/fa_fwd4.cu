@@ -225,46 +225,65 @@ __global__ void __launch_bounds__(F4_THREADS, 1) fa_fwd4_kernel(const __grid_con
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && nblk_max > 0) {
+    if (nblk_max > 0) {
       // --------------------------------------------------------------------- MMA
+      // The whole warp walks the schedule and waits; one elected lane issues the MMAs and
+      // commits.  (Issued from inside an `if (lane == 0)` branch, a 128 x 128 x 16 MMA cost
+      // ~60 cycles of issue against 64 cycles on the tensor pipe, so the issuing thread, not the
+      // pipe or the softmax, set the pace.)
       constexpr uint32_t idesc_s = make_idesc(128, 128, 1u);
       constexpr uint32_t idesc_pv = make_idesc(128, 128, 1u) | (1u << 16);  // B (= V) is MN-major
       const int nb[2] = {nblk0, nblk1};
-      bool ok = mbar_wait(&ctl.q_full, 0, &ctl.abort_flag, p.status, 0xD10);
+      const uint64_t q_desc0 = make_sw128_kmajor_desc(smem_u32(sQ));
+      const uint64_t k_desc0 = make_sw128_kmajor_desc(smem_u32(sK));
+      const uint64_t v_desc0 = f4_mnmajor_desc(smem_u32(sV));
+      constexpr uint64_t kTileStep = static_cast<uint64_t>(F4_TILE >> 4);
+      constexpr uint64_t kSubStep = static_cast<uint64_t>(F4_SUB >> 4);
+      auto wait_all = [&](uint64_t* bar, uint32_t parity, uint32_t detail) -> bool {
+        const bool w = mbar_wait(bar, parity, &ctl.abort_flag, p.status, detail);
+        return __all_sync(0xffffffffu, w ? 1 : 0) != 0;
+      };
+      bool ok = wait_all(&ctl.q_full, 0, 0xD10);
       auto issue_qk = [&](int t, int j) -> bool {
         const int s = j % F4_KST;
-        if (!mbar_wait(&ctl.k_full[s], (j / F4_KST) & 1, &ctl.abort_flag, p.status, 0xD11)) return false;
+        if (!wait_all(&ctl.k_full[s], (j / F4_KST) & 1, 0xD11)) return false;
         tc_fence_after_sync();
-        const uint32_t qa = smem_u32(sQ + t * F4_TILE), ka = smem_u32(sK + s * F4_TILE);
+        if (elect_one()) {
+          const uint64_t qa = q_desc0 + t * kTileStep, ka = k_desc0 + s * kTileStep;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint64_t a_desc = make_sw128_kmajor_desc(qa + (kk >> 2) * F4_SUB) + 2u * (kk & 3);
-          const uint64_t b_desc = make_sw128_kmajor_desc(ka + (kk >> 2) * F4_SUB) + 2u * (kk & 3);
-          mma_bf16_ss(tmem + 256u * t, a_desc, b_desc, idesc_s, kk > 0 ? 1u : 0u);
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t off = (kk >> 2) * kSubStep + 2u * (kk & 3);
+            mma_bf16_ss(tmem + 256u * t, qa + off, ka + off, idesc_s, kk > 0 ? 1u : 0u);
+          }
+          mma_commit(&ctl.s_full[t]);
         }
-        mma_commit(&ctl.s_full[t]);
+        __syncwarp();
         return true;
       };
       auto issue_pv = [&](int t, int j) -> bool {
         const int s = j % F4_VST;
-        if (!mbar_wait(&ctl.p_full[t], j & 1, &ctl.abort_flag, p.status, 0xD20 + t)) return false;
-        if (!mbar_wait(&ctl.v_full[s], (j / F4_VST) & 1, &ctl.abort_flag, p.status, 0xD22)) return false;
+        if (!wait_all(&ctl.p_full[t], j & 1, 0xD20 + t)) return false;
+        if (!wait_all(&ctl.v_full[s], (j / F4_VST) & 1, 0xD22)) return false;
         tc_fence_after_sync();
-        const uint32_t va = smem_u32(sV + s * F4_TILE);
-        const uint32_t d = tmem + 256u * t + 128u;
+        if (elect_one()) {
+          const uint64_t va = v_desc0 + s * kTileStep;
+          const uint32_t d = tmem + 256u * t + 128u;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          // A = P_t from tensor memory: 16 keys = 8 columns of bf16 pairs per step.
-          const uint64_t b_desc = f4_mnmajor_desc(va + kk * 2048);
-          mma_bf16_ts(d, tmem + 256u * t + 8u * kk, b_desc, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < 8; ++kk) {
+            // A = P_t from tensor memory: 16 keys = 8 columns of bf16 pairs per step.
+            mma_bf16_ts(d, tmem + 256u * t + 8u * kk, va + kk * (2048u >> 4), idesc_pv,
+                        (j > 0 || kk > 0) ? 1u : 0u);
+          }
+          mma_commit(&ctl.pv_done[t]);
         }
-        mma_commit(&ctl.pv_done[t]);
+        __syncwarp();
         return true;
       };
       // prologue: S_t(0) of both tiles
       for (int t = 0; ok && t < 2; ++t)
         if (nb[t] > 0) ok = issue_qk(t, 0);
-      if (ok) mma_commit(&ctl.k_empty[0]);
+      if (ok && elect_one()) mma_commit(&ctl.k_empty[0]);
+      __syncwarp();
       for (int j = 0; ok && j < nblk_max; ++j) {
         for (int t = 0; ok && t < 2; ++t) {
           if (j >= nb[t]) continue;
@@ -272,8 +291,11 @@ __global__ void __launch_bounds__(F4_THREADS, 1) fa_fwd4_kernel(const __grid_con
           if (ok && j + 1 < nb[t]) ok = issue_qk(t, j + 1);
         }
         if (!ok) break;
-        mma_commit(&ctl.v_empty[j % F4_VST]);
-        if (j + 1 < nblk_max) mma_commit(&ctl.k_empty[(j + 1) % F4_KST]);
+        if (elect_one()) {
+          mma_commit(&ctl.v_empty[j % F4_VST]);
+          if (j + 1 < nblk_max) mma_commit(&ctl.k_empty[(j + 1) % F4_KST]);
+        }
+        __syncwarp();
       }
     }
   } else {

@@ -106,7 +106,8 @@ def load_peaks() -> dict:
                 "source": "fallback"}
 
 
-NVLINK_GBS = 770.0  # measured peer copy, per direction per GPU
+NVLINK_GBS = 770.0        # measured peer copy, per direction per GPU ("of measured")
+NVLINK_LINK_GBS = 900.0   # NVLink 5 link rate, per direction per GPU ("of link")
 
 
 def main() -> int:
@@ -210,44 +211,38 @@ def main() -> int:
     ag_bytes = (world - 1) / world * T * H * 2.0
     rs_bytes = (world - 1) / world * T * H * 2.0
 
-    def roof(peak_tflops):
-        t1 = max(per_rank_flops_half / (peak_tflops * 1e12), ag_bytes / (NVLINK_GBS * 1e9))
-        t2 = max(per_rank_flops_half / (peak_tflops * 1e12), rs_bytes / (NVLINK_GBS * 1e9))
+    def roof(peak_tflops, link_gbs=NVLINK_GBS):
+        t1 = max(per_rank_flops_half / (peak_tflops * 1e12), ag_bytes / (link_gbs * 1e9))
+        t2 = max(per_rank_flops_half / (peak_tflops * 1e12), rs_bytes / (link_gbs * 1e9))
         return (t1 + t2) * 1e3
 
     extras = {}
     if not args.skip_extras:
-        # all-reduce bus bandwidth, bf16, symmetric tensors (in place), best of our algorithms
+        # All-reduce bus bandwidth, bf16, in place on symmetric tensors, through the library's
+        # own selector and default grids (`algo="auto"`).  With one rank there is nothing to
+        # reduce over a link: the entries are null.
         for mb in (64, 256):
             n = mb * (1 << 20) // 2
+            nbytes = n * 2
+            if world == 1:
+                extras[f"allreduce_{mb}MB"] = {"algo": None, "ms": None, "busbw_gbs": None,
+                                               "nccl_ms": None, "nccl_busbw_gbs": None}
+                continue
             t, _ = ctx.empty((n,), torch.bfloat16)
             t.fill_(0.001)
             sync_all()
-            best = None
-            algos = ["twoshot"] + (["nvls"] if ctx.has_multicast else [])
-            if world == 1:
-                algos = ["oneshot"]
-            for algo in algos:
-                if world == 1:
-                    o = torch.empty_like(t)
-                    fn = (lambda: coll.all_reduce(ctx, t, out=o, algo="oneshot", max_blocks=148))
-                else:
-                    fn = (lambda a=algo: coll.all_reduce(ctx, t, algo=a, max_blocks=148))
-                ms = timed(fn, 10, 3) / 10
-                if best is None or ms < best[1]:
-                    best = (algo, ms)
-            nccl_ms = None
-            if world > 1:
-                u = torch.full((n,), 0.001, dtype=torch.bfloat16, device=dev)
-                nccl_ms = timed(lambda: dist.all_reduce(u), 10, 3) / 10
-            nbytes = n * 2
-            factor = 2.0 * (world - 1) / world if world > 1 else 1.0
+            algo = coll.choose_all_reduce_algo(nbytes, world, ctx.has_multicast)
+            ms = timed(lambda: coll.all_reduce(ctx, t), 10, 3) / 10
+            u = torch.full((n,), 0.001, dtype=torch.bfloat16, device=dev)
+            nccl_ms = timed(lambda: dist.all_reduce(u), 10, 3) / 10
+            factor = 2.0 * (world - 1) / world
+            bus = factor * nbytes / (ms * 1e-3) / 1e9
             extras[f"allreduce_{mb}MB"] = {
-                "algo": best[0], "ms": round(best[1], 4),
-                "busbw_gbs": round(factor * nbytes / (best[1] * 1e-3) / 1e9, 1),
-                "nccl_ms": None if nccl_ms is None else round(nccl_ms, 4),
-                "nccl_busbw_gbs": None if nccl_ms is None else round(
-                    factor * nbytes / (nccl_ms * 1e-3) / 1e9, 1),
+                "algo": algo, "ms": round(ms, 4), "busbw_gbs": round(bus, 1),
+                "frac_of_link_900": round(bus / NVLINK_LINK_GBS, 4),
+                "frac_of_measured_770": round(bus / NVLINK_GBS, 4),
+                "nccl_ms": round(nccl_ms, 4),
+                "nccl_busbw_gbs": round(factor * nbytes / (nccl_ms * 1e-3) / 1e9, 1),
             }
         ctx.check_status()
 
@@ -271,7 +266,9 @@ def main() -> int:
             "unfused_ms_per_step": round(base_ms, 4),
             "speedup_vs_unfused": round(base_ms / ms_step, 4),
             "roofline": {
-                "peaks": peaks, "nvlink_gbs": NVLINK_GBS,
+                "peaks": peaks, "nvlink_gbs": NVLINK_GBS, "nvlink_link_gbs": NVLINK_LINK_GBS,
+                "frac_of_sustained_at_link_rate": round(
+                    roof(peaks["bf16_tflops_sustained"], NVLINK_LINK_GBS) / ms_step, 4),
                 "target_ms_burst": round(roof(peaks["bf16_tflops"]), 4),
                 "target_ms_sustained": round(roof(peaks["bf16_tflops_sustained"]), 4),
                 "frac_of_burst": round(roof(peaks["bf16_tflops"]) / ms_step, 4),

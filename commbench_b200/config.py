@@ -29,7 +29,7 @@ class Config:
     gemm_ar_oneshot_max_m: int = 0              # rows at or below use the one-shot epilogue (0: never)
     fused_poll_ns: int = 300                    # pause between polls of a peer-written flag
     # --- attention -------------------------------------------------------
-    attn_impl: int = 4                          # flash-attention kernel, 1..5 (4: P kept in TMEM)
+    attn_impl: int = 4                          # flash-attention kernel: 4 (P kept in TMEM) or 1
     # --- MoE ---------------------------------------------------------------
     moe_fused_swiglu: bool = True               # silu(gate)*up in the up-projection's epilogue
     # --- runtime -----------------------------------------------------------

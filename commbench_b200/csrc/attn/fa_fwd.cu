@@ -424,7 +424,7 @@ static int make_tmap_bshd(CUtensorMap* out, const void* base, int rows, int head
   return 0;
 }
 
-// Shared with the second forward kernel (fa_fwd2.cu).
+// Shared with the other attention kernels of this folder.
 int cb_attn_make_tmap_bshd(CUtensorMap* out, const void* base, int rows, int heads) {
   return make_tmap_bshd(out, base, rows, heads);
 }

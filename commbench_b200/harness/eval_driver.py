@@ -29,8 +29,8 @@ import time
 from . import compile_run as CR
 from .llm import factory as F
 from .llm import prompt as P
+from .verdict import ACCEPTABLE    # one definition: the driver and the verdict module agree
 
-ACCEPTABLE = {"better", "on_par", "info_only"}
 TASKS_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tasks")
 
 

@@ -72,10 +72,17 @@ def compute_verdict(entry, baseline_metrics: dict, candidate_metrics: dict) -> V
     if entry == "info_only":
         return Verdict(INFO_ONLY, {"note": "op has no numeric performance metric"})
     key, direction = entry["primary"], entry["direction"]
-    if key not in candidate_metrics or candidate_metrics[key] is None:
+
+    def numeric(v) -> bool:
+        return isinstance(v, (int, float)) and not isinstance(v, bool)
+
+    # Candidate first; a value that is not a number ("N/A", a dict) counts as missing.
+    if not numeric(candidate_metrics.get(key)):
         return Verdict(NO_CANDIDATE_METRICS, {"primary_metric": key})
-    if key not in baseline_metrics or baseline_metrics[key] is None:
+    if not numeric(baseline_metrics.get(key)):
         return Verdict(NO_BASELINE_METRICS, {"primary_metric": key})
+    if direction not in ("higher", "lower"):
+        return Verdict(UNKNOWN, {"primary_metric": key, "note": f"bad direction {direction!r}"})
     b, c = float(baseline_metrics[key]), float(candidate_metrics[key])
     pct, note = improvement_pct(b, c, direction)
     d = {"primary_metric": key, "direction": direction, "baseline": b, "candidate": c,

@@ -11,6 +11,20 @@ all-reduce (one-shot below a threshold, two-shot above:
 datasets/example097_vllm_custom_all_reduce/nv/empty_vllm_custom_all_reduce.py:104-145) plus the
 NVLS path of datasets/example048_thunderkitten_all_reduce_easy/nv/
 empty_thunderkitten_all_reduce.cu:64-94 when a multicast object is bound.
+
+**Ordering rule.**  The collectives of one context share the signal pad's channels (every
+kernel uses channels 0 .. blocks-1 and their epoch counters) and the staging block
+``coll_stage``.  They must therefore be *stream-ordered*: issue them on one stream, or order
+the streams with events, so that no two collectives of the same context overlap on the
+GPU - and every rank must issue them in the same order.  Overlapping calls race on the epochs
+and on the staging buffer (wrong sums, or waits that run out after the time-out).  Use a
+second ``CommContext`` for a second, concurrent stream of collectives.
+
+**After a time-out.**  A wait that runs out records the context's status word and later waits
+give up quickly, so results are garbage from then on.  Every launch first reads the
+host-mapped status word (no synchronisation) and raises :class:`CommError` instead of
+launching when it is set; ``ctx.check_status()`` reports and clears it, and
+``ctx.reset_sync_state()`` re-arms the flags once every rank has stopped.
 """
 from __future__ import annotations
 
@@ -89,7 +103,17 @@ _OP_NAMES = ("all_reduce.oneshot", "all_reduce.twoshot", "all_reduce.nvls", "all
              "all_gather.push", "reduce_scatter", "all_to_all", "all_to_all_4d", "broadcast")
 
 
+def _refuse_after_failure(ctx):
+    w = ctx.status_word()
+    if w != 0:
+        raise CommError(
+            f"rank {ctx.rank}: an earlier kernel of this context reported "
+            f"'{N.decode_status(w)}'; not launching on top of it - call ctx.check_status() / "
+            "ctx.reset_sync_state() on every rank first")
+
+
 def _launch(ctx, op: int, args: N.CollArgs, blocks: int, stream=None):
+    _refuse_after_failure(ctx)
     if get_config().nvtx:
         from ..utils.tracing import nvtx_range
 

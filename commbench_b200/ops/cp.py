@@ -32,9 +32,9 @@ def flash_attention(q, k, v, causal: bool = True, q_offset: int = 0, kv_offset: 
                     stream=None, impl: int | None = None):
     """One key/value chunk: returns (o [B,Sq,Hq,D] bf16 normalised, lse [B,Hq,Sq] fp32).
 
-    ``impl`` selects the kernel (default from ``CB200_ATTN_IMPL``): 3 = two query tiles per CTA,
-    two threads per query row (16 softmax warps), O in tensor memory; 2 = the same with one
-    thread per row (8 softmax warps); 1 = the first design (one tile, O in registers).
+    ``impl`` selects the kernel (default from ``CB200_ATTN_IMPL``): 4 = two query tiles per
+    CTA with a softmax warp-group each, O and P in tensor memory (the product kernel);
+    1 = the first design (one tile, O in registers), kept as a simple cross-check.
 
     ``q_offset`` / ``kv_offset`` are the global sequence positions of the first query / key;
     with ``causal`` key j is visible to query i iff kv_offset + j <= q_offset + i."""
@@ -54,10 +54,9 @@ def flash_attention(q, k, v, causal: bool = True, q_offset: int = 0, kv_offset: 
     sc = scale if scale is not None else 1.0 / math.sqrt(D)
     if impl is None:
         impl = get_config().attn_impl
-    fn = {1: lib.cb_attn_fwd, 2: lib.cb_attn_fwd2, 3: lib.cb_attn_fwd3,
-          4: lib.cb_attn_fwd4, 5: lib.cb_attn_fwd5}.get(impl)
+    fn = {1: lib.cb_attn_fwd, 4: lib.cb_attn_fwd4}.get(impl)
     if fn is None:
-        raise CommError(f"unknown attention kernel {impl} (1 to 5)")
+        raise CommError(f"unknown attention kernel {impl} (1 or 4)")
     rc = fn(N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(out), N.ptr(lse), B, Sq, Skv, Hq, Hkv,
             q_offset, kv_offset, int(causal), C.c_float(sc), C.c_void_p(status_ptr),
             N.stream_ptr(stream))

@@ -14,7 +14,7 @@ def _qkv(B, Sq, Skv, Hq, Hkv, seed):
     return q, k, v
 
 
-@pytest.mark.parametrize("impl", [1, 2, 3, 4, 5])
+@pytest.mark.parametrize("impl", [1, 4])
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("shape", [(1, 128, 128, 1, 1), (1, 256, 256, 4, 1), (2, 384, 384, 4, 2),
                                    (1, 200, 200, 2, 2), (1, 1024, 1024, 8, 2),

@@ -29,8 +29,8 @@ def test_defaults_and_environment_overrides(monkeypatch):
 
 
 def test_set_config_rejects_unknown_fields():
-    CFG.set_config(fused_poll_ns=500, attn_impl=2)
-    assert CFG.get_config().fused_poll_ns == 500 and CFG.get_config().attn_impl == 2
+    CFG.set_config(fused_poll_ns=500, attn_impl=1)
+    assert CFG.get_config().fused_poll_ns == 500 and CFG.get_config().attn_impl == 1
     with pytest.raises(KeyError):
         CFG.set_config(no_such_knob=1)
 

@@ -207,6 +207,21 @@ def test_round_loop_repairs_then_tunes(tmp_path):
     rdirs = sorted(os.listdir(t / "results" / "fake-model"))
     assert sum(d.startswith("round") for d in rdirs) == 3
     assert os.path.exists(t / "results" / "fake-model" / rdirs[0] / "prompt.txt")
+    # a correct candidate whose reference prints no primary metric is judged
+    # "no_baseline_metrics": accepted at once (no tuning round), and it counts as passed
+    (t / "ref_toy.py").write_text('import json\nprint(json.dumps({"Correctness": "PASS", "metrics": []}))\n')
+    asked = []
+
+    def once(prompt, *a):
+        asked.append(prompt)
+        return prog % ("PASS", 30.0)
+
+    passed, reason, result, rounds, perf = ED.generate_eval_one(
+        str(t), "m3", max_rounds=4, generate=once, quiet=True)
+    assert passed and rounds == 1 and len(asked) == 1
+    assert perf["performance"] == "no_baseline_metrics"
+    assert ED.ACCEPTABLE is __import__("commbench_b200.harness.verdict", fromlist=["x"]).ACCEPTABLE
+    (t / "ref_toy.py").write_text(prog % ("PASS", 10.0))
     # never passes: gives up after max_rounds with the last reason
     passed, reason, *_ = ED.generate_eval_one(str(t), "m2", max_rounds=2, quiet=True,
                                               generate=lambda *a: "raise SystemExit(3)\n")

@@ -57,6 +57,14 @@ def test_verdict_tiers_and_guards():
     assert V.compute_verdict(lower, {}, {"latency_avg": 1.0}).verdict == "no_baseline_metrics"
     with pytest.raises(ValueError):
         V.improvement_pct(1.0, 1.0, "sideways")
+    # values that are not numbers count as missing (candidate side first), a bad direction
+    # gives "unknown" instead of an exception: a foreign summary must not crash a re-judge pass
+    assert V.compute_verdict(lower, {"latency_avg": 1.0}, {"latency_avg": "N/A"}).verdict == "no_candidate_metrics"
+    assert V.compute_verdict(lower, {"latency_avg": {"x": 1}}, {"latency_avg": 1.0}).verdict == "no_baseline_metrics"
+    assert V.compute_verdict(lower, {"latency_avg": "N/A"}, {"latency_avg": True}).verdict == "no_candidate_metrics"
+    odd = V.compute_verdict({"primary": "latency_avg", "direction": "sideways"},
+                            {"latency_avg": 1.0}, {"latency_avg": 1.0})
+    assert odd.verdict == "unknown" and odd.acceptable
     assert V.geometric_mean_speedup([(2.0, 1.0), (1.0, 2.0)]) == pytest.approx(1.0)
     assert V.geometric_mean_speedup([(3.0, 1.0)]) == pytest.approx(3.0)
 

@@ -52,14 +52,25 @@ def test_noalloc_expert_sort_matches_existing_entry_point_twice():
         assert rc == 0, lib.cb_last_error()
         out_sorted = torch.full((n,), -1, dtype=torch.int32, device="cuda")
         out_counts = torch.empty(E, dtype=torch.int32, device="cuda")
-        before = torch.cuda.memory_allocated()
         rc = lib.cb_moe_expert_sort_noalloc(idx.data_ptr(), n, E, out_sorted.data_ptr(),
                                             out_counts.data_ptr(), stream)
         assert rc == 0, lib.cb_last_error()
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
         assert torch.equal(out_counts, ref_counts)
         assert torch.equal(out_sorted, ref_sorted)      # integer outputs: exact equality
+        # "Allocates nothing" is checked on the DEVICE's free memory, which also sees an
+        # allocation made inside the library (torch's own counters would not): after the
+        # call above has done the one-time set-up, another call must leave it unchanged.
+        out_sorted.fill_(-1)
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        rc = lib.cb_moe_expert_sort_noalloc(idx.data_ptr(), n, E, out_sorted.data_ptr(),
+                                            out_counts.data_ptr(), stream)
+        assert rc == 0, lib.cb_last_error()
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after == free_before
+        assert torch.equal(out_sorted, ref_sorted)
 
 
 def test_noalloc_expert_sort_rejects_oversize_problems():
@@ -72,4 +83,6 @@ def test_noalloc_expert_sort_rejects_oversize_problems():
                                           cnt.data_ptr(), stream) == -1
     assert b"exceeds" in lib.cb_last_error()
     assert lib.cb_moe_expert_sort_noalloc(idx.data_ptr(), 64, 1025, out.data_ptr(),
+                                          cnt.data_ptr(), stream) == -1
+    assert lib.cb_moe_expert_sort_noalloc(idx.data_ptr(), 0, 4, out.data_ptr(),
                                           cnt.data_ptr(), stream) == -1

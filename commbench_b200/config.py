@@ -30,6 +30,8 @@ class Config:
     fused_poll_ns: int = 300                    # pause between polls of a peer-written flag
     # --- attention -------------------------------------------------------
     attn_impl: int = 4                          # flash-attention kernel: 4 (P kept in TMEM) or 1
+    cp_comm_ctas: int = 4                       # ring attention: CTAs that pull the K/V shards
+    cp_comm_ctas_ulysses: int = 16              # Ulysses: CTAs that pull the K/V head slices
     # --- MoE ---------------------------------------------------------------
     moe_fused_swiglu: bool = True               # silu(gate)*up in the up-projection's epilogue
     # --- runtime -----------------------------------------------------------

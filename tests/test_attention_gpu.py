@@ -58,12 +58,75 @@ def test_ring_and_ulysses_single_rank(native_lib):
     from commbench_b200.runtime.context import CommContext
 
     ctx = CommContext(heap_bytes=64 << 20)
-    q, k, v = _qkv(1, 256, 256, 4, 1, 5)
-    ring = RingAttention(ctx, 1, 256, 4, 1)
-    o, _ = ring.forward(q, k, v, causal=True)
-    ro, _ = reference_attention(q, k, v, causal=True)
+    q, k, v = _qkv(1, 512, 512, 4, 1, 5)
+    ring = RingAttention(ctx, 1, 512, 4, 1)
+    o, lse = ring.forward(q, k, v, causal=True)
+    ro, rl = reference_attention(q, k, v, causal=True)
     assert torch.allclose(o.float(), ro, atol=2e-2, rtol=2e-2)
+    assert torch.allclose(lse, rl, atol=2e-2, rtol=1e-3)
     o2 = ulysses_attention(ctx, q, k, v, causal=True)
     assert torch.allclose(o2.float(), ro, atol=2e-2, rtol=2e-2)
     ctx.check_status()
     ctx.close()
+
+
+def _full(B, S, Hq, Hkv, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    q = torch.randn(B, S, Hq, 128, device="cuda", generator=g).bfloat16()
+    k = torch.randn(B, S, Hkv, 128, device="cuda", generator=g).bfloat16()
+    v = torch.randn(B, S, Hkv, 128, device="cuda", generator=g).bfloat16()
+    return q, k, v
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("zigzag", [True, False])
+@pytest.mark.parametrize("causal", [True, False])
+def test_ring_attention_kernel_virtual_ranks(native_lib, world, zigzag, causal):
+    """W virtual ranks on one GPU (their launches pull from each other's buffers, none waits
+    for another): every rank's rows must equal full-sequence attention, over three calls."""
+    from commbench_b200.ops.cp import RingAttention, reference_attention, zigzag_shard
+    from commbench_b200.runtime.context import EmuContext
+
+    B, Sl, Hq, Hkv = 2, 512, 4, 2
+    S = Sl * world
+    q, k, v = _full(B, S, Hq, Hkv, 31 + world)
+    ro, rl = reference_attention(q, k, v, causal=causal)
+    if zigzag:
+        shard = lambda x, r: zigzag_shard(x, world, r)
+    else:
+        shard = lambda x, r: x[:, r * Sl:(r + 1) * Sl].contiguous()
+    ctx = EmuContext(world)
+    ring = RingAttention(ctx, B, Sl, Hq, Hkv, zigzag=zigzag, num_comm=2)
+    qs = [shard(q, r) for r in range(world)]
+    ks = [shard(k, r) for r in range(world)]
+    vs = [shard(v, r) for r in range(world)]
+    for it in range(3):
+        outs, lses = ring.forward(qs, ks, vs, causal=causal)
+        ctx.check_status()
+        for r in range(world):
+            assert torch.allclose(outs[r].float(), shard(ro, r), atol=2e-2, rtol=2e-2), (it, r)
+            ref_l = shard(rl.permute(0, 2, 1), r).permute(0, 2, 1)
+            assert torch.allclose(lses[r], ref_l, atol=2e-2, rtol=1e-3), (it, r)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("causal", [True, False])
+def test_ulysses_attention_kernel_virtual_ranks(native_lib, world, causal):
+    """Sequence-sharded in and out; each virtual rank attends for its head slice over the whole
+    sequence, reading Q from and writing O to the other ranks' tensors."""
+    from commbench_b200.ops.cp import UlyssesAttention, reference_attention
+    from commbench_b200.runtime.context import EmuContext
+
+    B, Sl, Hq, Hkv = 1, 512, 8, 4
+    S = Sl * world
+    q, k, v = _full(B, S, Hq, Hkv, 57 + world)
+    ro, _ = reference_attention(q, k, v, causal=causal)
+    ctx = EmuContext(world)
+    op = UlyssesAttention(ctx, B, Sl, Hq, Hkv, num_comm=2)
+    sh = lambda x, r: x[:, r * Sl:(r + 1) * Sl].contiguous()
+    for it in range(3):
+        outs = op.forward([sh(q, r) for r in range(world)], [sh(k, r) for r in range(world)],
+                          [sh(v, r) for r in range(world)], causal=causal)
+        ctx.check_status()
+        for r in range(world):
+            assert torch.allclose(outs[r].float(), sh(ro, r), atol=2e-2, rtol=2e-2), (it, r)

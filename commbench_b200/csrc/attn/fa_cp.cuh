@@ -14,6 +14,11 @@
 //     tensor): the two zig-zag halves of a ring shard, or - for Ulysses - the W sequence shards,
 //     whose Q tiles are fetched straight from their owners' memory with plain (non-multicast)
 //     TMA loads and whose O rows are stored straight into their owners' output tensors;
+//   * registers are moved from the four utility warps (producer, MMA issuer, two idle) to
+//     the eight softmax warps with setmaxnreg (72 / 216 per thread), which keeps a 128-column row
+//     of scores in registers without spills, and every `kPoly`-th pair of exponentials is
+//     computed on the FMA pipe (a cubic after a round-to-nearest split) instead of the SFU,
+//     which otherwise is as busy as the tensor pipe;
 //   * CTAs draw tickets: the first `num_comm` tickets copy the list of 2-D pieces
 //     (peer -> local, 16-byte loads and stores), bumping each piece's counter when done; the
 //     others take (query tile pair, head, batch) items, heaviest first.
@@ -170,6 +175,17 @@ __device__ __forceinline__ void cp_comm_cta(const FaCpParams& p, int c) {
   }
 }
 
+template <int N>
+__device__ __forceinline__ void cp_reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void cp_reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// kPoly: every kPoly-th pair of keys takes its exponential from the FMA pipe (0: none).
+template <int kPoly>
 __global__ void __launch_bounds__(CP_THREADS, 1) fa_cp_kernel(const __grid_constant__ FaCpParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem =
@@ -180,9 +196,14 @@ __global__ void __launch_bounds__(CP_THREADS, 1) fa_cp_kernel(const __grid_const
   __shared__ CpCtl ctl;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
 
-  if (threadIdx.x == 0) ctl.ticket = static_cast<int>(atomicAdd(&p.sched[0], 1u));
-  __syncthreads();
-  const int ticket = ctl.ticket;
+  // Tickets only where communication CTAs must be the first to run; a launch without them
+  // (plain local attention) takes its item from the block index.
+  int ticket = static_cast<int>(blockIdx.x);
+  if (p.sched != nullptr) {
+    if (threadIdx.x == 0) ctl.ticket = static_cast<int>(atomicAdd(&p.sched[0], 1u));
+    __syncthreads();
+    ticket = ctl.ticket;
+  }
   bool attend = false;
   int qs_i = 0, pair = 0, head = 0, batch = 0;
   if (ticket < p.num_comm) {
@@ -245,6 +266,9 @@ __global__ void __launch_bounds__(CP_THREADS, 1) fa_cp_kernel(const __grid_const
     // tile t: S (fp32, 128 columns; its first 64 columns hold P as bf16 pairs after the
     // softmax) at column 256 t, O at column 256 t + 128.
 
+    // 128 x 72 + 256 x 216 registers = 64,512 of the SM's 65,536.
+    if (warp < 4) {
+    cp_reg_dec<72>();
     if (warp == 0) {
       if (lane == 0 && nblk > 0) {
         // ---------------------------------------------------------------- producer
@@ -385,9 +409,11 @@ __global__ void __launch_bounds__(CP_THREADS, 1) fa_cp_kernel(const __grid_const
           __syncwarp();
         }
       }
+    }
     } else {
+      cp_reg_inc<216>();
       // ------------------------------------------------------------------- softmax
-      const int t = warp >= 6 ? 1 : 0;
+      const int t = warp >= 8 ? 1 : 0;
       const uint32_t q = warp & 3u;
       const uint32_t r = q * 32u + lane;
       const uint32_t lane_addr = (q * 32u) << 16;
@@ -464,8 +490,27 @@ __global__ void __launch_bounds__(CP_THREADS, 1) fa_cp_kernel(const __grid_const
 #pragma unroll
         for (int i = 0; i < 128; i += 2) {
           const uint64_t y = cp_fma2(cp_pack_u(s[i], s[i + 1]), scale2, negm2);
-          const float p0 = cp_ex2(__uint_as_float(static_cast<uint32_t>(y)));
-          const float p1 = cp_ex2(__uint_as_float(static_cast<uint32_t>(y >> 32)));
+          float p0, p1;
+          if (kPoly > 0 && !need_mask && ((i >> 1) % (kPoly > 0 ? kPoly : 1)) == kPoly - 1) {
+            // 2^x on the FMA pipe: nearest-integer split with the 1.5 * 2^23 trick, a cubic on
+            // the fraction in [-0.5, 0.5] (relative error 7.5e-5, below bf16 rounding), the
+            // exponent added as an integer; inputs clamped to -126 so it cannot wrap.  Masked
+            // blocks keep the SFU everywhere: -inf must give an exact zero.
+            const float x0 = fmaxf(__uint_as_float(static_cast<uint32_t>(y)), -126.f);
+            const float x1 = fmaxf(__uint_as_float(static_cast<uint32_t>(y >> 32)), -126.f);
+            const uint64_t xx = cp_pack(x0, x1);
+            const uint64_t rr = cp_add2(xx, cp_pack(12582912.f, 12582912.f));
+            const uint64_t xf = cp_add2(rr, cp_pack(-12582912.f, -12582912.f));
+            const uint64_t fr = cp_fma2(xf, cp_pack(-1.f, -1.f), xx);
+            uint64_t qq = cp_fma2(fr, cp_pack(0.05517116f, 0.05517116f), cp_pack(0.24261014f, 0.24261014f));
+            qq = cp_fma2(qq, fr, cp_pack(0.69326097f, 0.69326097f));
+            qq = cp_fma2(qq, fr, cp_pack(0.99992812f, 0.99992812f));
+            p0 = __uint_as_float(static_cast<uint32_t>(qq) + (static_cast<uint32_t>(rr) << 23));
+            p1 = __uint_as_float(static_cast<uint32_t>(qq >> 32) + (static_cast<uint32_t>(rr >> 32) << 23));
+          } else {
+            p0 = cp_ex2(__uint_as_float(static_cast<uint32_t>(y)));
+            p1 = cp_ex2(__uint_as_float(static_cast<uint32_t>(y >> 32)));
+          }
           sum4[(i >> 1) & 3] = cp_add2(sum4[(i >> 1) & 3], cp_pack(p0, p1));
           __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
           s[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
@@ -485,7 +530,10 @@ __global__ void __launch_bounds__(CP_THREADS, 1) fa_cp_kernel(const __grid_const
       // ------------------------------------------------------------------ epilogue
       if (ok && nblk > 0)
         ok = mbar_wait(&ctl.pv_done[t], (nblk - 1) & 1, &ctl.abort_flag, p.status, 0xE34 + t);
-      if (ok && row_in_seg < qs.nrows) {
+      // Tile-uniform condition: the tensor-memory loads below are warp-collective; rows past
+      // the end of the segment are only kept from being stored.
+      if (ok && pair * 2 * CP_BM + t * CP_BM < qs.nrows) {
+        const bool row_ok = row_in_seg < qs.nrows;
         tc_fence_after_sync();
         const float inv = l > 0.f ? 1.f / l : 0.f;
         const int orow = qs.row0 + row_in_seg;
@@ -502,18 +550,20 @@ __global__ void __launch_bounds__(CP_THREADS, 1) fa_cp_kernel(const __grid_const
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = 0u;
           }
+          if (row_ok) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 v;
-            __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&v);
+            for (int i = 0; i < 32; i += 8) {
+              uint4 v;
+              __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&v);
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              hh[k] = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * k]) * inv,
-                                            __uint_as_float(o[i + 2 * k + 1]) * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+              for (int k = 0; k < 4; ++k)
+                hh[k] = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * k]) * inv,
+                                              __uint_as_float(o[i + 2 * k + 1]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+            }
           }
         }
-        if (p.lse[qs.out] != nullptr)
+        if (row_ok && p.lse[qs.out] != nullptr)
           p.lse[qs.out][(static_cast<size_t>(batch) * p.o_heads + p.o_head0 + head) *
                             p.o_rows[qs.out] + orow] =
               l > 0.f ? (m_ref * 0.6931471805599453f + logf(l)) : -INFINITY;
@@ -535,7 +585,7 @@ __global__ void __launch_bounds__(CP_THREADS, 1) fa_cp_kernel(const __grid_const
 
   // Last CTA out re-arms the ticket counter for the next launch.
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == 0 && p.sched != nullptr) {
     __threadfence();
     if (atomicAdd(&p.sched[1], 1u) == gridDim.x - 1u) {
       p.sched[0] = 0u;

@@ -14,7 +14,7 @@ static constexpr int CP_SUB = 16384;
 static constexpr int CP_TILE = 2 * CP_SUB;
 static constexpr int CP_KST = 3, CP_VST = 2;
 static constexpr int CP_SMEM = (2 + CP_KST + CP_VST) * CP_TILE + 1024;  // Q | K ring | V ring
-static constexpr int CP_THREADS = 320;
+static constexpr int CP_THREADS = 384;  // 4 utility warps (producer, MMA, 2 idle) + 8 softmax warps
 static constexpr float CP_RESCALE_THRESHOLD = 8.f;
 static constexpr int CP_MAX_SEGS = 32;
 static constexpr int CP_MAX_QSEGS = 8;

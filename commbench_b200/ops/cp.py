@@ -234,9 +234,13 @@ class RingAttention(_CpBase):
                 self.k_local(i).copy_(ks[i])
             if vs[i].data_ptr() != self.v_local(i).data_ptr():
                 self.v_local(i).copy_(vs[i])
-        # plan change (causal <-> full) rewrites the piece list; nothing of the old plan may run
+        # A plan change (causal <-> full) rewrites the piece list and renumbers the counters:
+        # nothing of the old plan may still run, and the counters start again from zero.
         if self._plan_key != (bool(causal),):
             torch.cuda.synchronize(self.ctx.device)
+            for f in self.flags:
+                f.zero_()
+            self.calls = 0
         self._barrier()                       # every shard is published
         for i, r in enumerate(self._ranks()):
             qi = qs[i]

@@ -107,6 +107,13 @@ def test_ring_attention_kernel_virtual_ranks(native_lib, world, zigzag, causal):
             assert torch.allclose(outs[r].float(), shard(ro, r), atol=2e-2, rtol=2e-2), (it, r)
             ref_l = shard(rl.permute(0, 2, 1), r).permute(0, 2, 1)
             assert torch.allclose(lses[r], ref_l, atol=2e-2, rtol=1e-3), (it, r)
+    # the same object with the other mask: the list of pieces to pull changes
+    ro2, _ = reference_attention(q, k, v, causal=not causal)
+    for it in range(2):
+        outs, _ = ring.forward(qs, ks, vs, causal=not causal)
+        ctx.check_status()
+        for r in range(world):
+            assert torch.allclose(outs[r].float(), shard(ro2, r), atol=2e-2, rtol=2e-2), (it, r)
 
 
 @pytest.mark.parametrize("world", [2, 4])

@@ -108,7 +108,8 @@ static int sm_count() {
 template <class Cfg>
 static int launch_plain(const void* a, const void* b, void* c, int M, int N, int K, float alpha,
                         uint32_t* status, int max_ctas, cudaStream_t st,
-                        unsigned long long* trace = nullptr) {
+                        unsigned long long* trace = nullptr, const float* a_scale = nullptr,
+                        const float* b_scale = nullptr) {
   PlainParams p;
   const TmapDtype dt = Cfg::FP8 ? TMAP_U8 : TMAP_BF16;
   const unsigned esz = Cfg::FP8 ? 1 : 2;
@@ -127,6 +128,8 @@ static int launch_plain(const void* a, const void* b, void* c, int M, int N, int
   p.g.num_k_blocks = (K + Cfg::BK - 1) / Cfg::BK;
   p.g.alpha = alpha;
   p.g.trace = trace;
+  p.g.a_scale = a_scale;
+  p.g.b_scale = b_scale;
   p.status = status;
   // Row blocks per raster panel: the panel's A rows (panel x K) stay in L2 while the B
   // tiles stream past them, so keep the panel near 32 MB.
@@ -252,6 +255,30 @@ int cb_gemm_fp8(const void* a, const void* b, void* c, int M, int N, int K, floa
       set_last_error("cb_gemm_fp8: bn must be 0, 64, 128, 256 or 512");
       return -1;
   }
+}
+
+// Block-scaled fp8: a [M,K] e4m3 with a_scale [M, K/128] fp32 (one scale per row and 128
+// columns), b [N,K] e4m3 with b_scale [ceil(N/128), K/128] (one per 128 x 128 block); K % 128 == 0.
+// C = alpha * (a * a_scale) (b * b_scale)^T in bf16.  The quantised operands feed the tensor
+// cores directly; every 128-wide K block's partial sum is scaled and accumulated in fp32
+// registers.  pair != 0: CTA pairs (256 x 256 tiles), else one CTA per 128 x 256 tile.
+int cb_gemm_fp8_blockscaled(const void* a, const void* a_scale, const void* b, const void* b_scale,
+                            void* c, int M, int N, int K, float alpha, int pair, int max_ctas,
+                            void* status, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 128) != 0 || (N % 8) != 0 || a_scale == nullptr ||
+      b_scale == nullptr) {
+    set_last_error("cb_gemm_fp8_blockscaled: need M,N,K > 0, K % 128 == 0, N % 8 == 0, scales");
+    return -1;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint32_t* s = static_cast<uint32_t*>(status);
+  const float* as = static_cast<const float*>(a_scale);
+  const float* bs = static_cast<const float*>(b_scale);
+  if (pair)
+    return launch_plain<GemmCfg<256, 5, true, 2, true>>(a, b, c, M, N, K, alpha, s, max_ctas, st,
+                                                        nullptr, as, bs);
+  return launch_plain<GemmCfg<256, 3, true, 1, true>>(a, b, c, M, N, K, alpha, s, max_ctas, st,
+                                                      nullptr, as, bs);
 }
 
 }  // extern "C"

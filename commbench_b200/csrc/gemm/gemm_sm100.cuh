@@ -33,6 +33,15 @@
 // its own 128 accumulator rows.  `Cfg::BM` is the height of a tile (128 or 256)
 // and is what policies count row blocks in.
 //
+// Block-scaled fp8 (`BS_ = true`): A carries one fp32 scale per row and 128 K-elements, B one
+// per 128 x 128 block (the "1x128 / 128x128" recipe).  One ring stage is one 128-wide K block;
+// the MMA thread starts a FRESH accumulator for every K block, alternating between the two
+// TMEM buffers, and commits it; eight epilogue warps (two per TMEM lane quadrant, 128 columns
+// each) read the partial sum, multiply it by a_scale[row, kb] * b_scale[n block, kb] and add it
+// to a running fp32 sum kept in registers - the promotion step that fp8 tensor cores need for
+// long K anyway - while the tensor core works on the next K block.  The quantised operands go
+// straight from memory into the MMA; nothing is expanded to bf16.
+//
 // No load in this file is a cluster-multicast load.  Every wait is bounded: on a
 // time-out the CTA raises its abort word (and its partner's), every role leaves
 // its loop, in-flight copies get a grace period, TMEM is freed and the kernel
@@ -47,9 +56,11 @@
 
 namespace cb {
 
-template <int BN_, int STAGES_, bool FP8_, int PAIR_ = 1>
+template <int BN_, int STAGES_, bool FP8_, int PAIR_ = 1, bool BS_ = false>
 struct GemmCfg {
   static constexpr int PAIR = PAIR_;          // CTAs that share a tile (1, or 2 = a cluster)
+  static constexpr bool BS = BS_;             // block-scaled fp8 with promotion in registers
+  static constexpr int EPI_WARPS = BS_ ? 8 : 4;
   static constexpr int CTA_M = 128;           // accumulator rows per CTA
   static constexpr int BM = CTA_M * PAIR_;    // tile height
   static constexpr int BN = BN_;
@@ -63,10 +74,16 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int EPI_COLS = 64;                 // bf16 columns per store box (128 B)
   static constexpr int EPI_BUF_BYTES = 32 * 128;      // 32 rows x 128 B per warp and buffer
-  static constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;
+  static constexpr int EPI_BYTES = EPI_WARPS * 2 * EPI_BUF_BYTES;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024;
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int THREADS = 224;  // producer, MMA, 4 epilogue warps, signal warp
+  // Warp roles.  Plain: producer, MMA, 4 epilogue warps, signal warp.  Block-scaled: a
+  // utility warp-group (producer, MMA, signal, one idle warp) that gives registers away and
+  // two epilogue warp-groups that take them (setmaxnreg works on whole warp-groups).
+  static constexpr int EPI_WARP0 = BS_ ? 4 : 2;
+  static constexpr int SIGNAL_WARP = BS_ ? 2 : 6;
+  static constexpr int THREADS = BS_ ? 384 : 224;
+  static_assert(!BS_ || (FP8_ && BN_ == 256), "block scales: fp8 operands, 256-column tiles");
   static_assert(PAIR_ == 1 || PAIR_ == 2, "one CTA or a pair per tile");
   static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN in {64,128,192,256}");
   static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS >= 32 && TMEM_COLS <= 512,
@@ -78,6 +95,10 @@ struct GemmShape {
   int M, N, K;
   int num_m_blocks, num_n_blocks, num_k_blocks;
   float alpha;
+  // Block-scaled fp8 only: A scales [M, ceil(K/128)] and B scales [ceil(N/128), ceil(K/128)],
+  // fp32, row-major (policies that gather A may supply their own through `a_scales`).
+  const float* a_scale = nullptr;
+  const float* b_scale = nullptr;
   // Optional role trace, 8 words per CTA of the launch (null = off): SM clock cycles the
   // MMA thread spent waiting for operands [0] and for a free accumulator [1] and its total
   // [2]; the producer's wait for free ring slots [3] and total [4]; the first epilogue
@@ -301,6 +322,63 @@ __device__ __forceinline__ void gemm_mma(const P& p, const GemmShape& g, uint8_t
   }
 }
 
+// MMA role with block scales: every 128-wide K block gets a fresh accumulator, the two TMEM
+// buffers alternating; `tmem_full[b]` / `tmem_empty[b]` are handed over once per K block.
+template <class Cfg, class Policy, class P>
+__device__ __forceinline__ void gemm_mma_bs(const P& p, const GemmShape& g, uint8_t* ring,
+                                            GemmCtl<Cfg::STAGES>* ctl, uint32_t* status, int cta,
+                                            int num_ctas, uint32_t tmem_base) {
+  constexpr uint32_t idesc = make_idesc(Cfg::BM, Cfg::BN, 0u);
+  uint32_t stage = 0, phase = 0, buf = 0, buf_phase = 0;
+  const int ntiles = Policy::num_tiles(p);
+  const uint64_t a_desc0 = make_sw128_kmajor_desc(smem_u32(ring));
+  constexpr uint64_t kStageStep = static_cast<uint64_t>(Cfg::STAGE_BYTES >> 4);
+  constexpr uint64_t kBStep = static_cast<uint64_t>(Cfg::A_BYTES >> 4);
+  const uint32_t empty0 = smem_u32(&ctl->empty[0]);
+  const uint32_t tfull0 = smem_u32(&ctl->tmem_full[0]);
+  const uint32_t empty0_peer = Cfg::PAIR == 2 ? map_to_cta(empty0, 1) : 0u;
+  const uint32_t tfull0_peer = Cfg::PAIR == 2 ? map_to_cta(tfull0, 1) : 0u;
+  for (int tile = cta; tile < ntiles; tile += num_ctas) {
+    for (int kb = 0; kb < g.num_k_blocks; ++kb) {
+      if (!mbar_wait_traced(&ctl->tmem_empty[buf], buf_phase ^ 1u, &ctl->abort_flag, status,
+                            0x200 + buf, false, nullptr))
+        return;
+      if (!mbar_wait_traced(&ctl->full[stage], phase, &ctl->abort_flag, status, 0x300 + stage,
+                            false, nullptr))
+        return;
+      tc_fence_after_sync();
+      if (elect_one()) {
+        const uint32_t d_tmem = tmem_base + buf * Cfg::BN;
+        const uint64_t a_desc = a_desc0 + stage * kStageStep;
+        const uint64_t b_desc = a_desc + kBStep;
+#pragma unroll
+        for (int k = 0; k < Cfg::MMAS_PER_STAGE; ++k) {
+          if constexpr (Cfg::PAIR == 2)
+            mma_fp8_ss_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, k > 0 ? 1u : 0u);
+          else
+            mma_fp8_ss(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, k > 0 ? 1u : 0u);
+        }
+        if constexpr (Cfg::PAIR == 2) {
+          mma_commit_pair(empty0 + stage * 8u);
+          mma_commit_pair(empty0_peer + stage * 8u);
+          mma_commit_pair(tfull0 + buf * 8u);
+          mma_commit_pair(tfull0_peer + buf * 8u);
+        } else {
+          mma_commit_addr(empty0 + stage * 8u);
+          mma_commit_addr(tfull0 + buf * 8u);
+        }
+      }
+      __syncwarp();
+      if (++stage == Cfg::STAGES) {
+        stage = 0;
+        phase ^= 1u;
+      }
+      buf ^= 1u;
+      if (buf == 0u) buf_phase ^= 1u;
+    }
+  }
+}
+
 // One epilogue warp has read accumulator `acc` for the last time: tell the MMA thread (which
 // lives in the even CTA of a pair).
 template <class Cfg>
@@ -406,6 +484,81 @@ __device__ __forceinline__ void acc_bf16x8(float (&a)[8], const uint4& v) {
   }
 }
 
+// Second half of the direct epilogue for one 128-column half `h` of the tile: the 32 x 256 B
+// staging buffer `buf` of this warp holds the bf16 rows; a half-warp takes a row and either
+// stores it to the policy's destinations or, for a tile that is reduced in place, adds the
+// staged partial copies and stores the final row.
+template <class Cfg, class Policy, class P>
+__device__ __forceinline__ void direct_store_half(const P& p, uint8_t* buf, uint32_t lane,
+                                                  uint32_t q, int h, int CH, int sub, int m_blk,
+                                                  int n_blk, const DirectTargets& tg,
+                                                  bool local_tile, const LocalReduce& lr) {
+  constexpr bool kReduce = policy_reduce_local<Policy>();
+  __syncwarp();
+  // Half-warp per row: 16 lanes x 16 B = 256 B (128 bf16 columns; 64 when BN == 64).
+  const uint32_t idx = lane & 15u;
+  const int col = h * 128 + static_cast<int>(idx) * 8;
+  const bool col_ok = (static_cast<int>(idx) < CH * 8) && col < tg.cols;
+  if constexpr (kReduce) {
+    if (local_tile) {
+      // Two rows per lane and step, every staged copy of both loaded before the sums.
+#pragma unroll 1
+      for (int i0 = 0; i0 < 16; i0 += 2) {
+        uint4 parts[2][7];
+        bool okr[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const uint32_t r = 2u * (i0 + u) + (lane >> 4);
+          const int row = sub * Cfg::CTA_M + static_cast<int>(q * 32u + r);
+          okr[u] = col_ok && row < tg.rows;
+          const long long off = row * lr.src_ld + col * 2ll;
+#pragma unroll
+          for (int sidx = 0; sidx < 7; ++sidx)
+            if (okr[u] && sidx < lr.nsrc)
+              parts[u][sidx] = __ldcg(reinterpret_cast<const uint4*>(lr.src[sidx] + off));
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (!okr[u]) continue;
+          const uint32_t r = 2u * (i0 + u) + (lane >> 4);
+          const int row = sub * Cfg::CTA_M + static_cast<int>(q * 32u + r);
+          const uint4 own =
+              *reinterpret_cast<const uint4*>(buf + r * 256u + ((idx ^ (r & 7u)) * 16u));
+          float a[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) a[k] = 0.f;
+          acc_bf16x8(a, own);
+#pragma unroll
+          for (int sidx = 0; sidx < 7; ++sidx)
+            if (sidx < lr.nsrc) acc_bf16x8(a, parts[u][sidx]);
+          uint4 o;
+          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(a[2 * k], a[2 * k + 1]);
+          st_v4(lr.out + row * lr.out_ld + col * 2ll, o);
+        }
+      }
+      __syncwarp();
+      return;
+    }
+  }
+#pragma unroll 4
+  for (int i = 0; i < 16; ++i) {
+    const uint32_t r = 2u * i + (lane >> 4);
+    const int row = sub * Cfg::CTA_M + static_cast<int>(q * 32u + r);
+    const uint4 v = *reinterpret_cast<const uint4*>(buf + r * 256u + ((idx ^ (r & 7u)) * 16u));
+    if constexpr (Policy::kScatterRows) {
+      // Every output row has its own destination (MoE combine): look it up.
+      uint8_t* rb = col_ok ? Policy::row_base(p, m_blk, row) : nullptr;
+      if (rb != nullptr) st_sys_v4(rb + (static_cast<long long>(n_blk) * Cfg::BN + col) * 2ll, v);
+    } else if (col_ok && row < tg.rows) {
+      const long long off = row * tg.ld_bytes + col * 2ll;
+      for (int d = 0; d < tg.n; ++d) st_sys_v4(tg.base[d] + off, v);
+    }
+  }
+  __syncwarp();
+}
+
 // Epilogue for policies with `kDirect`: accumulator -> bf16 -> shared memory
 // (transposition) -> row-contiguous 16-byte global stores, 256 bytes per row and
 // half-warp.  Used where the destination is another GPU: load/store traffic
@@ -463,69 +616,7 @@ __device__ __forceinline__ void gemm_epilogue_direct(const P& p, const GemmShape
         }
         epi_write_row_256(buf, lane, cc, r0, r1, g.alpha);
       }
-      __syncwarp();
-      // Half-warp per row: 16 lanes x 16 B = 256 B (128 bf16 columns; 64 when BN == 64).
-      const uint32_t idx = lane & 15u;
-      const int col = h * 128 + static_cast<int>(idx) * 8;
-      const bool col_ok = (static_cast<int>(idx) < CH * 8) && col < tg.cols;
-      if constexpr (kReduce) {
-        if (local_tile) {
-          // Two rows per lane and step, every staged copy of both loaded before the sums.
-#pragma unroll 1
-          for (int i0 = 0; i0 < 16; i0 += 2) {
-            uint4 parts[2][7];
-            bool okr[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const uint32_t r = 2u * (i0 + u) + (lane >> 4);
-              const int row = sub * Cfg::CTA_M + static_cast<int>(q * 32u + r);
-              okr[u] = col_ok && row < tg.rows;
-              const long long off = row * lr.src_ld + col * 2ll;
-#pragma unroll
-              for (int sidx = 0; sidx < 7; ++sidx)
-                if (okr[u] && sidx < lr.nsrc)
-                  parts[u][sidx] = __ldcg(reinterpret_cast<const uint4*>(lr.src[sidx] + off));
-            }
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              if (!okr[u]) continue;
-              const uint32_t r = 2u * (i0 + u) + (lane >> 4);
-              const int row = sub * Cfg::CTA_M + static_cast<int>(q * 32u + r);
-              const uint4 own =
-                  *reinterpret_cast<const uint4*>(buf + r * 256u + ((idx ^ (r & 7u)) * 16u));
-              float a[8];
-#pragma unroll
-              for (int k = 0; k < 8; ++k) a[k] = 0.f;
-              acc_bf16x8(a, own);
-#pragma unroll
-              for (int sidx = 0; sidx < 7; ++sidx)
-                if (sidx < lr.nsrc) acc_bf16x8(a, parts[u][sidx]);
-              uint4 o;
-              __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-              for (int k = 0; k < 4; ++k) oh[k] = __floats2bfloat162_rn(a[2 * k], a[2 * k + 1]);
-              st_v4(lr.out + row * lr.out_ld + col * 2ll, o);
-            }
-          }
-          __syncwarp();
-          continue;
-        }
-      }
-#pragma unroll 4
-      for (int i = 0; i < 16; ++i) {
-        const uint32_t r = 2u * i + (lane >> 4);
-        const int row = sub * Cfg::CTA_M + static_cast<int>(q * 32u + r);
-        const uint4 v = *reinterpret_cast<const uint4*>(buf + r * 256u + ((idx ^ (r & 7u)) * 16u));
-        if constexpr (Policy::kScatterRows) {
-          // Every output row has its own destination (MoE combine): look it up.
-          uint8_t* rb = col_ok ? Policy::row_base(p, m_blk, row) : nullptr;
-          if (rb != nullptr) st_sys_v4(rb + (static_cast<long long>(n_blk) * Cfg::BN + col) * 2ll, v);
-        } else if (col_ok && row < tg.rows) {
-          const long long off = row * tg.ld_bytes + col * 2ll;
-          for (int d = 0; d < tg.n; ++d) st_sys_v4(tg.base[d] + off, v);
-        }
-      }
-      __syncwarp();
+      direct_store_half<Cfg, Policy>(p, buf, lane, q, h, CH, sub, m_blk, n_blk, tg, local_tile, lr);
     }
     // Hand the tile to the signal warp: it runs the (slow, ~20 us under store traffic)
     // system-scope fence and raises the flag while these warps go on with the next tile.
@@ -692,12 +783,185 @@ __device__ __forceinline__ void gemm_epilogue_tma(const P& p, const GemmShape& g
   }
 }
 
+__device__ __forceinline__ uint64_t pack_u32x2(uint32_t lo, uint32_t hi) {
+  return static_cast<uint64_t>(lo) | (static_cast<uint64_t>(hi) << 32);
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  return pack_u32x2(__float_as_uint(lo), __float_as_uint(hi));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+template <int N>
+__device__ __forceinline__ void warpgroup_reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void warpgroup_reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// Where the scales of a tile come from: by default the arrays of GemmShape, indexed by the
+// policy's A / B row coordinates; a policy whose A rows were gathered from other ranks names
+// its own source with `static const float* a_scales(const P&, int m_blk)` (scales of the
+// tile's first row, K-block-major per row).
+template <class Policy, class P, class Cfg>
+__device__ __forceinline__ const float* tile_a_scales(const P& p, const GemmShape& g, int m_blk) {
+  if constexpr (requires { Policy::a_scales(p, m_blk); }) {
+    return Policy::a_scales(p, m_blk);
+  } else {
+    return g.a_scale + static_cast<long long>(Policy::a_row(p, m_blk)) * g.num_k_blocks;
+  }
+}
+
+// Epilogue warps of the block-scaled kernel: promotion of every K block's partial sum into
+// registers, then the usual conversion and store (TMA boxes, or the direct / reducing path).
+// Epilogue warp e of the eight reads TMEM lane quadrant (warp index) % 4 (a hardware rule)
+// and the 128-column half h = e / 4 of the tile, which is exactly one 128 x 128 block of B.
+// The running sums are kept as packed pairs and updated with two-wide FMAs.
+template <class Cfg, class Policy, class P>
+__device__ __forceinline__ void gemm_epilogue_bs(const P& p, const GemmShape& g, uint8_t* epi_smem,
+                                                 GemmCtl<Cfg::STAGES>* ctl, uint32_t* status,
+                                                 int cta, int num_ctas, uint32_t tmem_base,
+                                                 uint32_t warp, uint32_t lane, int sub) {
+  const uint32_t q = warp & 3u;
+  const uint32_t ew = warp - Cfg::EPI_WARP0;  // 0..7
+  const int h = static_cast<int>(ew >> 2);
+  uint8_t* bufs = epi_smem + ew * (2 * Cfg::EPI_BUF_BYTES);
+  uint32_t buf = 0, buf_phase = 0, seq = 0, sbuf = 0;
+  const int ntiles = Policy::num_tiles(p);
+  const int nkb = g.num_k_blocks;
+  for (int tile = cta; tile < ntiles; tile += num_ctas) {
+    int m_blk, n_blk;
+    Policy::tile_coord(p, tile, &m_blk, &n_blk);
+    const int row_in_tile = sub * Cfg::CTA_M + static_cast<int>(q * 32u + lane);
+    // scales of this thread's row and of this warp's block of B
+    const float* as = tile_a_scales<Policy, P, Cfg>(p, g, m_blk) +
+                      static_cast<long long>(row_in_tile) * nkb;
+    const bool row_ok = m_blk * Cfg::BM + row_in_tile < g.M;  // rows past M read no scale
+    const int b_blk = (Policy::b_row(p, m_blk, n_blk) >> 7) + h;
+    const bool bcol_ok = n_blk * Cfg::BN + h * 128 < g.N;
+    const float* bs = g.b_scale + static_cast<long long>(b_blk) * nkb;
+    uint64_t acc2[64];  // 128 fp32 sums as pairs
+#pragma unroll
+    for (int i = 0; i < 64; ++i) acc2[i] = 0ull;
+    for (int kb = 0; kb < nkb; ++kb) {
+      const float f = (row_ok && bcol_ok) ? __ldg(as + kb) * __ldg(bs + kb) : 0.f;
+      const uint64_t f2 = pack_f32x2(f, f);
+      if (!mbar_wait_traced(&ctl->tmem_full[buf], buf_phase, &ctl->abort_flag, status,
+                            0x400 + buf, false, nullptr))
+        return;
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + ((q * 32u) << 16) + buf * Cfg::BN + h * 128;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32(taddr + c * 64, r0);
+        tmem_ld_32x32(taddr + c * 64 + 32, r1);
+        tmem_wait_ld();
+        if (c == 1) {
+          // last read of this partial sum: the MMA thread may start the K block after next
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) release_accumulator<Cfg>(ctl, buf, sub);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          acc2[c * 32 + i] = fma_f32x2(pack_u32x2(r0[2 * i], r0[2 * i + 1]), f2, acc2[c * 32 + i]);
+          acc2[c * 32 + 16 + i] =
+              fma_f32x2(pack_u32x2(r1[2 * i], r1[2 * i + 1]), f2, acc2[c * 32 + 16 + i]);
+        }
+      }
+      buf ^= 1u;
+      if (buf == 0u) buf_phase ^= 1u;
+    }
+    // ---- store: two 64-column chunks of this warp's half
+    if constexpr (Policy::kDirect) {
+      DirectTargets tg;
+      Policy::direct_targets(p, m_blk, n_blk, &tg);
+      constexpr bool kReduce = policy_reduce_local<Policy>();
+      bool local_tile = false;
+      LocalReduce lr;
+      if constexpr (kReduce) {
+        local_tile = Policy::tile_is_local(p, m_blk);
+        if (local_tile) {
+          Policy::local_reduce(p, m_blk, n_blk, &lr);
+          int ok = 1;
+          if (lane == 0 && lr.nsrc > 0) ok = Policy::wait_local_ready(p, m_blk, n_blk, sub) ? 1 : 0;
+          if (__shfl_sync(0xffffffffu, ok, 0) == 0) {
+            ctl->abort_flag = 1;
+            return;
+          }
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r0[32], r1[32];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          r0[2 * i] = static_cast<uint32_t>(acc2[c * 32 + i]);
+          r0[2 * i + 1] = static_cast<uint32_t>(acc2[c * 32 + i] >> 32);
+          r1[2 * i] = static_cast<uint32_t>(acc2[c * 32 + 16 + i]);
+          r1[2 * i + 1] = static_cast<uint32_t>(acc2[c * 32 + 16 + i] >> 32);
+        }
+        epi_write_row_256(bufs, lane, c, r0, r1, g.alpha);
+      }
+      direct_store_half<Cfg, Policy>(p, bufs, lane, q, h, 2, sub, m_blk, n_blk, tg, local_tile, lr);
+      __syncwarp();
+      if (Policy::kSignalPerTile && !local_tile) {
+        if (lane == 0) {
+          const uint32_t slot = seq & 7u;
+          if (!mbar_wait(&ctl->sig_empty[slot], ((seq >> 3) & 1u) ^ 1u, &ctl->abort_flag, status,
+                         0x800 + slot))
+            return;
+          mbar_arrive(&ctl->sig_full[slot]);
+        }
+        ++seq;
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r0[32], r1[32];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          r0[2 * i] = static_cast<uint32_t>(acc2[c * 32 + i]);
+          r0[2 * i + 1] = static_cast<uint32_t>(acc2[c * 32 + i] >> 32);
+          r1[2 * i] = static_cast<uint32_t>(acc2[c * 32 + 16 + i]);
+          r1[2 * i + 1] = static_cast<uint32_t>(acc2[c * 32 + 16 + i] >> 32);
+        }
+        // The buffer about to be filled was read by the store issued two boxes ago.
+        if (lane == 0) bulk_wait_read<1>();
+        __syncwarp();
+        uint8_t* b = bufs + sbuf * Cfg::EPI_BUF_BYTES;
+        epi_write_row_swizzled(b, lane, r0, r1, g.alpha);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          Policy::store_box(p, m_blk, n_blk, sub * Cfg::CTA_M + static_cast<int>(q * 32u),
+                            h * 128 + c * Cfg::EPI_COLS, b);
+          bulk_commit();
+        }
+        sbuf ^= 1u;
+      }
+      if (lane == 0) Policy::tile_done(p, m_blk, n_blk, sub * 4 + static_cast<int>(q));
+    }
+  }
+  if constexpr (!Policy::kDirect) {
+    if (lane == 0) bulk_wait_all<0>();
+  }
+}
+
 template <class Cfg, class Policy, class P>
 __device__ __forceinline__ void gemm_epilogue(const P& p, const GemmShape& g, uint8_t* epi_smem,
                                               GemmCtl<Cfg::STAGES>* ctl, uint32_t* status,
                                               int cta, int num_ctas, uint32_t tmem_base,
                                               uint32_t warp, uint32_t lane, int sub) {
-  if constexpr (Policy::kDirect) {
+  if constexpr (Cfg::BS) {
+    gemm_epilogue_bs<Cfg, Policy>(p, g, epi_smem, ctl, status, cta, num_ctas, tmem_base, warp, lane,
+                                  sub);
+  } else if constexpr (Policy::kDirect) {
     gemm_epilogue_direct<Cfg, Policy>(p, g, epi_smem, ctl, status, cta, num_ctas, tmem_base, warp,
                                       lane, sub);
   } else {
@@ -721,10 +985,10 @@ __device__ __forceinline__ uint32_t gemm_setup(GemmCtl<Cfg::STAGES>* ctl, uint32
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&ctl->tmem_full[a], 1);
-      mbar_init(&ctl->tmem_empty[a], 4 * Cfg::PAIR);  // one arrival per epilogue warp (of the pair)
+      mbar_init(&ctl->tmem_empty[a], Cfg::EPI_WARPS * Cfg::PAIR);  // one arrival per epilogue warp (of the pair)
     }
     for (int i = 0; i < 8; ++i) {
-      mbar_init(&ctl->sig_full[i], 4);
+      mbar_init(&ctl->sig_full[i], Cfg::EPI_WARPS);
       mbar_init(&ctl->sig_empty[i], 1);
     }
     ctl->abort_flag = 0;
@@ -800,11 +1064,30 @@ __device__ __forceinline__ void gemm_cta_main(const P& p, const GemmShape& g, ui
   // A pair walks the tile list as one worker; `sub` is this CTA's half of every tile.
   const int sub = Cfg::PAIR == 2 ? static_cast<int>(cluster_ctarank()) : 0;
   const int worker = cta / Cfg::PAIR, num_workers = num_ctas / Cfg::PAIR;
-  if (warp == 0) {
+  if constexpr (Cfg::BS) {
+    // 128 x 56 + 256 x 224 registers = 64,512, what 384 threads x 168 were launched with.
+    if (warp < 4) {
+      warpgroup_reg_dec<56>();
+      if (warp == 0) {
+        gemm_producer<Cfg, Policy>(p, g, ring, &ctl, status, worker, num_workers, sub);
+      } else if (warp == 1) {
+        if (sub == 0)
+          gemm_mma_bs<Cfg, Policy>(p, g, ring, &ctl, status, worker, num_workers, tmem_base);
+      } else if (warp == 2) {
+        if constexpr (Policy::kDirect && Policy::kSignalPerTile) {
+          if (lane == 0) gemm_signal<Cfg, Policy>(p, &ctl, status, worker, num_workers, sub);
+        }
+      }
+    } else {
+      warpgroup_reg_inc<224>();
+      gemm_epilogue<Cfg, Policy>(p, g, epi, &ctl, status, worker, num_workers, tmem_base, warp,
+                                 lane, sub);
+    }
+  } else if (warp == 0) {
     gemm_producer<Cfg, Policy>(p, g, ring, &ctl, status, worker, num_workers, sub);
   } else if (warp == 1) {
     if (sub == 0) gemm_mma<Cfg, Policy>(p, g, ring, &ctl, status, worker, num_workers, tmem_base);
-  } else if (warp < 6) {
+  } else if (warp < 2 + Cfg::EPI_WARPS) {
     gemm_epilogue<Cfg, Policy>(p, g, epi, &ctl, status, worker, num_workers, tmem_base, warp,
                                lane, sub);
   } else {

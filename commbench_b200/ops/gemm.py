@@ -113,10 +113,43 @@ def dequantize_blockscaled(q: torch.Tensor, s: torch.Tensor, row_block: int = 1,
     return out
 
 
-def gemm_fp8_blockscaled(a_q, a_s, b_q, b_s, out=None, b_cache: dict | None = None):
-    """``out = dequant(a_q, a_s [1x128]) @ dequant(b_q, b_s [128x128]).T``: fp8 storage with
-    block scales, bf16 tensor-core math.  ``b_cache`` (a dict) keeps the expanded weight across
-    calls, as a static weight needs expanding only once."""
+def gemm_fp8_blockscaled(a_q, a_s, b_q, b_s, out=None, alpha: float = 1.0, pair: bool | None = None,
+                         max_ctas: int = 0, status_ptr: int = 0, stream=None):
+    """``out = (a_q * a_s [1x128 blocks]) @ (b_q * b_s [128x128 blocks]).T`` on the fp8 tensor
+    cores: the quantised operands are the MMA operands, and every 128-wide K block's partial sum
+    is multiplied by its two scales and accumulated in fp32 registers inside the kernel."""
+    lib = N.load()
+    _check(a_q, "a_q")
+    _check(b_q, "b_q")
+    M, K = a_q.shape
+    Nn = b_q.shape[0]
+    if a_q.dtype != torch.float8_e4m3fn or b_q.dtype != torch.float8_e4m3fn:
+        raise GemmError("operands must be float8_e4m3fn")
+    if K % 128 or b_q.shape[1] != K:
+        raise GemmError("K must be a multiple of 128 and equal for both operands")
+    if tuple(a_s.shape) != (M, K // 128) or tuple(b_s.shape) != ((Nn + 127) // 128, K // 128):
+        raise GemmError("scales must be [M, K/128] and [ceil(N/128), K/128]")
+    if not (a_s.is_contiguous() and b_s.is_contiguous() and a_s.dtype == torch.float32
+            and b_s.dtype == torch.float32):
+        raise GemmError("scales must be contiguous fp32 tensors")
+    if out is None:
+        out = torch.empty((M, Nn), dtype=torch.bfloat16, device=a_q.device)
+    _check(out, "out")
+    if pair is None:
+        nsm = torch.cuda.get_device_properties(a_q.device).multi_processor_count
+        pair = ((M + 255) // 256) * ((Nn + 255) // 256) * 2 >= nsm
+    rc = lib.cb_gemm_fp8_blockscaled(N.ptr(a_q), N.ptr(a_s), N.ptr(b_q), N.ptr(b_s), N.ptr(out), M,
+                                     Nn, K, C.c_float(alpha), int(bool(pair)), max_ctas,
+                                     C.c_void_p(status_ptr), N.stream_ptr(stream))
+    if rc != 0:
+        raise GemmError(f"gemm launch failed: {N.last_error()}")
+    return out
+
+
+def gemm_fp8_blockscaled_expanded(a_q, a_s, b_q, b_s, out=None, b_cache: dict | None = None):
+    """The same product through bf16: both operands are expanded by a bandwidth-bound kernel and
+    multiplied on the bf16 path.  Kept as the slow cross-check of :func:`gemm_fp8_blockscaled`.
+    ``b_cache`` (a dict) keeps the expanded weight across calls."""
     a = dequantize_blockscaled(a_q, a_s, 1)
     key = (b_q.data_ptr(), b_s.data_ptr())
     if b_cache is not None and key in b_cache:

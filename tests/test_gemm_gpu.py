@@ -89,8 +89,8 @@ def test_gemm_fp8_matches_fp32_reference(native_lib, shape):
 def test_blockscaled_fp8_roundtrip_and_gemm(native_lib):
     """1x128 activation scales and 128x128 weight scales: quantise, check against a PyTorch
     emulation of the same scheme, then run the GEMM on the expanded operands."""
-    from commbench_b200.ops.gemm import (dequantize_blockscaled, gemm_fp8_blockscaled,
-                                         quantize_blockscaled)
+    from commbench_b200.ops.gemm import (dequantize_blockscaled, quantize_blockscaled)
+    from commbench_b200.ops.gemm import gemm_fp8_blockscaled_expanded as gemm_fp8_blockscaled
 
     M, N, K = 256, 384, 512
     g = torch.Generator(device="cuda").manual_seed(21)
@@ -112,3 +112,39 @@ def test_blockscaled_fp8_roundtrip_and_gemm(native_lib):
     ref = ad.float() @ bd.float().t()
     _check(out, ref, 1e-2)
     _check(out, a.float() @ b.float().t(), 6e-2)
+
+
+def _bs_reference(aq, as_, bq, bs):
+    """fp32 product of the SAME quantised operands with their block scales applied."""
+    M, K = aq.shape
+    N = bq.shape[0]
+    a = aq.float().view(M, K // 128, 128) * as_[:, :, None]
+    bsr = bs.repeat_interleave(128, dim=0)[:N]
+    b = bq.float().view(N, K // 128, 128) * bsr[:, :, None]
+    return a.view(M, K) @ b.view(N, K).t()
+
+
+@pytest.mark.parametrize("pair", [True, False])
+@pytest.mark.parametrize("shape", [(128, 256, 128), (256, 256, 256), (512, 768, 1024),
+                                   (1000, 1304, 640), (256, 512, 4096)])
+def test_blockscaled_fp8_gemm_in_kernel_scales(native_lib, shape, pair):
+    """Block-scaled fp8 contraction with the scales applied inside the kernel (per K block,
+    fp32 promotion): against the fp32 product of the same quantised operands."""
+    from commbench_b200.ops.gemm import gemm_fp8_blockscaled, quantize_blockscaled
+
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(5 + M + N + K)
+    # magnitudes that differ per block, so that a wrong or missing scale shows
+    a = torch.randn(M, K, device="cuda", generator=g) * \
+        (1.0 + torch.arange(K // 128, device="cuda").float().repeat_interleave(128))[None, :]
+    b = torch.randn(N, K, device="cuda", generator=g) * 0.02 * \
+        (1.0 + (torch.arange(N, device="cuda") // 128).float())[:, None]
+    aq, as_ = quantize_blockscaled(a.bfloat16().contiguous(), 1)
+    bq, bs = quantize_blockscaled(b.bfloat16().contiguous(), 128)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    out = gemm_fp8_blockscaled(aq, as_, bq, bs, pair=pair, status_ptr=status.data_ptr())
+    torch.cuda.synchronize()
+    assert int(status[0].item()) == 0, hex(int(status[0].item()) & 0xffffffff)
+    ref = _bs_reference(aq, as_, bq, bs)
+    _check(out, ref, 1e-2)
+    _check(out, a.bfloat16().float() @ b.bfloat16().float().t(), 6e-2)

@@ -42,8 +42,16 @@ __global__ void dequant_blockscaled_kernel(const uint8_t* __restrict__ x,
 
 // bf16 [rows, K] -> e4m3 + scales (rb = 1: one scale per row and 128 columns; rb = 128: one
 // per 128 x 128 block).  One warp per (row block, k block).
+//
+// pow2 != 0: the scale is rounded UP to a power of two (so that it is exactly representable as an
+// 8-bit exponent, "UE8M0", the scale format the tensor cores apply in hardware) and, when
+// `sf_bytes` is given, its exponent byte is also written there in the packed layout of the
+// block-scaled GEMM: byte (kb % 4) of the 32-bit word [kb / 4][row], `sf_ld` = rows per K group.
+// For rb = 128 the byte is replicated to every row of the block (one byte per output column
+// of a GEMM and K block).
 __global__ void quant_blockscaled_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
-                                         float* __restrict__ scale, long long rows, int K, int rb) {
+                                         float* __restrict__ scale, long long rows, int K, int rb,
+                                         int pow2, uint8_t* __restrict__ sf_bytes, int sf_ld) {
   const int kblocks = K / 128;
   const long long nblocks = ((rows + rb - 1) / rb) * kblocks;
   const long long w = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
@@ -62,7 +70,21 @@ __global__ void quant_blockscaled_kernel(const __nv_bfloat16* __restrict__ x, ui
     amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))));
   }
   for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  const float s = amax > 0.f ? amax / 448.f : 1.f;
+  float s = amax > 0.f ? amax / 448.f : 1.f;
+  if (pow2) {
+    // smallest power of two >= s (clamped to the normal range): bump the exponent when any
+    // mantissa bit is set
+    uint32_t bits = __float_as_uint(s);
+    uint32_t e = (bits >> 23) & 0xffu;
+    if ((bits & 0x7fffffu) != 0u) ++e;
+    if (e < 1u) e = 1u;
+    if (e > 254u) e = 254u;
+    s = __uint_as_float(e << 23);
+    if (sf_bytes != nullptr)
+      for (long long r = r0 + lane; r < r1; r += 32)
+        sf_bytes[(static_cast<long long>(kb >> 2) * sf_ld + r) * 4 + (kb & 3)] =
+            static_cast<uint8_t>(e);
+  }
   const float inv = 1.f / s;
   if (lane == 0) scale[br * kblocks + kb] = s;
   for (long long r = r0; r < r1; ++r) {
@@ -109,7 +131,28 @@ int cb_quant_blockscaled(const void* x, void* q, void* scale, long long rows, in
   quant_blockscaled_kernel<<<static_cast<unsigned>(blocks), threads, 0,
                              static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), static_cast<float*>(scale),
-      rows, K, row_block);
+      rows, K, row_block, 0, nullptr, 0);
+  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// Same with power-of-two scales; `sf_words` = ceil(K / 512) x sf_rows 32-bit words (sf_rows >=
+// rows; pre-filled with 0x7f7f7f7f = 1.0 by the caller) receives the packed exponent bytes (see
+// the kernel).  Feeds cb_gemm_fp8_mx.
+int cb_quant_blockscaled_pow2(const void* x, void* q, void* scale, void* sf_words, int sf_rows,
+                              long long rows, int K, int row_block, void* stream) {
+  const void* sf_bytes = sf_words;
+  const int sf_ld = sf_rows;
+  if (K % 128 != 0 || (row_block != 1 && row_block != 128) || sf_rows < rows) {
+    set_last_error("block scales: K % 128 == 0, row_block 1 or 128, sf_rows >= rows");
+    return -1;
+  }
+  const long long nblocks = ((rows + row_block - 1) / row_block) * (K / 128);
+  const int threads = 256;
+  const long long blocks = (nblocks * 32 + threads - 1) / threads;
+  quant_blockscaled_kernel<<<static_cast<unsigned>(blocks), threads, 0,
+                             static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(q), static_cast<float*>(scale),
+      rows, K, row_block, 1, static_cast<uint8_t*>(const_cast<void*>(sf_bytes)), sf_ld);
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

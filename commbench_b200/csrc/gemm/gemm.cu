@@ -109,7 +109,8 @@ template <class Cfg>
 static int launch_plain(const void* a, const void* b, void* c, int M, int N, int K, float alpha,
                         uint32_t* status, int max_ctas, cudaStream_t st,
                         unsigned long long* trace = nullptr, const float* a_scale = nullptr,
-                        const float* b_scale = nullptr) {
+                        const float* b_scale = nullptr, const uint32_t* sfa = nullptr,
+                        const uint32_t* sfb = nullptr) {
   PlainParams p;
   const TmapDtype dt = Cfg::FP8 ? TMAP_U8 : TMAP_BF16;
   const unsigned esz = Cfg::FP8 ? 1 : 2;
@@ -130,6 +131,10 @@ static int launch_plain(const void* a, const void* b, void* c, int M, int N, int
   p.g.trace = trace;
   p.g.a_scale = a_scale;
   p.g.b_scale = b_scale;
+  p.g.sfa = sfa;
+  p.g.sfb = sfb;
+  p.g.sfa_rows = M;
+  p.g.sfb_rows = N;
   p.status = status;
   // Row blocks per raster panel: the panel's A rows (panel x K) stay in L2 while the B
   // tiles stream past them, so keep the panel near 32 MB.
@@ -279,6 +284,44 @@ int cb_gemm_fp8_blockscaled(const void* a, const void* a_scale, const void* b, c
                                                         nullptr, as, bs);
   return launch_plain<GemmCfg<256, 3, true, 1, true>>(a, b, c, M, N, K, alpha, s, max_ctas, st,
                                                       nullptr, as, bs);
+}
+
+// Block-scaled fp8 with POWER-OF-TWO scales applied by the tensor core: a [M,K], b [N,K] e4m3;
+// sfa [ceil(K/512), M] and sfb [ceil(K/512), N] 32-bit words, each packing the exponent bytes
+// (value 2^(byte - 127)) of four consecutive 128-wide K blocks of one operand row, lowest byte
+// first (cb_quant_blockscaled_pow2 writes them; for a 128 x 128-block weight every row of a
+// block carries the block's byte).  K % 128 == 0.
+int cb_gemm_fp8_mx_traced(const void* a, const void* sfa, const void* b, const void* sfb, void* c,
+                          int M, int N, int K, float alpha, int max_ctas, void* trace,
+                          void* status, void* stream);
+
+int cb_gemm_fp8_mx(const void* a, const void* sfa, const void* b, const void* sfb, void* c, int M,
+                   int N, int K, float alpha, int max_ctas, void* status, void* stream) {
+  return cb_gemm_fp8_mx_traced(a, sfa, b, sfb, c, M, N, K, alpha, max_ctas, nullptr, status,
+                               stream);
+}
+
+// The same with the MMA role's trace on (`trace`: 8 x number-of-SMs 64-bit words, may be null).
+int cb_gemm_fp8_mx_traced(const void* a, const void* sfa, const void* b, const void* sfb, void* c,
+                          int M, int N, int K, float alpha, int max_ctas, void* trace,
+                          void* status, void* stream) {
+  // max_ctas < 0 selects the one-CTA-per-tile form (128 x 192 tiles) instead of CTA pairs.
+  const bool single = max_ctas < 0;
+  if (single) max_ctas = 0;
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 128) != 0 || (N % 8) != 0 || sfa == nullptr ||
+      sfb == nullptr) {
+    set_last_error("cb_gemm_fp8_mx: need K % 128 == 0, N % 8 == 0 and both scale arrays");
+    return -1;
+  }
+  if (single)
+    return launch_plain<GemmCfg<192, 4, true, 1, false, true>>(
+        a, b, c, M, N, K, alpha, static_cast<uint32_t*>(status), max_ctas,
+        static_cast<cudaStream_t>(stream), static_cast<unsigned long long*>(trace), nullptr,
+        nullptr, static_cast<const uint32_t*>(sfa), static_cast<const uint32_t*>(sfb));
+  return launch_plain<GemmCfg<192, 6, true, 2, false, true>>(
+      a, b, c, M, N, K, alpha, static_cast<uint32_t*>(status), max_ctas,
+      static_cast<cudaStream_t>(stream), static_cast<unsigned long long*>(trace), nullptr, nullptr,
+      static_cast<const uint32_t*>(sfa), static_cast<const uint32_t*>(sfb));
 }
 
 }  // extern "C"

@@ -42,6 +42,15 @@
 // long K anyway - while the tensor core works on the next K block.  The quantised operands go
 // straight from memory into the MMA; nothing is expanded to bf16.
 //
+// Hardware block scaling (`MX_ = true`): when the scales are powers of two (8-bit exponents,
+// "UE8M0", chosen at quantisation) the tensor core applies them itself
+// (`tcgen05.mma.kind::mxf8f6f4.block_scale`), reading one scale byte per operand row and 32
+// K-elements from tensor memory, and the whole K loop accumulates in TMEM as in the unscaled
+// kernels.  Four scale warps (one per TMEM lane quadrant) fetch the bytes of the next K blocks
+// and store them into a ring of scale-factor columns beside the accumulators (tcgen05.st),
+// one slot per ring stage; tiles are 128 x 192 so that two accumulators and the ring fit
+// in the 512 columns.
+//
 // No load in this file is a cluster-multicast load.  Every wait is bounded: on a
 // time-out the CTA raises its abort word (and its partner's), every role leaves
 // its loop, in-flight copies get a grace period, TMEM is freed and the kernel
@@ -56,8 +65,12 @@
 
 namespace cb {
 
-template <int BN_, int STAGES_, bool FP8_, int PAIR_ = 1, bool BS_ = false>
+template <int BN_, int STAGES_, bool FP8_, int PAIR_ = 1, bool BS_ = false, bool MX_ = false>
 struct GemmCfg {
+  static constexpr bool MX = MX_;             // power-of-two block scales applied by the tensor core
+  static constexpr int SF_BASE = 2 * BN_;     // first scale-factor column in TMEM (MX)
+  static constexpr int SF_STRIDE = 16;        // columns per K block: 4 for A rows, up to 8 for B rows
+  static constexpr int SF_SLOTS = 8;          // K blocks of scale factors in TMEM: 2 groups of 4
   static constexpr int PAIR = PAIR_;          // CTAs that share a tile (1, or 2 = a cluster)
   static constexpr bool BS = BS_;             // block-scaled fp8 with promotion in registers
   static constexpr int EPI_WARPS = BS_ ? 8 : 4;
@@ -76,13 +89,17 @@ struct GemmCfg {
   static constexpr int EPI_BUF_BYTES = 32 * 128;      // 32 rows x 128 B per warp and buffer
   static constexpr int EPI_BYTES = EPI_WARPS * 2 * EPI_BUF_BYTES;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 1024;
-  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int TMEM_COLS = MX_ ? 512 : 2 * BN;
   // Warp roles.  Plain: producer, MMA, 4 epilogue warps, signal warp.  Block-scaled: a
   // utility warp-group (producer, MMA, signal, one idle warp) that gives registers away and
   // two epilogue warp-groups that take them (setmaxnreg works on whole warp-groups).
   static constexpr int EPI_WARP0 = BS_ ? 4 : 2;
   static constexpr int SIGNAL_WARP = BS_ ? 2 : 6;
-  static constexpr int THREADS = BS_ ? 384 : 224;
+  static constexpr int SCALE_WARP0 = 8;       // MX: warps 8..11 write scale factors
+  static constexpr int THREADS = (BS_ || MX_) ? 384 : 224;
+  static_assert(!MX_ || (FP8_ && !BS_ && BN_ <= 192 &&
+                         2 * BN_ + SF_SLOTS * SF_STRIDE <= 512),
+                "hardware block scales: fp8, accumulators + scale ring within 512 TMEM columns");
   static_assert(!BS_ || (FP8_ && BN_ == 256), "block scales: fp8 operands, 256-column tiles");
   static_assert(PAIR_ == 1 || PAIR_ == 2, "one CTA or a pair per tile");
   static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN in {64,128,192,256}");
@@ -99,6 +116,13 @@ struct GemmShape {
   // fp32, row-major (policies that gather A may supply their own through `a_scales`).
   const float* a_scale = nullptr;
   const float* b_scale = nullptr;
+  // Hardware block scales only: exponent bytes, one per operand row and 128-wide K block,
+  // packed four K blocks to a 32-bit word and stored K-group-major, word [kg * rows + row]
+  // (B: one row per output column), so that the 32 lanes of a scale warp read 32 consecutive
+  // words.  `sfa_rows` / `sfb_rows` are the row counts (pitches) of the two arrays.
+  const uint32_t* sfa = nullptr;
+  const uint32_t* sfb = nullptr;
+  int sfa_rows = 0, sfb_rows = 0;
   // Optional role trace, 8 words per CTA of the launch (null = off): SM clock cycles the
   // MMA thread spent waiting for operands [0] and for a free accumulator [1] and its total
   // [2]; the producer's wait for free ring slots [3] and total [4]; the first epilogue
@@ -146,6 +170,8 @@ struct GemmCtl {
   uint64_t empty[STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t sf_full[2];    // scale warps -> MMA thread: a group of 4 K blocks of scale factors is in TMEM
+  uint64_t sf_empty[2];   // MMA thread -> scale warps: the group's MMAs are done
   uint64_t sig_full[8];   // epilogue warps -> signal warp: a tile's stores were issued
   uint64_t sig_empty[8];  // signal warp -> epilogue warps: slot may be reused
   uint32_t tmem_base;
@@ -269,9 +295,10 @@ __device__ __forceinline__ void gemm_mma(const P& p, const GemmShape& g, uint8_t
                             tracing, &w_full))
         return;
       tc_fence_after_sync();
+      // operands computed warp-uniformly, outside the elected region
+      const uint64_t a_desc = a_desc0 + stage * kStageStep;
+      const uint64_t b_desc = a_desc + kBStep;
       if (elect_one()) {
-        const uint64_t a_desc = a_desc0 + stage * kStageStep;
-        const uint64_t b_desc = a_desc + kBStep;
 #pragma unroll
         for (int k = 0; k < Cfg::MMAS_PER_STAGE; ++k) {
           // 32 bytes along K per instruction: +2 in the descriptor's 16-byte address units.
@@ -375,6 +402,193 @@ __device__ __forceinline__ void gemm_mma_bs(const P& p, const GemmShape& g, uint
       }
       buf ^= 1u;
       if (buf == 0u) buf_phase ^= 1u;
+    }
+  }
+}
+
+// MMA role with hardware block scales: as gemm_mma, plus the wait for the stage's scale
+// factors and the scale-factor operands of the instruction.
+template <class Cfg, class Policy, class P>
+__device__ __forceinline__ void gemm_mma_mx(const P& p, const GemmShape& g, uint8_t* ring,
+                                            GemmCtl<Cfg::STAGES>* ctl, uint32_t* status, int cta,
+                                            int num_ctas, uint32_t tmem_base) {
+  uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+  const int ntiles = Policy::num_tiles(p);
+  const uint64_t a_desc0 = make_sw128_kmajor_desc(smem_u32(ring));
+  constexpr uint64_t kStageStep = static_cast<uint64_t>(Cfg::STAGE_BYTES >> 4);
+  constexpr uint64_t kBStep = static_cast<uint64_t>(Cfg::A_BYTES >> 4);
+  const uint32_t empty0 = smem_u32(&ctl->empty[0]);
+  const uint32_t tfull0 = smem_u32(&ctl->tmem_full[0]);
+  const uint32_t sfe0 = smem_u32(&ctl->sf_empty[0]);
+  const uint32_t empty0_peer = Cfg::PAIR == 2 ? map_to_cta(empty0, 1) : 0u;
+  const uint32_t tfull0_peer = Cfg::PAIR == 2 ? map_to_cta(tfull0, 1) : 0u;
+  const uint32_t sfe0_peer = Cfg::PAIR == 2 ? map_to_cta(sfe0, 1) : 0u;
+  uint32_t gcount = 0;  // groups of 4 K blocks so far (a tile starts a new group)
+  const bool tracing = g.trace != nullptr;  // [0] operands, [1] accumulator + scale factors
+  long long w_full = 0, w_other = 0;
+  const long long t_begin = tracing ? clock64() : 0;
+  for (int tile = cta; tile < ntiles; tile += num_ctas) {
+    if (!mbar_wait_traced(&ctl->tmem_empty[acc], acc_phase ^ 1u, &ctl->abort_flag, status,
+                          0x200 + acc, tracing, &w_other))
+      return;
+    tc_fence_after_sync();
+    const uint32_t d_tmem = tmem_base + acc * Cfg::BN;
+    for (int kb = 0; kb < g.num_k_blocks; ++kb) {
+      const uint32_t grp = gcount & 1u;
+      if ((kb & 3) == 0 &&
+          !mbar_wait_traced(&ctl->sf_full[grp], (gcount >> 1) & 1u, &ctl->abort_flag, status,
+                            0x380 + grp, tracing, &w_other))
+        return;
+      if (!mbar_wait_traced(&ctl->full[stage], phase, &ctl->abort_flag, status, 0x300 + stage,
+                            tracing, &w_full))
+        return;
+      tc_fence_after_sync();
+      const bool group_ends = (kb & 3) == 3 || kb == g.num_k_blocks - 1;
+      // Operands are computed by the whole (converged) warp, so they can live in uniform
+      // registers; only the asynchronous instructions themselves sit under the election.
+      const uint64_t a_desc = a_desc0 + stage * kStageStep;
+      const uint64_t b_desc = a_desc + kBStep;
+      const uint32_t sfa =
+          tmem_base + Cfg::SF_BASE + (grp * 4u + static_cast<uint32_t>(kb & 3)) * Cfg::SF_STRIDE;
+      const uint32_t sfb = sfa + 4u;
+      const uint32_t first = kb > 0 ? 1u : 0u;
+      if (elect_one()) {
+        // Four K steps of 32; step j takes byte j of the scale columns.
+        if constexpr (Cfg::PAIR == 2) {
+          mma_mxf8_ss_pair(d_tmem, a_desc, b_desc, make_idesc_mx(Cfg::BM, Cfg::BN, 0u), sfa, sfb, first);
+          mma_mxf8_ss_pair(d_tmem, a_desc + 2u, b_desc + 2u, make_idesc_mx(Cfg::BM, Cfg::BN, 1u), sfa, sfb, 1u);
+          mma_mxf8_ss_pair(d_tmem, a_desc + 4u, b_desc + 4u, make_idesc_mx(Cfg::BM, Cfg::BN, 2u), sfa, sfb, 1u);
+          mma_mxf8_ss_pair(d_tmem, a_desc + 6u, b_desc + 6u, make_idesc_mx(Cfg::BM, Cfg::BN, 3u), sfa, sfb, 1u);
+          mma_commit_pair(empty0 + stage * 8u);
+          mma_commit_pair(empty0_peer + stage * 8u);
+          if (group_ends) {  // the group's scale columns are free, in both CTAs
+            mma_commit_pair(sfe0 + grp * 8u);
+            mma_commit_pair(sfe0_peer + grp * 8u);
+          }
+        } else {
+          mma_mxf8_ss(d_tmem, a_desc, b_desc, make_idesc_mx(Cfg::BM, Cfg::BN, 0u), sfa, sfb, first);
+          mma_mxf8_ss(d_tmem, a_desc + 2u, b_desc + 2u, make_idesc_mx(Cfg::BM, Cfg::BN, 1u), sfa, sfb, 1u);
+          mma_mxf8_ss(d_tmem, a_desc + 4u, b_desc + 4u, make_idesc_mx(Cfg::BM, Cfg::BN, 2u), sfa, sfb, 1u);
+          mma_mxf8_ss(d_tmem, a_desc + 6u, b_desc + 6u, make_idesc_mx(Cfg::BM, Cfg::BN, 3u), sfa, sfb, 1u);
+          mma_commit_addr(empty0 + stage * 8u);
+          if (group_ends) mma_commit_addr(sfe0 + grp * 8u);  // the group's scale columns are free
+        }
+      }
+      __syncwarp();
+      if (group_ends) ++gcount;
+      if (++stage == Cfg::STAGES) {
+        stage = 0;
+        phase ^= 1u;
+      }
+    }
+    if (elect_one()) {
+      if constexpr (Cfg::PAIR == 2) {
+        mma_commit_pair(tfull0 + acc * 8u);
+        mma_commit_pair(tfull0_peer + acc * 8u);
+      } else {
+        mma_commit_addr(tfull0 + acc * 8u);
+      }
+    }
+    __syncwarp();
+    acc ^= 1u;
+    if (acc == 0u) acc_phase ^= 1u;
+  }
+  if (tracing && (threadIdx.x & 31u) == 0) {
+    g.trace[blockIdx.x * 8 + 0] = static_cast<unsigned long long>(w_full);
+    g.trace[blockIdx.x * 8 + 1] = static_cast<unsigned long long>(w_other);
+    g.trace[blockIdx.x * 8 + 2] = static_cast<unsigned long long>(clock64() - t_begin);
+  }
+}
+
+// Packed exponent words of the A rows of a tile (K group 0; a K group further is `*pitch`
+// words on): GemmShape::sfa at the policy's A row, unless the policy gathered A from other ranks
+// and names its own source (`a_sf(p, m_blk, &pitch)`).
+template <class Policy, class P>
+__device__ __forceinline__ const uint32_t* tile_a_sf(const P& p, const GemmShape& g, int m_blk,
+                                                     long long* pitch) {
+  if constexpr (requires { Policy::a_sf(p, m_blk, pitch); }) {
+    return Policy::a_sf(p, m_blk, pitch);
+  } else {
+    *pitch = g.sfa_rows;
+    return g.sfa + Policy::a_row(p, m_blk);
+  }
+}
+
+// Scale warp (one per TMEM lane quadrant; all four write the same data, the layout wants it
+// replicated): lane l holds rows l, l+32, l+64, l+96 of A and l, l+32, ... of the B tile.  It
+// works in groups of four K blocks - one 32-bit load per row brings their four exponent bytes,
+// the next group's loads in flight meanwhile - and two groups of TMEM columns alternate: wait
+// until the MMAs of the group's previous use are done, store 4 x (4 + 8) columns, one
+// tcgen05.wait::st, one arrival.
+template <class Cfg, class Policy, class P>
+__device__ __forceinline__ void gemm_scale_writer(const P& p, const GemmShape& g,
+                                                  GemmCtl<Cfg::STAGES>* ctl, uint32_t* status,
+                                                  int cta, int num_ctas, uint32_t tmem_base,
+                                                  uint32_t warp, uint32_t lane, int sub) {
+  constexpr int NB = Cfg::BN / 32;  // B-row groups of this tile (<= 8)
+  const uint32_t q = warp & 3u;
+  uint32_t gcount = 0;  // groups of 4 K blocks so far, in step with the MMA role
+  const int ntiles = Policy::num_tiles(p);
+  const int nkb = g.num_k_blocks;
+  const uint32_t t0 = tmem_base + ((q * 32u) << 16) + Cfg::SF_BASE;
+  constexpr uint32_t kOne = 0x7f7f7f7fu;  // exponent 127 = 1.0, for rows outside the operands
+  for (int tile = cta; tile < ntiles; tile += num_ctas) {
+    int m_blk, n_blk;
+    Policy::tile_coord(p, tile, &m_blk, &n_blk);
+    // this CTA's 128 rows of the tile; all BN columns of B
+    long long pitch_a = 0;
+    const uint32_t* pa = tile_a_sf<Policy>(p, g, m_blk, &pitch_a) + sub * Cfg::CTA_M;
+    const int a_rows_left = g.M - m_blk * Cfg::BM - sub * Cfg::CTA_M;
+    const int b_row0 = Policy::b_row(p, m_blk, n_blk);
+    const int b_rows_left = g.N - n_blk * Cfg::BN;
+    auto load_group = [&](int kb, uint32_t (&wa)[4], uint32_t (&wb)[NB]) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int r = c * 32 + static_cast<int>(lane);
+        wa[c] = (kb < nkb && r < a_rows_left) ? __ldg(pa + (kb >> 2) * pitch_a + r) : kOne;
+      }
+#pragma unroll
+      for (int c = 0; c < NB; ++c) {
+        const int r = c * 32 + static_cast<int>(lane);
+        wb[c] = (kb < nkb && r < b_rows_left)
+                    ? __ldg(g.sfb + static_cast<long long>(kb >> 2) * g.sfb_rows + b_row0 + r)
+                    : kOne;
+      }
+    };
+    uint32_t wa[4], wb[NB], na[4], nb[NB];
+    load_group(0, wa, wb);
+    for (int kg = 0; kg < nkb; kg += 4) {
+      load_group(kg + 4, na, nb);  // in flight while this group is written
+      const uint32_t grp = gcount & 1u;
+      if (!mbar_wait_traced(&ctl->sf_empty[grp], ((gcount >> 1) & 1u) ^ 1u, &ctl->abort_flag,
+                            status, 0x500 + grp, false, nullptr))
+        return;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t ra[4], rb[8];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) ra[c] = ((wa[c] >> (8 * j)) & 0xffu) * 0x01010101u;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          rb[c] = c < NB ? ((wb[c < NB ? c : 0] >> (8 * j)) & 0xffu) * 0x01010101u : kOne;
+        const uint32_t t = t0 + (grp * 4u + j) * Cfg::SF_STRIDE;
+        tmem_st_32x4(t, ra);
+        tmem_st_32x8(t + 4u, rb);
+      }
+      tmem_wait_st();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if (Cfg::PAIR == 2 && sub != 0)
+          mbar_arrive_cluster(map_to_cta(smem_u32(&ctl->sf_full[grp]), 0));
+        else
+          mbar_arrive(&ctl->sf_full[grp]);
+      }
+      ++gcount;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) wa[c] = na[c];
+#pragma unroll
+      for (int c = 0; c < NB; ++c) wb[c] = nb[c];
     }
   }
 }
@@ -983,6 +1197,10 @@ __device__ __forceinline__ uint32_t gemm_setup(GemmCtl<Cfg::STAGES>* ctl, uint32
       mbar_init(&ctl->full[s], 1);
       mbar_init(&ctl->empty[s], 1);
     }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&ctl->sf_full[i], 4 * Cfg::PAIR);  // one arrival per scale warp (of the pair)
+      mbar_init(&ctl->sf_empty[i], 1);
+    }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&ctl->tmem_full[a], 1);
       mbar_init(&ctl->tmem_empty[a], Cfg::EPI_WARPS * Cfg::PAIR);  // one arrival per epilogue warp (of the pair)
@@ -1086,11 +1304,21 @@ __device__ __forceinline__ void gemm_cta_main(const P& p, const GemmShape& g, ui
   } else if (warp == 0) {
     gemm_producer<Cfg, Policy>(p, g, ring, &ctl, status, worker, num_workers, sub);
   } else if (warp == 1) {
-    if (sub == 0) gemm_mma<Cfg, Policy>(p, g, ring, &ctl, status, worker, num_workers, tmem_base);
+    if constexpr (Cfg::MX) {
+      if (sub == 0)
+        gemm_mma_mx<Cfg, Policy>(p, g, ring, &ctl, status, worker, num_workers, tmem_base);
+    } else {
+      if (sub == 0)
+        gemm_mma<Cfg, Policy>(p, g, ring, &ctl, status, worker, num_workers, tmem_base);
+    }
+  } else if (Cfg::MX && warp >= Cfg::SCALE_WARP0) {
+    if constexpr (Cfg::MX)
+      gemm_scale_writer<Cfg, Policy>(p, g, &ctl, status, worker, num_workers, tmem_base, warp,
+                                     lane, sub);
   } else if (warp < 2 + Cfg::EPI_WARPS) {
     gemm_epilogue<Cfg, Policy>(p, g, epi, &ctl, status, worker, num_workers, tmem_base, warp,
                                lane, sub);
-  } else {
+  } else if (warp == Cfg::SIGNAL_WARP) {
     if constexpr (Policy::kDirect && Policy::kSignalPerTile) {
       if (lane == 0) gemm_signal<Cfg, Policy>(p, &ctl, status, worker, num_workers, sub);
     }

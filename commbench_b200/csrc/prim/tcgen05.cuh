@@ -124,6 +124,57 @@ __device__ __forceinline__ void mma_commit_addr(uint32_t bar_addr) {
                : "memory");
 }
 
+// Block-scaled fp8 MMA (`kind::mxf8f6f4.block_scale`): D (+)= (A * SFA) * (B * SFB)^T with one
+// 8-bit power-of-two scale (UE8M0) per operand row and 32 K-elements, read from tensor memory.
+// Scale-factor layout in TMEM (32-bit columns starting at `sfa_tmem` / `sfb_tmem`): the scale
+// of row r for K step j of a group of four sits in lane r % 32 (of EVERY 32-lane quadrant: the
+// data is replicated over the four quadrants), column r / 32, byte j; the instruction
+// descriptor's a_sf_id / b_sf_id fields pick the byte.
+__host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t m, uint32_t n, uint32_t sf_id) {
+  return (0u << 7) | (0u << 10) |   // A, B = e4m3
+         (0u << 15) | (0u << 16) |  // K-major
+         ((n >> 3) << 17) | (1u << 23) /* scales are UE8M0 */ | ((m >> 4) << 24) |
+         (sf_id << 29) /* a_sf_id */ | (sf_id << 4) /* b_sf_id */;
+}
+__device__ __forceinline__ void mma_mxf8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// CTA-pair form (M = 256): each CTA's tensor memory holds the scale factors of its own 128 A rows
+// and of ALL N columns of B, at the same addresses in both CTAs.
+__device__ __forceinline__ void mma_mxf8_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                 uint32_t idesc, uint32_t sfa_tmem,
+                                                 uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// 32 lanes x 4 / 8 columns stores (registers -> TMEM), thread t writes lane (base + t).
+__device__ __forceinline__ void tmem_st_32x4(uint32_t taddr, const uint32_t (&r)[4]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr),
+               "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+      : "memory");
+}
+
 // ------------------------------------------------- CTA pairs (cta_group::2)
 // A pair is the two CTAs of a cluster of 2.  Both CTAs run the allocation and
 // the free (same warp index, same shared-memory word), the even CTA issues the

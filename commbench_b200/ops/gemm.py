@@ -100,6 +100,64 @@ def quantize_blockscaled(x: torch.Tensor, row_block: int = 1):
     return q, s
 
 
+def quantize_blockscaled_pow2(x: torch.Tensor, row_block: int = 1):
+    """As :func:`quantize_blockscaled` with every scale rounded up to a power of two, the form
+    the tensor cores can apply themselves.  Returns ``(q, scales fp32, sf)`` where ``sf`` is an
+    int32 tensor ``[ceil(K/512), rows]``: word ``[kg, r]`` packs the exponent bytes (value
+    ``2 ** (byte - 127)``) of K blocks ``4 kg .. 4 kg + 3`` of row ``r``, lowest byte first
+    (missing blocks: 127).  For ``row_block=128`` every row of a block carries the block's
+    byte, so ``sf`` has one column per row of ``x`` either way - what :func:`gemm_fp8_mx` takes."""
+    lib = N.load()
+    _check(x, "x")
+    rows, K = x.shape
+    q = torch.empty(rows, K, dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty((rows + row_block - 1) // row_block, K // 128, dtype=torch.float32,
+                    device=x.device)
+    sf = torch.full(((K // 128 + 3) // 4, rows), 0x7f7f7f7f, dtype=torch.int32, device=x.device)
+    rc = lib.cb_quant_blockscaled_pow2(N.ptr(x), N.ptr(q), N.ptr(s), N.ptr(sf), rows,
+                                       C.c_longlong(rows), K, row_block, N.stream_ptr())
+    if rc != 0:
+        raise GemmError(N.last_error())
+    return q, s, sf
+
+
+def sf_exponents(sf: torch.Tensor, kblocks: int) -> torch.Tensor:
+    """Unpacks :func:`quantize_blockscaled_pow2`'s words to exponent bytes ``[rows, kblocks]``."""
+    kg, rows = sf.shape
+    b = sf.view(torch.uint8).view(kg, rows, 4).permute(1, 0, 2).reshape(rows, kg * 4)
+    return b[:, :kblocks]
+
+
+def gemm_fp8_mx(a_q, a_sf, b_q, b_sf, out=None, alpha: float = 1.0, pair: bool = True,
+                status_ptr: int = 0, stream=None):
+    """``out = (a_q * 2^(a_sf-127)) @ (b_q * 2^(b_sf-127)).T`` with the power-of-two block scales
+    applied by the tensor cores (``tcgen05.mma.kind::mxf8f6f4.block_scale``): ``a_sf``
+    [ceil(K/512), M], ``b_sf`` [ceil(K/512), N] int32 from :func:`quantize_blockscaled_pow2`."""
+    lib = N.load()
+    _check(a_q, "a_q")
+    _check(b_q, "b_q")
+    M, K = a_q.shape
+    Nn = b_q.shape[0]
+    if a_q.dtype != torch.float8_e4m3fn or b_q.dtype != torch.float8_e4m3fn:
+        raise GemmError("operands must be float8_e4m3fn")
+    if K % 128 or b_q.shape[1] != K:
+        raise GemmError("K must be a multiple of 128 and equal for both operands")
+    kg = (K // 128 + 3) // 4
+    for t, rows, name in ((a_sf, M, "a_sf"), (b_sf, Nn, "b_sf")):
+        if not (t.dtype == torch.int32 and t.is_contiguous() and tuple(t.shape) == (kg, rows)):
+            raise GemmError(f"{name} must be a contiguous int32 tensor [{kg}, {rows}]")
+    if out is None:
+        out = torch.empty((M, Nn), dtype=torch.bfloat16, device=a_q.device)
+    _check(out, "out")
+    # pair: a CTA pair per 256 x 192 tile (default, fastest); otherwise one CTA per 128 x 192
+    rc = lib.cb_gemm_fp8_mx(N.ptr(a_q), N.ptr(a_sf), N.ptr(b_q), N.ptr(b_sf), N.ptr(out), M, Nn, K,
+                            C.c_float(alpha), 0 if pair else -1, C.c_void_p(status_ptr),
+                            N.stream_ptr(stream))
+    if rc != 0:
+        raise GemmError(f"gemm launch failed: {N.last_error()}")
+    return out
+
+
 def dequantize_blockscaled(q: torch.Tensor, s: torch.Tensor, row_block: int = 1,
                            out: torch.Tensor | None = None) -> torch.Tensor:
     lib = N.load()

@@ -148,3 +148,45 @@ def test_blockscaled_fp8_gemm_in_kernel_scales(native_lib, shape, pair):
     ref = _bs_reference(aq, as_, bq, bs)
     _check(out, ref, 1e-2)
     _check(out, a.bfloat16().float() @ b.bfloat16().float().t(), 6e-2)
+
+
+def test_pow2_quantisation_bytes_match_scales(native_lib):
+    from commbench_b200.ops.gemm import quantize_blockscaled_pow2, sf_exponents
+
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = (torch.randn(300, 640, device="cuda", generator=g) * 3).bfloat16()
+    for rb in (1, 128):
+        q, s, sf = quantize_blockscaled_pow2(x, rb)
+        assert sf.shape == (2, 300)
+        assert torch.equal(torch.exp2(torch.log2(s).round()), s)          # powers of two
+        per_row = s.repeat_interleave(rb, dim=0)[:300]
+        assert torch.equal(torch.exp2(sf_exponents(sf, 5).float() - 127.0), per_row)
+        assert bool((sf_exponents(sf, 8)[:, 5:] == 127).all())             # padding = 1.0
+        amax = x.float().view(300, 5, 128).abs().amax(-1)
+        if rb == 1:
+            assert bool((s >= amax / 448.0).all()) and bool((s < 2 * amax / 448.0 + 1e-30).all())
+
+
+@pytest.mark.parametrize("pair", [True, False])
+@pytest.mark.parametrize("shape", [(128, 192, 128), (128, 192, 512), (256, 384, 1024),
+                                   (1000, 1304, 640), (512, 8192, 2048)])
+def test_fp8_gemm_with_hardware_block_scales(native_lib, shape, pair):
+    """Power-of-two 1x128 / 128x128 block scales applied by the tensor core: against the fp32
+    product of the same quantised operands with the same scales."""
+    from commbench_b200.ops.gemm import gemm_fp8_mx, quantize_blockscaled_pow2
+
+    M, N, K = shape
+    g = torch.Generator(device="cuda").manual_seed(9 + M + N + K)
+    a = torch.randn(M, K, device="cuda", generator=g) * \
+        (1.0 + torch.arange(K // 128, device="cuda").float().repeat_interleave(128))[None, :] * \
+        (1.0 + (torch.arange(M, device="cuda") % 7).float())[:, None]
+    b = torch.randn(N, K, device="cuda", generator=g) * 0.02 * \
+        (1.0 + (torch.arange(N, device="cuda") // 128).float())[:, None]
+    aq, as_, asf = quantize_blockscaled_pow2(a.bfloat16().contiguous(), 1)
+    bq, bs, bsf = quantize_blockscaled_pow2(b.bfloat16().contiguous(), 128)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    out = gemm_fp8_mx(aq, asf, bq, bsf, pair=pair, status_ptr=status.data_ptr())
+    torch.cuda.synchronize()
+    assert int(status[0].item()) == 0, hex(int(status[0].item()) & 0xffffffff)
+    ref = _bs_reference(aq, as_, bq, bs)
+    _check(out, ref, 1e-2)

@@ -47,6 +47,11 @@ struct AgGemmParams {
   FusedSeq seq;
   uint32_t* status;
   unsigned long long timeout_ns;
+  // Hardware block scales (fp8): packed exponent words of the local A rows [K groups][M / W]
+  // and, per parity and rank, of the gathered rows [K groups][M]; K groups = ceil(K / 512).
+  const uint32_t* a_sf_local;
+  uint32_t* a_sf_full_peer[2][CB_MAX_RANKS];
+  int sf_kgroups;
 };
 
 struct AgRt {
@@ -100,6 +105,16 @@ struct AgPolicy {
     // The rows were written by a peer's bulk copies; our TMA load must see them.
     fence_proxy_async();
     return true;
+  }
+  // Scale words of a tile's A rows: this rank's own array, or the gathered one.
+  __device__ static const uint32_t* a_sf(const AgRt& r, int m_blk, long long* pitch) {
+    const AgGemmParams& p = *r.p;
+    if (is_local(p, m_blk)) {
+      *pitch = p.g.M / p.world;
+      return p.a_sf_local + (m_blk - p.rank * p.blocks_per_rank) * Cfg::BM;
+    }
+    *pitch = p.g.M;
+    return p.a_sf_full_peer[r.parity][p.rank] + m_blk * Cfg::BM;
   }
   static constexpr bool kDirect = false;  // C is local: TMA-store epilogue
   static constexpr bool kSignalPerTile = false;
@@ -161,6 +176,19 @@ __device__ __forceinline__ void ag_comm_cta(const AgGemmParams& p, uint32_t pari
         for (int d = 1; d < p.world; ++d)
           st_sys_v4(reinterpret_cast<uint4*>(p.a_full_peer[parity][(p.rank + d) % p.world]) +
                         dst_vec + i, v);
+      }
+    }
+    // Block-scaled operands: the row block's scale words travel with its first piece.
+    if (p.a_sf_local != nullptr && part == 0) {
+      const int bm = static_cast<int>(p.row_block_bytes / (static_cast<unsigned long long>(p.g.K)));
+      const int Ml = p.g.M / p.world;
+      for (int w = threadIdx.x; w < p.sf_kgroups * bm; w += blockDim.x) {
+        const int kg = w / bm, rr = w - kg * bm;
+        const uint32_t v = p.a_sf_local[static_cast<long long>(kg) * Ml + rb * bm + rr];
+        const long long dst = static_cast<long long>(kg) * p.g.M +
+                              (p.rank * p.blocks_per_rank + rb) * bm + rr;
+        for (int d = 1; d < p.world; ++d)
+          st_relaxed_sys(p.a_sf_full_peer[parity][(p.rank + d) % p.world] + dst, v);
       }
     }
     // One thread fences for the CTA (the barrier makes the others' stores precede it);
@@ -263,15 +291,27 @@ struct CbAgGemmDesc {
   void* seq;              // uint32 [2] local: {call counter, done CTAs}
   void* status;
   unsigned long long timeout_ns;
+  // bn == 192 only (fp8 with power-of-two block scales applied by the tensor core, CTA pairs on
+  // 256 x 192 tiles): packed exponent words, see cb_gemm_fp8_mx.
+  const void* a_sf_local;                 // [ceil(K/512)][M / world]
+  void* a_sf_full_peer[2][CB_MAX_RANKS];  // [ceil(K/512)][M] per parity and rank
+  const void* b_sf;                       // [ceil(K/512)][N]
 };
 
 static int build_ag_params(const CbAgGemmDesc& d, AgGemmParams* p) {
   const int esz = d.fp8 ? 1 : 2;
   const int BK = d.fp8 ? 128 : 64;
   const TmapDtype dt = d.fp8 ? TMAP_U8 : TMAP_BF16;
-  const int pair = d.bn == 512 ? 2 : 1;
+  const bool mx = d.bn == 192;
+  const int pair = (d.bn == 512 || mx) ? 2 : 1;
   const int bm = 128 * pair;                 // tile height = rows per flag
   const int tile_n = d.bn == 512 ? 256 : d.bn;
+  if (mx && (!d.fp8 || d.K % 128 != 0 || d.a_sf_local == nullptr || d.b_sf == nullptr ||
+             (d.world > 1 && d.a_sf_full_peer[0][d.rank] == nullptr))) {
+    set_last_error("ag_gemm: bn 192 is the block-scaled fp8 form: fp8 inputs, K % 128 == 0 and "
+                   "scale words for A (local and gathered) and B");
+    return -1;
+  }
   if (d.world < 1 || d.M % (d.world * bm) != 0) {
     set_last_error("ag_gemm: M must be a multiple of world * tile height (128, or 256 for bn 512)");
     return -1;
@@ -334,6 +374,13 @@ static int build_ag_params(const CbAgGemmDesc& d, AgGemmParams* p) {
   p->seq.done_ctas = static_cast<uint32_t*>(d.seq) + 1;
   p->status = static_cast<uint32_t*>(d.status);
   p->timeout_ns = d.timeout_ns;
+  p->a_sf_local = mx ? static_cast<const uint32_t*>(d.a_sf_local) : nullptr;
+  for (int par = 0; par < 2; ++par)
+    for (int r = 0; r < CB_MAX_RANKS; ++r)
+      p->a_sf_full_peer[par][r] = mx ? static_cast<uint32_t*>(d.a_sf_full_peer[par][r]) : nullptr;
+  p->sf_kgroups = (d.K / 128 + 3) / 4;
+  p->g.sfb = mx ? static_cast<const uint32_t*>(d.b_sf) : nullptr;
+  p->g.sfb_rows = d.N;
   if (d.world > 1 && p->num_comm_ctas < 1) {
     set_last_error("ag_gemm: world > 1 needs at least one comm CTA");
     return -1;
@@ -374,6 +421,8 @@ int cb_ag_gemm(const CbAgGemmDesc* descs, int n, void* emu_table, void* stream) 
   }
   const CbAgGemmDesc& d = descs[0];
   if (d.fp8) {
+    if (d.bn == 192)
+      return launch_ag<GemmCfg<192, 6, true, 2, false, true>>(hp[0], emu, n, d.ctas_per_rank, st);
     if (d.bn == 512)
       return launch_ag<GemmCfg<256, 6, true, 2>>(hp[0], emu, n, d.ctas_per_rank, st);
     if (d.bn == 256) return launch_ag<GemmCfg<256, 4, true>>(hp[0], emu, n, d.ctas_per_rank, st);

@@ -216,15 +216,25 @@ struct CbGemmRsDesc {
   void* seq;
   void* status;
   unsigned long long timeout_ns;
+  // bn == 192 only (fp8 with power-of-two block scales, CTA pairs on 256 x 192 tiles): packed
+  // exponent words, see cb_gemm_fp8_mx.
+  const void* a_sf;   // [ceil(K/512)][M]
+  const void* b_sf;   // [ceil(K/512)][N]
 };
 
 static int build_rs_params(const CbGemmRsDesc& d, GemmRsParams* p) {
   const int esz = d.fp8 ? 1 : 2;
   const int BK = d.fp8 ? 128 : 64;
   const TmapDtype dt = d.fp8 ? TMAP_U8 : TMAP_BF16;
-  const int pair = d.bn == 512 ? 2 : 1;
+  const bool mx = d.bn == 192;
+  const int pair = (d.bn == 512 || mx) ? 2 : 1;
   const int bm = 128 * pair;
   const int tile_n = d.bn == 512 ? 256 : d.bn;
+  if (mx && (!d.fp8 || d.K % 128 != 0 || d.a_sf == nullptr || d.b_sf == nullptr)) {
+    set_last_error("gemm_rs: bn 192 is the block-scaled fp8 form: fp8 inputs, K % 128 == 0 and "
+                   "scale words for A and B");
+    return -1;
+  }
   if (d.world < 1 || d.M % (d.world * bm) != 0) {
     set_last_error("gemm_rs: M must be a multiple of world * tile height (128, or 256 for bn 512)");
     return -1;
@@ -256,6 +266,10 @@ static int build_rs_params(const CbGemmRsDesc& d, GemmRsParams* p) {
   p->g.num_n_blocks = num_n;
   p->g.num_k_blocks = (d.K + BK - 1) / BK;
   p->g.alpha = d.alpha;
+  p->g.sfa = mx ? static_cast<const uint32_t*>(d.a_sf) : nullptr;
+  p->g.sfb = mx ? static_cast<const uint32_t*>(d.b_sf) : nullptr;
+  p->g.sfa_rows = d.M;
+  p->g.sfb_rows = d.N;
   p->rank = d.rank;
   p->world = d.world;
   p->blocks_per_rank = Ml / bm;
@@ -295,6 +309,8 @@ int cb_gemm_rs(const CbGemmRsDesc* descs, int n, void* emu_table, void* stream) 
   }
   const CbGemmRsDesc& d = descs[0];
   if (d.fp8) {
+    if (d.bn == 192)
+      return launch_rs<GemmCfg<192, 6, true, 2, false, true>>(hp[0], emu, n, d.ctas_per_rank, st);
     if (d.bn == 512)
       return launch_rs<GemmCfg<256, 6, true, 2>>(hp[0], emu, n, d.ctas_per_rank, st);
     if (d.bn == 256) return launch_rs<GemmCfg<256, 4, true>>(hp[0], emu, n, d.ctas_per_rank, st);

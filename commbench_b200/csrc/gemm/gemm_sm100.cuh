@@ -176,6 +176,7 @@ struct GemmCtl {
   uint64_t sig_empty[8];  // signal warp -> epilogue warps: slot may be reused
   uint32_t tmem_base;
   int abort_flag;
+  int a_ready_tiles;  // tiles whose A rows the producer has found ready (read by the scale warps)
 };
 
 // The three role loops.  `P` is the policy's parameter block.
@@ -218,6 +219,7 @@ __device__ __forceinline__ void gemm_producer(const P& p, const GemmShape& g, ui
   const uint32_t lane = threadIdx.x & 31u;
   const uint32_t ring_addr = smem_u32(ring);
   const uint32_t full0 = smem_u32(&ctl->full[0]);
+  int ready_tiles = 0;
   // Pair: both CTAs' bytes are counted on the even CTA's barrier, the one its MMA warp waits on.
   const uint32_t full0_leader = Cfg::PAIR == 2 ? map_to_cta(full0, 0) : full0;
   for (int tile = cta; tile < ntiles; tile += num_ctas) {
@@ -227,6 +229,12 @@ __device__ __forceinline__ void gemm_producer(const P& p, const GemmShape& g, ui
     int ready = 1;
     if (lane == 0) ready = Policy::wait_a_ready(p, m_blk, &ctl->abort_flag) ? 1 : 0;
     if (__shfl_sync(0xffffffffu, ready, 0) == 0) return;
+    if constexpr (Cfg::MX) {
+      if (lane == 0) {
+        __threadfence_block();
+        *reinterpret_cast<volatile int*>(&ctl->a_ready_tiles) = ++ready_tiles;
+      }
+    }
     const CUtensorMap* ma = Policy::map_a(p, m_blk);
     const CUtensorMap* mb = Policy::map_b(p);
     const int arow = Policy::a_row(p, m_blk) + sub * Cfg::CTA_M;
@@ -528,6 +536,7 @@ __device__ __forceinline__ void gemm_scale_writer(const P& p, const GemmShape& g
   constexpr int NB = Cfg::BN / 32;  // B-row groups of this tile (<= 8)
   const uint32_t q = warp & 3u;
   uint32_t gcount = 0;  // groups of 4 K blocks so far, in step with the MMA role
+  int tcount = 0;       // tiles so far, against the producer's count of tiles whose A rows are there
   const int ntiles = Policy::num_tiles(p);
   const int nkb = g.num_k_blocks;
   const uint32_t t0 = tmem_base + ((q * 32u) << 16) + Cfg::SF_BASE;
@@ -536,6 +545,31 @@ __device__ __forceinline__ void gemm_scale_writer(const P& p, const GemmShape& g
     int m_blk, n_blk;
     Policy::tile_coord(p, tile, &m_blk, &n_blk);
     // this CTA's 128 rows of the tile; all BN columns of B
+    // A tile whose A rows come from another rank: its scale words arrive with the rows.  The
+    // producer waits for them before its first load of the tile and then counts the tile in
+    // `a_ready_tiles`; this warp follows that count.
+    {
+      int ok = 1;
+      if (lane == 0) {
+        uint64_t t_start = 0;
+        for (uint32_t it = 0; *reinterpret_cast<volatile int*>(&ctl->a_ready_tiles) <= tcount; ++it) {
+          if ((it & 63u) == 63u) {
+            if (*reinterpret_cast<volatile int*>(&ctl->abort_flag) != 0) { ok = 0; break; }
+            const uint64_t now = globaltimer_ns();
+            if (t_start == 0) t_start = now;
+            if (now - t_start > CB_MBAR_TIMEOUT_NS) {
+              ctl->abort_flag = 1;
+              report_status(status, CB_TIMEOUT_MBARRIER, 0, 0x580);
+              ok = 0;
+              break;
+            }
+          }
+        }
+        __threadfence_block();
+      }
+      if (__shfl_sync(0xffffffffu, ok, 0) == 0) return;
+      ++tcount;
+    }
     long long pitch_a = 0;
     const uint32_t* pa = tile_a_sf<Policy>(p, g, m_blk, &pitch_a) + sub * Cfg::CTA_M;
     const int a_rows_left = g.M - m_blk * Cfg::BM - sub * Cfg::CTA_M;
@@ -545,7 +579,8 @@ __device__ __forceinline__ void gemm_scale_writer(const P& p, const GemmShape& g
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const int r = c * 32 + static_cast<int>(lane);
-        wa[c] = (kb < nkb && r < a_rows_left) ? __ldg(pa + (kb >> 2) * pitch_a + r) : kOne;
+        // L2-coherent load: the words of gathered rows were written by a peer during this launch
+        wa[c] = (kb < nkb && r < a_rows_left) ? __ldcg(pa + (kb >> 2) * pitch_a + r) : kOne;
       }
 #pragma unroll
       for (int c = 0; c < NB; ++c) {
@@ -1210,6 +1245,7 @@ __device__ __forceinline__ uint32_t gemm_setup(GemmCtl<Cfg::STAGES>* ctl, uint32
       mbar_init(&ctl->sig_empty[i], 1);
     }
     ctl->abort_flag = 0;
+    ctl->a_ready_tiles = 0;
     fence_mbar_init();
   }
   if (warp == 1) {

@@ -39,6 +39,7 @@ class _AgDesc(C.Structure):
         ("a_full_peer", _P8 * 2), ("a_full_mc", C.c_void_p * 2),
         ("flags_peer", _P8), ("flags_mc", C.c_void_p),
         ("seq", C.c_void_p), ("status", C.c_void_p), ("timeout_ns", C.c_ulonglong),
+        ("a_sf_local", C.c_void_p), ("a_sf_full_peer", _P8 * 2), ("b_sf", C.c_void_p),
     ]
 
 
@@ -49,6 +50,7 @@ class _RsDesc(C.Structure):
         ("a", C.c_void_p), ("b", C.c_void_p), ("out", C.c_void_p),
         ("stage_peer", _P8 * 2), ("flags_peer", _P8),
         ("seq", C.c_void_p), ("status", C.c_void_p), ("timeout_ns", C.c_ulonglong),
+        ("a_sf", C.c_void_p), ("b_sf", C.c_void_p),
     ]
 
 
@@ -152,9 +154,15 @@ class AgGemm(_FusedBase):
         nbytes = max_m * k * _esz(dtype)
         self.a_full = [_Sym(ctx, nbytes), _Sym(ctx, nbytes)]
         self.flags = _Sym(ctx, 2 * 1024 * 4, zero=True)
+        # fp8 with hardware block scales: the gathered rows' packed scale words, per parity
+        self.sf_full = None
+        if dtype == torch.float8_e4m3fn and k % 128 == 0:
+            sf_bytes = ((k // 128 + 3) // 4) * max_m * 4
+            self.sf_full = [_Sym(ctx, sf_bytes), _Sym(ctx, sf_bytes)]
         self._sync_init()
 
-    def _desc(self, r, a_local, b, c, M, Nn, K, alpha, bn, comm_ctas, parts, use_mc=True) -> _AgDesc:
+    def _desc(self, r, a_local, b, c, M, Nn, K, alpha, bn, comm_ctas, parts, use_mc=True,
+              a_sf=None, b_sf=None) -> _AgDesc:
         d = _AgDesc()
         d.rank, d.world, d.M, d.N, d.K = r, self.world, M, Nn, K
         d.fp8 = int(self.dtype == torch.float8_e4m3fn)
@@ -169,12 +177,20 @@ class AgGemm(_FusedBase):
         d.seq = self.seq[r if self.emu else 0].data_ptr()
         d.status = self._status_ptr(r)
         d.timeout_ns = self.ctx.timeout_ns
+        if a_sf is not None:
+            d.a_sf_local, d.b_sf = a_sf.data_ptr(), b_sf.data_ptr()
+            for par in range(2):
+                _fill_p8(d.a_sf_full_peer[par], self.sf_full[par].ptrs)
         return d
 
     @traced("cb200.ag_gemm")
     def __call__(self, a_local, b, out=None, alpha: float = 1.0, bn: int | None = None,
                  comm_ctas: int | None = None, parts: int | None = None, use_mc: bool = True,
-                 stream=None):
+                 stream=None, a_sf=None, b_sf=None):
+        """``a_sf`` / ``b_sf``: packed power-of-two block scales of fp8 operands
+        (``ops.gemm.quantize_blockscaled_pow2``; ``a_sf`` of the LOCAL rows): the tensor cores
+        apply them (``bn`` is then 192, CTA pairs on 256 x 192 tiles) and the scale words of a
+        row block travel to the peers with its rows."""
         cfg = get_config()
         if comm_ctas is None:
             comm_ctas = cfg.ag_gemm_comm_ctas if self.world > 1 else 0
@@ -192,13 +208,20 @@ class AgGemm(_FusedBase):
         M = Ml * self.world
         if M > self.max_m or K != self.k:
             raise CommError(f"AgGemm built for M<={self.max_m}, K={self.k}; got M={M}, K={K}")
-        if bn is None:
+        if a_sf is not None:
+            if self.sf_full is None or b_sf is None or M % (self.world * 256):
+                raise CommError("block-scaled AgGemm: build it with dtype float8_e4m3fn, pass both "
+                                "scale tensors, and shard whole 256-row blocks")
+            bn = 192
+        elif bn is None:
             bn = self._pick_bn(M, Nn)
         if self.emu:
             outs = out or [torch.empty((M, Nn), dtype=torch.bfloat16, device=a0.device)
                            for _ in range(self.world)]
             descs = (_AgDesc * self.world)(*[
-                self._desc(r, a_local[r], b[r], outs[r], M, Nn, K, alpha, bn, comm_ctas, parts)
+                self._desc(r, a_local[r], b[r], outs[r], M, Nn, K, alpha, bn, comm_ctas, parts,
+                           True, a_sf[r] if a_sf is not None else None,
+                           b_sf[r] if b_sf is not None else None)
                 for r in range(self.world)])
             table = self._emu_table(self.lib.cb_sizeof_ag_gemm_params() * self.world)
             rc = self.lib.cb_ag_gemm(descs, self.world, table, N.stream_ptr(stream))
@@ -207,7 +230,7 @@ class AgGemm(_FusedBase):
             if out is None:
                 out = torch.empty((M, Nn), dtype=torch.bfloat16, device=a0.device)
             descs = (_AgDesc * 1)(self._desc(self.ctx.rank, a_local, b, out, M, Nn, K, alpha, bn,
-                                             comm_ctas, parts, use_mc))
+                                             comm_ctas, parts, use_mc, a_sf, b_sf))
             rc = self.lib.cb_ag_gemm(descs, 1, None, N.stream_ptr(stream))
             result = out
         if rc != 0:
@@ -227,7 +250,7 @@ class GemmRs(_FusedBase):
         self.flags = _Sym(ctx, 2 * 8192 * 4, zero=True)
         self._sync_init()
 
-    def _desc(self, r, a, b, out, M, Nn, K, alpha, bn, fp8) -> _RsDesc:
+    def _desc(self, r, a, b, out, M, Nn, K, alpha, bn, fp8, a_sf=None, b_sf=None) -> _RsDesc:
         d = _RsDesc()
         d.rank, d.world, d.M, d.N, d.K = r, self.world, M, Nn, K
         d.fp8, d.alpha, d.bn, d.ctas_per_rank = int(fp8), alpha, bn, self._ctas()
@@ -238,16 +261,26 @@ class GemmRs(_FusedBase):
         d.seq = self.seq[r if self.emu else 0].data_ptr()
         d.status = self._status_ptr(r)
         d.timeout_ns = self.ctx.timeout_ns
+        if a_sf is not None:
+            d.a_sf, d.b_sf = a_sf.data_ptr(), b_sf.data_ptr()
         return d
 
     @traced("cb200.gemm_rs")
-    def __call__(self, a, b, out=None, alpha: float = 1.0, bn: int | None = None, stream=None):
+    def __call__(self, a, b, out=None, alpha: float = 1.0, bn: int | None = None, stream=None,
+                 a_sf=None, b_sf=None):
+        """``a_sf`` / ``b_sf``: packed power-of-two block scales of fp8 operands
+        (``ops.gemm.quantize_blockscaled_pow2``), applied by the tensor cores."""
         a0, b0 = (a[0], b[0]) if self.emu else (a, b)
         M, K = a0.shape
         Nn = b0.shape[0]
         if M > self.max_m or Nn > self.max_n:
             raise CommError(f"GemmRs built for M<={self.max_m}, N<={self.max_n}")
-        if bn is None:
+        if a_sf is not None:
+            if b_sf is None or M % (self.world * 256):
+                raise CommError("block-scaled GemmRs: pass both scale tensors and shard whole "
+                                "256-row blocks")
+            bn = 192
+        elif bn is None:
             bn = self._pick_bn(M, Nn)
         fp8 = a0.dtype == torch.float8_e4m3fn
         Ml = M // self.world
@@ -255,7 +288,9 @@ class GemmRs(_FusedBase):
             outs = out or [torch.empty((Ml, Nn), dtype=torch.bfloat16, device=a0.device)
                            for _ in range(self.world)]
             descs = (_RsDesc * self.world)(*[
-                self._desc(r, a[r], b[r], outs[r], M, Nn, K, alpha, bn, fp8)
+                self._desc(r, a[r], b[r], outs[r], M, Nn, K, alpha, bn, fp8,
+                           a_sf[r] if a_sf is not None else None,
+                           b_sf[r] if b_sf is not None else None)
                 for r in range(self.world)])
             table = self._emu_table(self.lib.cb_sizeof_gemm_rs_params() * self.world)
             rc = self.lib.cb_gemm_rs(descs, self.world, table, N.stream_ptr(stream))
@@ -263,7 +298,8 @@ class GemmRs(_FusedBase):
         else:
             if out is None:
                 out = torch.empty((Ml, Nn), dtype=torch.bfloat16, device=a0.device)
-            descs = (_RsDesc * 1)(self._desc(self.ctx.rank, a, b, out, M, Nn, K, alpha, bn, fp8))
+            descs = (_RsDesc * 1)(self._desc(self.ctx.rank, a, b, out, M, Nn, K, alpha, bn, fp8,
+                                             a_sf, b_sf))
             rc = self.lib.cb_gemm_rs(descs, 1, None, N.stream_ptr(stream))
             result = out
         if rc != 0:

@@ -2,13 +2,19 @@
 activations, 128x128 scales on the weights (the DeepSeek-V3 recipe the target configurations
 name).
 
-Operands are STORED as fp8 + fp32 scales (half the bytes in HBM and in checkpoints) and expanded
-to bf16 by a bandwidth-bound kernel right before the fused bf16 tcgen05 kernel; a static weight is
-expanded once and cached.  The activation expansion reads N bytes and writes 2N (for the
-8192 x 8192 activation of the target shape: 64 MB in, 128 MB out, ~30 us at HBM speed, against
-~400 us for the fused GEMM).  A mainloop that feeds fp8 tiles and applies the scales per K block
-inside the kernel is the next step; the per-tensor-scale fp8 mainloop (``kind::f8f6f4``) already
-exists and is reachable through the same ops by passing fp8 tensors directly.
+Two forms:
+
+* **power-of-two scales, applied by the tensor cores** (:func:`quantize_act_mx`,
+  :class:`MxWeight`, :func:`fused_mx`): the quantised tensors are the MMA operands
+  (``tcgen05.mma.kind::mxf8f6f4.block_scale``), the 8-bit scale exponents ride in tensor memory,
+  and in the all-gather -> GEMM kernel the scale words of a row block travel to the peers with
+  its rows.  Nothing is expanded; this is the path to use.
+* **arbitrary fp32 scales through bf16** (:class:`BlockScaledWeight`, :func:`fused_blockscaled`):
+  operands are expanded to bf16 by a bandwidth-bound kernel right before the bf16 kernel (a
+  static weight once, cached).  Kept for scales that are not powers of two and as a cross-check.
+
+Tensors with one scale per tensor need neither: pass fp8 tensors to ``AgGemm`` / ``GemmRs`` /
+``GemmAr`` and fold the scales into ``alpha``.
 
 The reference's fp8 fused examples use per-tensor fp8 only
 (datasets/example052_thunderkitten_ag_gemm_fp8_easy, example055_thunderkitten_gemm_rs_fp8_easy).
@@ -17,7 +23,8 @@ from __future__ import annotations
 
 import torch
 
-from .gemm import dequantize_blockscaled, quantize_blockscaled  # noqa: F401
+from .gemm import (dequantize_blockscaled, quantize_blockscaled,  # noqa: F401
+                   quantize_blockscaled_pow2)
 
 
 class BlockScaledWeight:
@@ -54,3 +61,32 @@ def fused_blockscaled(op, a_q, a_s, weight, **kw):
     a = _expand_act(a_q, a_s)
     b = [w.bf16() for w in weight] if isinstance(weight, (list, tuple)) else weight.bf16()
     return op(a, b, **kw)
+
+
+# ------------------------------------------------------------- hardware-applied block scales
+def quantize_act_mx(x: torch.Tensor):
+    """bf16 activation [rows, K] -> (e4m3, packed 1x128 power-of-two scale words)."""
+    q, _, sf = quantize_blockscaled_pow2(x, 1)
+    return q, sf
+
+
+class MxWeight:
+    """An fp8 weight [N, K] with power-of-two 128x128 block scales in the packed form the
+    block-scaled kernels read (one exponent byte per output column and K block)."""
+
+    def __init__(self, q: torch.Tensor, sf: torch.Tensor):
+        self.q, self.sf = q, sf
+
+    @classmethod
+    def from_bf16(cls, w: torch.Tensor) -> "MxWeight":
+        q, _, sf = quantize_blockscaled_pow2(w, 128)
+        return cls(q, sf)
+
+
+def fused_mx(op, a_q, a_sf, weight, **kw):
+    """Runs ``AgGemm`` or ``GemmRs`` on fp8 operands whose block scales the tensor cores apply.
+    ``a_q`` / ``a_sf`` from :func:`quantize_act_mx`, ``weight`` an :class:`MxWeight` (lists with
+    one entry per virtual rank under rank emulation)."""
+    if isinstance(weight, (list, tuple)):
+        return op(a_q, [w.q for w in weight], a_sf=a_sf, b_sf=[w.sf for w in weight], **kw)
+    return op(a_q, weight.q, a_sf=a_sf, b_sf=weight.sf, **kw)

@@ -9,6 +9,7 @@
 #include <string>
 
 #include "../prim/barrier.cuh"
+#include "../prim/pdl.cuh"
 
 namespace cb {
 void set_last_error(const std::string& s);
@@ -36,6 +37,8 @@ struct MoeSendArgs {
 // row; the CTA then releases once and bumps the expert's arrival counter.
 __global__ void __launch_bounds__(256)
     moe_dispatch_send_kernel(const __grid_constant__ MoeSendArgs a) {
+  pdl_wait();                // chained with programmatic dependent launch: see prim/pdl.cuh
+  pdl_launch_dependents();
   const int e = blockIdx.x;
   const int El = a.E / a.world;
   const int dst = e / El;
@@ -119,6 +122,8 @@ struct MoeRecvArgs {
 // zeroed and marked with source rank -1 so later stages skip them.
 __global__ void __launch_bounds__(256)
     moe_recv_dequant_kernel(const __grid_constant__ MoeRecvArgs a) {
+  pdl_wait();                // chained with programmatic dependent launch: see prim/pdl.cuh
+  pdl_launch_dependents();
   const int j = blockIdx.x;
   const int expect = a.recv_expected[j];
   const int base = a.recv_base[j];
@@ -187,14 +192,21 @@ __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat1
   }
 }
 
-// y[t, :] = sum_k w[t,k] * buf[t, k, :]   after every expert rank has reported in.
+// y[t, :] = sum_k w[t,k] * buf[t, k, :] (+ bias0[t, :] + bias1[t, :])   after every expert rank
+// has reported in.  The two optional bias inputs [T, H] bf16 are those of the reference's
+// reduction epilogue (datasets/example083_deepep_jit_combine_reduce_epilogue/nv/
+// empty_deepep_jit_combine_reduce_epilogue.cu:28): a shared-expert output or a residual can be
+// added here instead of in another pass over y.
 // `done` = W words on this rank (one per expert rank); cleared by the last CTA.
 __global__ void __launch_bounds__(256)
     moe_combine_reduce_kernel(const __nv_bfloat16* __restrict__ buf, const float* __restrict__ w,
                               const int* __restrict__ topk_idx, __nv_bfloat16* __restrict__ y,
                               int T, int K, int H, uint32_t* done, int world,
                               unsigned long long timeout_ns, uint32_t* status,
-                              uint32_t* done_ctas) {
+                              uint32_t* done_ctas, const __nv_bfloat16* __restrict__ bias0,
+                              const __nv_bfloat16* __restrict__ bias1) {
+  pdl_wait();                // chained with programmatic dependent launch: see prim/pdl.cuh
+  pdl_launch_dependents();
   bool ok = true;
   if (threadIdx.x < static_cast<unsigned>(world))
     ok = wait_flag_ge_sys(done + threadIdx.x, 1u, timeout_ns, status, PH_MOE_COMBINE2,
@@ -208,6 +220,18 @@ __global__ void __launch_bounds__(256)
       float acc[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int b = 0; b < 2; ++b) {
+        const __nv_bfloat16* bias = b == 0 ? bias0 : bias1;
+        if (bias == nullptr) continue;
+        const uint4 raw = *(reinterpret_cast<const uint4*>(bias + t * H) + v);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h[i]);
+          acc[2 * i] += f.x;
+          acc[2 * i + 1] += f.y;
+        }
+      }
       for (int k = 0; k < K; ++k) {
         if (topk_idx[t * K + k] < 0) continue;
         const float wk = w[t * K + k];
@@ -252,14 +276,18 @@ int cb_moe_dispatch_send(const MoeSendArgs* a, int slices, void* stream) {
     return -1;
   }
   dim3 grid(a->E, slices < 1 ? 1 : slices);
-  moe_dispatch_send_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(*a);
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  return launch_pdl(moe_dispatch_send_kernel, grid, dim3(256), 0,
+                    static_cast<cudaStream_t>(stream), *a) == cudaSuccess
+             ? 0
+             : -1;
 }
 
 int cb_moe_recv_dequant(const MoeRecvArgs* a, int n_local_experts, int slices, void* stream) {
   dim3 grid(n_local_experts, slices < 1 ? 1 : slices);
-  moe_recv_dequant_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(*a);
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  return launch_pdl(moe_recv_dequant_kernel, grid, dim3(256), 0,
+                    static_cast<cudaStream_t>(stream), *a) == cudaSuccess
+             ? 0
+             : -1;
 }
 
 int cb_moe_swiglu(const void* in, void* out, const void* n_rows_dev, int I, void* stream) {
@@ -270,16 +298,28 @@ int cb_moe_swiglu(const void* in, void* out, const void* n_rows_dev, int I, void
   return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
+// bias0 / bias1: optional [T, H] bf16 tensors added to the weighted sum (may be null).
+int cb_moe_combine_reduce_bias(const void* buf, const void* w, const void* topk_idx, void* y,
+                               int T, int K, int H, void* done, int world,
+                               unsigned long long timeout_ns, void* status, void* done_ctas,
+                               const void* bias0, const void* bias1, void* stream) {
+  if (H % 8 != 0) return -1;
+  return launch_pdl(moe_combine_reduce_kernel, dim3(592), dim3(256), 0,
+                    static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(buf),
+                    static_cast<const float*>(w), static_cast<const int*>(topk_idx),
+                    static_cast<__nv_bfloat16*>(y), T, K, H, static_cast<uint32_t*>(done), world,
+                    timeout_ns, static_cast<uint32_t*>(status), static_cast<uint32_t*>(done_ctas),
+                    static_cast<const __nv_bfloat16*>(bias0),
+                    static_cast<const __nv_bfloat16*>(bias1)) == cudaSuccess
+             ? 0
+             : -1;
+}
+
 int cb_moe_combine_reduce(const void* buf, const void* w, const void* topk_idx, void* y, int T,
                           int K, int H, void* done, int world, unsigned long long timeout_ns,
                           void* status, void* done_ctas, void* stream) {
-  if (H % 8 != 0) return -1;
-  moe_combine_reduce_kernel<<<592, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(buf), static_cast<const float*>(w),
-      static_cast<const int*>(topk_idx), static_cast<__nv_bfloat16*>(y), T, K, H,
-      static_cast<uint32_t*>(done), world, timeout_ns, static_cast<uint32_t*>(status),
-      static_cast<uint32_t*>(done_ctas));
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  return cb_moe_combine_reduce_bias(buf, w, topk_idx, y, T, K, H, done, world, timeout_ns, status,
+                                    done_ctas, nullptr, nullptr, stream);
 }
 
 }  // extern "C"

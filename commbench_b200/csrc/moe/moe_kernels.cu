@@ -30,6 +30,7 @@
 #include <string>
 
 #include "../prim/barrier.cuh"
+#include "../prim/pdl.cuh"
 
 namespace cb {
 void set_last_error(const std::string& s);
@@ -129,6 +130,8 @@ constexpr int kSlotWarps = 16;
 __global__ void __launch_bounds__(kSlotWarps * 32)
     moe_slot_kernel(const int* __restrict__ topk_idx, int n_pairs, int E, int* __restrict__ slot,
                     int* __restrict__ counts) {
+  pdl_wait();                // chained with programmatic dependent launch: see prim/pdl.cuh
+  pdl_launch_dependents();
   __shared__ int chunk_hits[kSlotWarps];
   const int e = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -178,6 +181,8 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts_all, int W, int E
                                 int* send_row_base, int* src_pair_base, int* recv_expected,
                                 int* recv_base, int* mblk_expert, int* n_mblocks,
                                 int max_recv_rows, uint32_t* status) {
+  pdl_wait();                // chained with programmatic dependent launch: see prim/pdl.cuh
+  pdl_launch_dependents();
   const int El = E / W;
   __shared__ int rows_sh[1024];   // rows(d,j) for every global expert
   __shared__ int base_sh[1024];   // base(d,j)
@@ -230,6 +235,8 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts_all, int W, int E
 __global__ void moe_sort_pairs_kernel(const int* __restrict__ topk_idx, const int* __restrict__ slot,
                                       const int* __restrict__ src_pair_base, int n_pairs, int E,
                                       int* __restrict__ sorted_pair) {
+  pdl_wait();                // chained with programmatic dependent launch: see prim/pdl.cuh
+  pdl_launch_dependents();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_pairs) return;
   const int e = topk_idx[i];
@@ -271,10 +278,11 @@ int cb_moe_dispatch_layout(const void* topk_idx, int T, int K, int R, int E, voi
 }
 
 int cb_moe_slots(const void* topk_idx, int n_pairs, int E, void* slot, void* counts, void* stream) {
-  moe_slot_kernel<<<E, kSlotWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const int*>(topk_idx), n_pairs, E, static_cast<int*>(slot),
-      static_cast<int*>(counts));
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  return launch_pdl(moe_slot_kernel, dim3(E), dim3(kSlotWarps * 32), 0,
+                    static_cast<cudaStream_t>(stream), static_cast<const int*>(topk_idx), n_pairs,
+                    E, static_cast<int*>(slot), static_cast<int*>(counts)) == cudaSuccess
+             ? 0
+             : -1;
 }
 
 int cb_moe_plan(const void* counts_all, int W, int E, int rank, void* send_row_base,
@@ -284,20 +292,24 @@ int cb_moe_plan(const void* counts_all, int W, int E, int rank, void* send_row_b
     set_last_error("plan: E <= 1024 and divisible by the world size required");
     return -1;
   }
-  moe_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const int*>(counts_all), W, E, rank, static_cast<int*>(send_row_base),
-      static_cast<int*>(src_pair_base), static_cast<int*>(recv_expected),
-      static_cast<int*>(recv_base), static_cast<int*>(mblk_expert), static_cast<int*>(n_mblocks),
-      max_recv_rows, static_cast<uint32_t*>(status));
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  return launch_pdl(moe_plan_kernel, dim3(1), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                    static_cast<const int*>(counts_all), W, E, rank,
+                    static_cast<int*>(send_row_base), static_cast<int*>(src_pair_base),
+                    static_cast<int*>(recv_expected), static_cast<int*>(recv_base),
+                    static_cast<int*>(mblk_expert), static_cast<int*>(n_mblocks), max_recv_rows,
+                    static_cast<uint32_t*>(status)) == cudaSuccess
+             ? 0
+             : -1;
 }
 
 int cb_moe_sort_pairs(const void* topk_idx, const void* slot, const void* src_pair_base,
                       int n_pairs, int E, void* sorted_pair, void* stream) {
-  moe_sort_pairs_kernel<<<(n_pairs + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const int*>(topk_idx), static_cast<const int*>(slot),
-      static_cast<const int*>(src_pair_base), n_pairs, E, static_cast<int*>(sorted_pair));
-  return cudaGetLastError() == cudaSuccess ? 0 : -1;
+  return launch_pdl(moe_sort_pairs_kernel, dim3((n_pairs + 255) / 256), dim3(256), 0,
+                    static_cast<cudaStream_t>(stream), static_cast<const int*>(topk_idx),
+                    static_cast<const int*>(slot), static_cast<const int*>(src_pair_base), n_pairs,
+                    E, static_cast<int*>(sorted_pair)) == cudaSuccess
+             ? 0
+             : -1;
 }
 
 }  // extern "C"

@@ -298,6 +298,98 @@ def main(argv=None) -> int:
         record("gemm_rs", "bf16", (M, K, N // world), "bf16", correct=all_ok(err < 2e-2), max_err=err,
                time_ms=ms, baseline_ms=bms, tflops=fl / (ms * 1e-3) / 1e12,
                roofline_frac=roofline.fraction(roofline.roofline_ms(fl, link, peaks, True), ms))
+        # ---- the same two shapes on fp8 e4m3: one scale per tensor, and 1x128 / 128x128
+        # power-of-two block scales applied by the tensor cores.  Baseline: NCCL collective on the
+        # fp8 bytes + torch._scaled_mm.  The fp8 roofline takes twice the measured bf16 rate.
+        from ..ops.gemm import gemm_fp8_mx, quantize_blockscaled_pow2
+
+        f8 = torch.float8_e4m3fn
+        one = torch.ones(1, device=dev)
+
+        def smm(x, w):
+            return torch._scaled_mm(x, w.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+
+        def bs_ref_rows(q, sfw, rows):
+            """fp32 rows `rows` of a block-scaled operand (packed exponent words -> scales)."""
+            from ..ops.gemm import sf_exponents
+            e = sf_exponents(sfw, q.shape[1] // 128)[rows].float()
+            return q[rows].float() * torch.exp2(e - 127.0).repeat_interleave(128, dim=1)
+
+        aq, _, asf = quantize_blockscaled_pow2(a_loc, 1)
+        b1q, _, b1sf = quantize_blockscaled_pow2(b1, 128)
+        a2q, _, a2sf = quantize_blockscaled_pow2(a2, 1)
+        b2q, _, b2sf = quantize_blockscaled_pow2(b2, 128)
+        sample = torch.arange(0, M // world, max(1, M // world // 64), device=dev)
+        if world > 1:
+            ag8 = AgGemm(ctx, M, K, dtype=f8)
+
+            def base_ag8():
+                full = torch.empty(M, K, dtype=torch.uint8, device=dev)
+                dist.all_gather_into_tensor(full, aq.view(torch.uint8))
+                return smm(full.view(f8), b1q)
+
+            def base_rs8():
+                part = smm(a2q, b2q)
+                y = torch.empty(M // world, K, dtype=torch.bfloat16, device=dev)
+                dist.reduce_scatter_tensor(y, part)
+                return y
+            cases = (
+                ("ag_gemm", "fp8-per-tensor", lambda: ag8(aq, b1q), base_ag8, (M, N // world, K),
+                 "all_gather", M * K),
+                ("ag_gemm", "fp8-blockscaled", lambda: ag8(aq, b1q, a_sf=asf, b_sf=b1sf), base_ag8,
+                 (M, N // world, K), "all_gather", M * K),
+                ("gemm_rs", "fp8-per-tensor", lambda: rs(a2q, b2q), base_rs8, (M, K, N // world),
+                 "reduce_scatter", M * K * 2),
+                ("gemm_rs", "fp8-blockscaled", lambda: rs(a2q, b2q, a_sf=a2sf, b_sf=b2sf), base_rs8,
+                 (M, K, N // world), "reduce_scatter", M * K * 2),
+            )
+        else:
+            cases = (
+                ("ag_gemm", "fp8-per-tensor", lambda: gemm(aq, b1q), lambda: smm(aq, b1q),
+                 (M, N, K), "all_gather", 0),
+                ("ag_gemm", "fp8-blockscaled", lambda: gemm_fp8_mx(aq, asf, b1q, b1sf),
+                 lambda: smm(aq, b1q), (M, N, K), "all_gather", 0),
+                ("gemm_rs", "fp8-per-tensor", lambda: gemm(a2q, b2q), lambda: smm(a2q, b2q),
+                 (M, K, N), "reduce_scatter", 0),
+                ("gemm_rs", "fp8-blockscaled", lambda: gemm_fp8_mx(a2q, a2sf, b2q, b2sf),
+                 lambda: smm(a2q, b2q), (M, K, N), "reduce_scatter", 0),
+            )
+        for op_name, variant, ours, theirs, shape, coll_name, coll_bytes in cases:
+            c = ours()
+            ctx.check_status()
+            if variant == "fp8-per-tensor":
+                r = theirs()
+                err = ((c.float() - r.float()).abs().max() / (r.float().abs().max() + 1e-9)).item()
+            elif op_name == "ag_gemm" and world == 1:
+                # sampled rows against the fp32 product of the same quantised, scaled operands
+                r = bs_ref_rows(aq, asf, sample) @ bs_ref_rows(b1q, b1sf, slice(None)).t()
+                err = ((c[sample].float() - r).abs().max() / (r.abs().max() + 1e-9)).item()
+            elif op_name == "gemm_rs" and world == 1:
+                r = bs_ref_rows(a2q, a2sf, sample) @ bs_ref_rows(b2q, b2sf, slice(None)).t()
+                err = ((c[sample].float() - r).abs().max() / (r.abs().max() + 1e-9)).item()
+            elif op_name == "ag_gemm":
+                # own rows of the gathered product (the other ranks' rows are covered by the
+                # per-tensor case and by the virtual-rank tests)
+                rows = sample + rank * (M // world)
+                r = bs_ref_rows(aq, asf, sample) @ bs_ref_rows(b1q, b1sf, slice(None)).t()
+                err = ((c[rows].float() - r).abs().max() / (r.abs().max() + 1e-9)).item()
+            else:
+                # reduce-scatter: sum over ranks of the sampled rows' partial products
+                rows = sample + rank * (M // world)
+                part = bs_ref_rows(a2q, a2sf, slice(None)) @ bs_ref_rows(b2q, b2sf, slice(None)).t()
+                ref_full = part.clone()
+                dist.all_reduce(ref_full)
+                r = ref_full[rows]
+                err = ((c[sample].float() - r).abs().max() / (r.abs().max() + 1e-9)).item()
+                del part, ref_full
+            ms, bms = timed(ours), timed(theirs)
+            fl = 2.0 * shape[0] * shape[1] * shape[2]
+            link = roofline.nvlink_bytes(coll_name, coll_bytes, world) if world > 1 else 0
+            record(op_name, variant, shape, "fp8", correct=all_ok(err < 2e-2), max_err=err,
+                   time_ms=ms, baseline_ms=bms, tflops=fl / (ms * 1e-3) / 1e12,
+                   roofline_frac=roofline.fraction(roofline.roofline_ms(fl / 2, link, peaks, True), ms),
+                   note="fp8 roofline = 2 x measured bf16 rate; baseline NCCL + torch._scaled_mm "
+                        "with unit scales")
         Kd, Nd = 8192 // world, 8192
         if world > 1:
             ar = GemmAr(ctx, 1024, Nd)

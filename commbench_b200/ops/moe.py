@@ -206,12 +206,19 @@ class MoELayer:
 
     # ------------------------------------------------------------------ forward
     @traced("cb200.moe.forward")
-    def forward(self, xs, topk_idx, topk_w):
+    def forward(self, xs, topk_idx, topk_w, bias0=None, bias1=None):
         """xs [T, H] bf16, topk_idx [T, K] int32, topk_w [T, K] fp32 (lists in emulation).
-        Returns y [T, H] bf16 (list in emulation)."""
+        ``bias0`` / ``bias1``: optional [T, H] bf16 tensors added in the combine reduction (a
+        shared expert's output, a residual).  Returns y [T, H] bf16 (list in emulation).
+
+        The small kernels of the layer (slots, plan, pair sort, dispatch, receive, combine
+        reduction) are chained with programmatic dependent launch: each may be scheduled while
+        its predecessor still runs and waits on the device for it."""
         lib, W, E, K, T, H, I = self.lib, self.W, self.E, self.K, self.T, self.H, self.I
         if not self.emu:
             xs, topk_idx, topk_w = [xs], [topk_idx], [topk_w]
+            bias0 = [bias0] if bias0 is not None else None
+            bias1 = [bias1] if bias1 is not None else None
         sp = N.stream_ptr()
         n_pairs = T * K
         self._mark("begin")
@@ -300,11 +307,13 @@ class MoELayer:
             N.check(lib.cb_moe_grouped_gemm(C.byref(d2), sp), "grouped gemm (down)")
             self._mark("gemm_down+scatter")
         # 7. weighted reduction at the token owners
-        for st, idx, w in zip(self.states, topk_idx, topk_w):
-            N.check(lib.cb_moe_combine_reduce(
+        for i, (st, idx, w) in enumerate(zip(self.states, topk_idx, topk_w)):
+            N.check(lib.cb_moe_combine_reduce_bias(
                 N.ptr(self._local(self.combine, st)), N.ptr(w), N.ptr(idx), N.ptr(st.y), T, K, H,
                 N.ptr(self._local(self.done, st)), W, C.c_ulonglong(self.ctx.timeout_ns),
-                C.c_void_p(self._status(st)), C.c_void_p(st.done_ctas.data_ptr() + 8), sp),
+                C.c_void_p(self._status(st)), C.c_void_p(st.done_ctas.data_ptr() + 8),
+                N.ptr(bias0[i] if bias0 is not None else None),
+                N.ptr(bias1[i] if bias1 is not None else None), sp),
                 "combine_reduce")
         self._mark("combine_reduce")
         ys = [st.y for st in self.states]

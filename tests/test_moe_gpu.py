@@ -70,6 +70,15 @@ def test_moe_layer_virtual_ranks(native_lib, world, fused_swiglu):
             err = (ys[r].float() - ref).abs().max().item()
             scale = ref.abs().max().item() + 1e-6
             assert err / scale < 3e-2, (it, r, err, scale)
+    # the two optional bias inputs of the combine reduction (shared expert / residual)
+    b0 = [torch.randn(T, H, device="cuda").bfloat16() for _ in range(world)]
+    b1 = [torch.randn(T, H, device="cuda").bfloat16() for _ in range(world)]
+    ys = layer.forward(xs, idxs, ws, bias0=b0, bias1=b1)
+    ctx.check_status()
+    for r in range(world):
+        ref = reference_moe(xs[r], idxs[r], ws[r], w1_all, w2_all, I) + b0[r].float() + b1[r].float()
+        err = (ys[r].float() - ref).abs().max().item()
+        assert err / (ref.abs().max().item() + 1e-6) < 3e-2, (r, err)
 
 
 @pytest.mark.parametrize("n,E", [(100, 4), (4096 * 8, 256), (777, 33)])

@@ -183,6 +183,32 @@ class AgGemm(_FusedBase):
                 _fill_p8(d.a_sf_full_peer[par], self.sf_full[par].ptrs)
         return d
 
+    @staticmethod
+    def pick_comm_ctas(M: int, Nn: int, bn: int, ctas: int, at_least: int) -> int:
+        """Communication CTAs for a launch of ``ctas`` CTAs: the LARGEST even count between
+        ``at_least`` and 24 that does not add a wave of tiles to the compute CTAs.  (8192 x 3584
+        in 256 x 256 pair tiles = 448 tiles: 70 pairs and 64 pairs both need 7 waves, so 20 CTAs
+        can push rows instead of 8 at no cost; 8192 x 14336 = 1792 tiles: 72 pairs need 25
+        waves, 70 need 26, so only 4 are taken.)"""
+        pair = 2 if bn in (512, 192) else 1
+        tile_m = 128 * pair
+        tile_n = {512: 256, 192: 192}.get(bn, bn)
+        tiles = ((M + tile_m - 1) // tile_m) * ((Nn + tile_n - 1) // tile_n)
+
+        def waves(c):
+            workers = (ctas - c) // pair
+            return -(-tiles // workers) if workers > 0 else 1 << 30
+        best, best_w = None, None
+        for c in range(2, 26, 2):
+            w = waves(c)
+            if best is None or w < best_w or (w == best_w and c >= best):
+                if w < (best_w or 1 << 30) or c <= 24:
+                    best, best_w = c, w
+        # never below the floor unless that saves a whole wave
+        if best < at_least and waves(at_least) == best_w:
+            best = at_least
+        return best
+
     @traced("cb200.ag_gemm")
     def __call__(self, a_local, b, out=None, alpha: float = 1.0, bn: int | None = None,
                  comm_ctas: int | None = None, parts: int | None = None, use_mc: bool = True,
@@ -192,12 +218,13 @@ class AgGemm(_FusedBase):
         apply them (``bn`` is then 192, CTA pairs on 256 x 192 tiles) and the scale words of a
         row block travel to the peers with its rows."""
         cfg = get_config()
+        auto_comm = comm_ctas is None
         if comm_ctas is None:
             comm_ctas = cfg.ag_gemm_comm_ctas if self.world > 1 else 0
         if self.emu:
             comm_ctas = min(comm_ctas, 4) if self.world > 1 else 0
         comm_ctas += comm_ctas % 2
-        if parts is None:
+        if parts is None and not (auto_comm and not self.emu and self.world > 1):
             parts = max(comm_ctas, 1)   # every comm CTA works on the same row block
         if self.emu:
             a0, b0 = a_local[0], b[0]
@@ -215,6 +242,10 @@ class AgGemm(_FusedBase):
             bn = 192
         elif bn is None:
             bn = self._pick_bn(M, Nn)
+        if auto_comm and not self.emu and self.world > 1:
+            comm_ctas = self.pick_comm_ctas(M, Nn, bn, self._ctas(), comm_ctas)
+            if parts is None or parts < 1:
+                parts = comm_ctas
         if self.emu:
             outs = out or [torch.empty((M, Nn), dtype=torch.bfloat16, device=a0.device)
                            for _ in range(self.world)]

@@ -231,7 +231,7 @@ def main() -> int:
             t, _ = ctx.empty((n,), torch.bfloat16)
             t.fill_(0.001)
             sync_all()
-            algo = coll.choose_all_reduce_algo(nbytes, world, ctx.has_multicast)
+            algo = coll.plan_all_reduce(ctx, nbytes, True)["algo"]
             ms = timed(lambda: coll.all_reduce(ctx, t), 10, 3) / 10
             u = torch.full((n,), 0.001, dtype=torch.bfloat16, device=dev)
             nccl_ms = timed(lambda: dist.all_reduce(u), 10, 3) / 10

@@ -55,6 +55,8 @@ class CollArgs(C.Structure):
         ("a2a_h", C.c_int),
         ("a2a_d", C.c_int),
         ("a2a_to_heads", C.c_int),
+        ("unroll", C.c_int),
+        ("variant", C.c_int),
     ]
 
 

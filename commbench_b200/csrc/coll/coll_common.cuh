@@ -28,6 +28,13 @@ struct CollArgs {
   int dtype;
   // 4-D all-to-all geometry (elements): [B, S_local, H, D] <-> [B, S, H_local, D]
   int a2a_b, a2a_s_local, a2a_h, a2a_d, a2a_to_heads;
+  // Tuning: 16-byte vectors each thread keeps in flight in the bandwidth loops (0: the
+  // kernel's default of 4; values are rounded down to 2, 4 or 8).
+  int unroll;
+  // Bit 0 picks the push form where an op has one: two-shot all-reduce stores each reduced
+  // vector to every rank instead of letting the ranks pull it in a second phase; flat
+  // all-to-all stores chunk p of `in` into rank p's sym[] instead of pulling.
+  int variant;
 };
 
 // Several ranks can be emulated inside ONE launch on one GPU: the grid gets

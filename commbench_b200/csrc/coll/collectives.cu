@@ -54,6 +54,37 @@ __device__ __forceinline__ void copy_vec_slice(void* dst, const void* src, unsig
   for (; i < v1; i += blockDim.x) d[i] = s[i];
 }
 
+// Bandwidth loop over vectors [begin, end) of one CTA: every thread issues U independent
+// loads and only then the U stores, so U 16-byte requests per thread are in flight.  The
+// latency of a peer or multicast load is a few microseconds, so bytes in flight decide the
+// rate.  `load(i)` returns vector i, `store(i, v)` writes it.
+template <int U, class L, class S>
+__device__ __forceinline__ void span_copy_fixed(unsigned long long begin, unsigned long long end,
+                                                L load, S store) {
+  const unsigned long long st = blockDim.x;
+  unsigned long long i = begin + threadIdx.x;
+  for (; i + static_cast<unsigned long long>(U - 1) * st < end;
+       i += static_cast<unsigned long long>(U) * st) {
+    uint4 r[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) r[u] = load(i + static_cast<unsigned long long>(u) * st);
+#pragma unroll
+    for (int u = 0; u < U; ++u) store(i + static_cast<unsigned long long>(u) * st, r[u]);
+  }
+  for (; i < end; i += st) store(i, load(i));
+}
+// `unroll` is uniform over the grid (it comes from the argument block).
+template <class L, class S>
+__device__ __forceinline__ void span_copy(int unroll, unsigned long long begin,
+                                          unsigned long long end, L load, S store) {
+  if (unroll >= 8)
+    span_copy_fixed<8>(begin, end, load, store);
+  else if (unroll >= 4 || unroll <= 0)
+    span_copy_fixed<4>(begin, end, load, store);
+  else
+    span_copy_fixed<2>(begin, end, load, store);
+}
+
 // Copies bytes [16*v0, min(16*v1, nbytes)) of an arbitrary local tensor into /
 // out of a 16-byte padded symmetric buffer; the ragged tail goes byte-wise.
 __device__ __forceinline__ void copy_bytes_slice(void* dst, const void* src,
@@ -110,6 +141,76 @@ __device__ __forceinline__ uint32_t begin_epoch(const CbComm& c, uint32_t ch) {
 __device__ __forceinline__ void end_epoch(const CbComm& c, uint32_t ch, uint32_t value) {
   __syncthreads();
   if (threadIdx.x == 0) c.epoch[ch] = value;
+}
+
+// Sum over the W ranks of vector (off + i) for i in [begin, end), pulled with system-scope
+// loads.  raw[r] comes from rank r and the sum runs in rank order 0..W-1, so every rank
+// rounds alike; the indices are compile-time constants, so the vectors stay in registers.
+// U vectors x W ranks are in flight per thread; `store(i, v)` takes the sum.
+template <int DT, int W>
+__device__ __forceinline__ uint4 sum_in_rank_order(const uint4 (&raw)[W]) {
+  float acc[Vec16<DT>::N];
+#pragma unroll
+  for (int r = 0; r < W; ++r) {
+    float f[Vec16<DT>::N];
+    Vec16<DT>::unpack(raw[r], f);
+#pragma unroll
+    for (int k = 0; k < Vec16<DT>::N; ++k) acc[k] = (r == 0) ? f[k] : acc[k] + f[k];
+  }
+  return Vec16<DT>::pack(acc);
+}
+template <int DT, int W, int U, class S>
+__device__ __forceinline__ void reduce_span_fixed(const CollArgs& a, unsigned long long off,
+                                                  unsigned long long begin,
+                                                  unsigned long long end, S store) {
+  const unsigned long long st = blockDim.x;
+  const uint4* base[W];
+#pragma unroll
+  for (int r = 0; r < W; ++r) base[r] = static_cast<const uint4*>(a.sym[r]) + off;
+  unsigned long long i = begin + threadIdx.x;
+  for (; i + static_cast<unsigned long long>(U - 1) * st < end;
+       i += static_cast<unsigned long long>(U) * st) {
+    uint4 raw[U][W];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int r = 0; r < W; ++r)
+        raw[u][r] = ld_sys_v4(base[r] + i + static_cast<unsigned long long>(u) * st);
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      store(i + static_cast<unsigned long long>(u) * st, sum_in_rank_order<DT, W>(raw[u]));
+  }
+  for (; i < end; i += st) {
+    uint4 raw[W];
+#pragma unroll
+    for (int r = 0; r < W; ++r) raw[r] = ld_sys_v4(base[r] + i);
+    store(i, sum_in_rank_order<DT, W>(raw));
+  }
+}
+// Runtime choice of U: at most 16 loads per thread (register budget of a 512-thread CTA),
+// eight by default.
+template <int DT, int W, class S>
+__device__ __forceinline__ void reduce_span(const CollArgs& a, unsigned long long off,
+                                            unsigned long long begin, unsigned long long end,
+                                            S store) {
+  constexpr int UMAX = (W >= 16) ? 1 : (16 / W > 8 ? 8 : 16 / W);
+  constexpr int UDEF = (W >= 8) ? 1 : 8 / W;
+  const int u = a.unroll <= 0 ? UDEF : a.unroll;
+  if constexpr (UMAX >= 4) {
+    if (u >= UMAX)
+      reduce_span_fixed<DT, W, UMAX>(a, off, begin, end, store);
+    else if (u >= UMAX / 2)
+      reduce_span_fixed<DT, W, UMAX / 2>(a, off, begin, end, store);
+    else
+      reduce_span_fixed<DT, W, UMAX / 4>(a, off, begin, end, store);
+  } else if constexpr (UMAX == 2) {
+    if (u >= 2)
+      reduce_span_fixed<DT, W, 2>(a, off, begin, end, store);
+    else
+      reduce_span_fixed<DT, W, 1>(a, off, begin, end, store);
+  } else {
+    reduce_span_fixed<DT, W, 1>(a, off, begin, end, store);
+  }
 }
 
 // ------------------------------------------------------------ one-shot pull AR
@@ -176,6 +277,7 @@ __global__ void __launch_bounds__(kCollThreads)
   const uint32_t e = begin_epoch(c, ch);
   const unsigned long long nvec = (a.nbytes + 15ull) / 16ull;
   const unsigned long long per_rank = (nvec + W - 1) / W;
+  const bool push = (a.variant & 1) != 0;
 
   if (a.copy_in)
     for_each_chunk_slice(nvec, per_rank, W, [&](unsigned long long v0, unsigned long long v1) {
@@ -189,27 +291,29 @@ __global__ void __launch_bounds__(kCollThreads)
     if (c1 > nvec) c1 = nvec;
     unsigned long long s0, s1;
     slice_of(c1 - c0, gridDim.x, blockIdx.x, &s0, &s1);
-    for (unsigned long long i = c0 + s0 + threadIdx.x; i < c0 + s1; i += blockDim.x) {
-      float acc[Vec16<DT>::N];
-      uint4 raw[W];
+    if (push) {
+      // Each sum goes to every rank at once: no second phase.  A vector is read and later
+      // overwritten by the same thread, and no other rank touches chunk `rank`.
+      reduce_span<DT, W>(a, 0, c0 + s0, c0 + s1, [&](unsigned long long i, uint4 v) {
 #pragma unroll
-      for (int p = 0; p < W; ++p) {
-        const int src = (c.rank + p) % W;
-        raw[p] = ld_sys_v4(static_cast<const uint4*>(a.sym[src]) + i);
-      }
-#pragma unroll
-      for (int r = 0; r < W; ++r) {
-        const int p = (r - c.rank + W) % W;
-        float f[Vec16<DT>::N];
-        Vec16<DT>::unpack(raw[p], f);
-#pragma unroll
-        for (int k = 0; k < Vec16<DT>::N; ++k) acc[k] = (r == 0) ? f[k] : acc[k] + f[k];
-      }
-      st_sys_v4(static_cast<uint4*>(a.sym[c.rank]) + i, Vec16<DT>::pack(acc));
+        for (int r = 0; r < W; ++r) st_sys_v4(static_cast<uint4*>(a.sym[r]) + i, v);
+      });
+    } else {
+      reduce_span<DT, W>(a, 0, c0 + s0, c0 + s1, [&](unsigned long long i, uint4 v) {
+        st_sys_v4(static_cast<uint4*>(a.sym[c.rank]) + i, v);
+      });
     }
-    ok = rank_barrier_block(c, ch, e + 2, PH_BARRIER_MID);
+    ok = rank_barrier_block(c, ch, e + 2, PH_BARRIER_MID);  // its release orders the stores
   }
-  if (ok) {
+  if (ok && push) {
+    // Slice b of every chunk was written here by block b of that chunk's owner.
+    if (a.copy_out)
+      for_each_chunk_slice(nvec, per_rank, W, [&](unsigned long long v0, unsigned long long v1) {
+        copy_bytes_slice(a.out, a.sym[c.rank], a.nbytes, v0, v1, false);
+      });
+    // Keeps the epoch arithmetic of the pull form: nobody waits on e + 3 later, the next
+    // call starts from the stored epoch.
+  } else if (ok) {
     // Phase 2: gather slice b of every rank's reduced chunk.
     unsigned char* outb = static_cast<unsigned char*>(a.copy_out ? a.out : a.sym[c.rank]);
     const unsigned long long full = a.nbytes / 16ull;
@@ -223,20 +327,13 @@ __global__ void __launch_bounds__(kCollThreads)
       unsigned long long s0, s1;
       slice_of(c1 - c0, gridDim.x, blockIdx.x, &s0, &s1);
       const uint4* sp = static_cast<const uint4*>(a.sym[src]);
-      unsigned long long i = c0 + s0 + threadIdx.x;
-      // Whole vectors, four loads in flight per thread.
-      for (; i + 3ull * blockDim.x < c0 + s1 && i + 3ull * blockDim.x < full;
-           i += 4ull * blockDim.x) {
-        const uint4 x0 = ld_sys_v4(sp + i), x1 = ld_sys_v4(sp + i + blockDim.x),
-                    x2 = ld_sys_v4(sp + i + 2ull * blockDim.x),
-                    x3 = ld_sys_v4(sp + i + 3ull * blockDim.x);
-        uint4* d = reinterpret_cast<uint4*>(outb);
-        d[i] = x0;
-        d[i + blockDim.x] = x1;
-        d[i + 2ull * blockDim.x] = x2;
-        d[i + 3ull * blockDim.x] = x3;
-      }
-      for (; i < c0 + s1; i += blockDim.x) {
+      // Whole vectors first; the vector that holds the ragged tail goes through the slow loop.
+      const unsigned long long vend = (c0 + s1 < full) ? c0 + s1 : (full > c0 + s0 ? full : c0 + s0);
+      uint4* d = reinterpret_cast<uint4*>(outb);
+      span_copy(
+          a.unroll, c0 + s0, vend, [&](unsigned long long i) { return ld_sys_v4(sp + i); },
+          [&](unsigned long long i, uint4 v) { d[i] = v; });
+      for (unsigned long long i = vend + threadIdx.x; i < c0 + s1; i += blockDim.x) {
         const uint4 v = ld_sys_v4(sp + i);
         if (i < full || !a.copy_out) {
           *reinterpret_cast<uint4*>(outb + i * 16ull) = v;
@@ -275,18 +372,10 @@ __global__ void __launch_bounds__(kCollThreads)
     unsigned long long s0, s1;
     slice_of(c1 - c0, gridDim.x, blockIdx.x, &s0, &s1);
     uint4* mc = static_cast<uint4*>(a.mc);
-    unsigned long long i = c0 + s0 + threadIdx.x;
-    for (; i + 3ull * blockDim.x < c0 + s1; i += 4ull * blockDim.x) {
-      uint4 r0 = Vec16<DT>::mm_reduce(mc + i);
-      uint4 r1 = Vec16<DT>::mm_reduce(mc + i + blockDim.x);
-      uint4 r2 = Vec16<DT>::mm_reduce(mc + i + 2ull * blockDim.x);
-      uint4 r3 = Vec16<DT>::mm_reduce(mc + i + 3ull * blockDim.x);
-      mm_st_v4(mc + i, r0);
-      mm_st_v4(mc + i + blockDim.x, r1);
-      mm_st_v4(mc + i + 2ull * blockDim.x, r2);
-      mm_st_v4(mc + i + 3ull * blockDim.x, r3);
-    }
-    for (; i < c0 + s1; i += blockDim.x) mm_st_v4(mc + i, Vec16<DT>::mm_reduce(mc + i));
+    span_copy(
+        a.unroll, c0 + s0, c0 + s1,
+        [&](unsigned long long i) { return Vec16<DT>::mm_reduce(mc + i); },
+        [&](unsigned long long i, uint4 v) { mm_st_v4(mc + i, v); });
     // multimem.st results must be visible on every rank before anyone reads them: the
     // barrier's CTA sync followed by its release stores orders them (a system fence by
     // every thread here costs tens of microseconds under store traffic).
@@ -326,18 +415,10 @@ __global__ void __launch_bounds__(kCollThreads)
       const uint4* sp = static_cast<const uint4*>(a.sym[src]);
       unsigned char* dst = outb + a.nbytes * src;
       if (aligned) {
-        unsigned long long i = v0 + threadIdx.x;
-        for (; i + 3ull * blockDim.x < v1; i += 4ull * blockDim.x) {
-          uint4 x0 = ld_sys_v4(sp + i), x1 = ld_sys_v4(sp + i + blockDim.x),
-                x2 = ld_sys_v4(sp + i + 2ull * blockDim.x),
-                x3 = ld_sys_v4(sp + i + 3ull * blockDim.x);
-          uint4* d = reinterpret_cast<uint4*>(dst);
-          d[i] = x0;
-          d[i + blockDim.x] = x1;
-          d[i + 2ull * blockDim.x] = x2;
-          d[i + 3ull * blockDim.x] = x3;
-        }
-        for (; i < v1; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = ld_sys_v4(sp + i);
+        uint4* d = reinterpret_cast<uint4*>(dst);
+        span_copy(
+            a.unroll, v0, v1, [&](unsigned long long i) { return ld_sys_v4(sp + i); },
+            [&](unsigned long long i, uint4 v) { d[i] = v; });
       } else {
         // Shard size not a multiple of 16 B: destinations are unaligned, go 4 bytes / 1 byte.
         const unsigned long long b0 = v0 * 16ull;
@@ -372,26 +453,19 @@ __global__ void __launch_bounds__(kCollThreads)
     const unsigned long long off = nvec * c.rank;
     if (a.mc != nullptr) {
       uint4* mc = static_cast<uint4*>(a.mc) + off;
-      unsigned long long i = v0 + threadIdx.x;
-      // Four independent loads in flight per thread before the first multicast store.
-      for (; i + 3ull * blockDim.x < v1; i += 4ull * blockDim.x) {
-        const uint4 x0 = src[i], x1 = src[i + blockDim.x], x2 = src[i + 2ull * blockDim.x],
-                    x3 = src[i + 3ull * blockDim.x];
-        mm_st_v4(mc + i, x0);
-        mm_st_v4(mc + i + blockDim.x, x1);
-        mm_st_v4(mc + i + 2ull * blockDim.x, x2);
-        mm_st_v4(mc + i + 3ull * blockDim.x, x3);
-      }
-      for (; i < v1; i += blockDim.x) mm_st_v4(mc + i, src[i]);
+      span_copy(
+          a.unroll, v0, v1, [&](unsigned long long i) { return src[i]; },
+          [&](unsigned long long i, uint4 v) { mm_st_v4(mc + i, v); });
     } else {
-      for (unsigned long long i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
-        const uint4 v = src[i];
+      span_copy(
+          a.unroll, v0, v1, [&](unsigned long long i) { return src[i]; },
+          [&](unsigned long long i, uint4 v) {
 #pragma unroll
-        for (int p = 0; p < W; ++p) {
-          const int dst = (c.rank + p) % W;
-          st_sys_v4(static_cast<uint4*>(a.sym[dst]) + off + i, v);
-        }
-      }
+            for (int p = 0; p < W; ++p) {
+              const int dst = (c.rank + p) % W;
+              st_sys_v4(static_cast<uint4*>(a.sym[dst]) + off + i, v);
+            }
+          });
     }
     ok = rank_barrier_block(c, ch, e + 2, PH_BARRIER_END);  // its release orders the stores
   }
@@ -421,58 +495,11 @@ __global__ void __launch_bounds__(kCollThreads)
     uint4* out = static_cast<uint4*>(a.out);
     if (a.mc != nullptr) {
       const uint4* mc = static_cast<const uint4*>(a.mc) + c0;
-      unsigned long long i = s0 + threadIdx.x;
-      for (; i + 3ull * blockDim.x < s1; i += 4ull * blockDim.x) {
-        uint4 r0 = Vec16<DT>::mm_reduce(mc + i);
-        uint4 r1 = Vec16<DT>::mm_reduce(mc + i + blockDim.x);
-        uint4 r2 = Vec16<DT>::mm_reduce(mc + i + 2ull * blockDim.x);
-        uint4 r3 = Vec16<DT>::mm_reduce(mc + i + 3ull * blockDim.x);
-        out[i] = r0;
-        out[i + blockDim.x] = r1;
-        out[i + 2ull * blockDim.x] = r2;
-        out[i + 3ull * blockDim.x] = r3;
-      }
-      for (; i < s1; i += blockDim.x) out[i] = Vec16<DT>::mm_reduce(mc + i);
+      span_copy(
+          a.unroll, s0, s1, [&](unsigned long long i) { return Vec16<DT>::mm_reduce(mc + i); },
+          [&](unsigned long long i, uint4 v) { out[i] = v; });
     } else {
-      // At least eight 16-byte loads in flight per thread: U vectors x W ranks per iteration.
-      constexpr int U = (W >= 8) ? 1 : 8 / W;
-      auto reduce_one = [&](const uint4(&raw)[W]) {
-        float acc[Vec16<DT>::N];
-#pragma unroll
-        for (int r = 0; r < W; ++r) {  // always summed in rank order, so every rank rounds alike
-          const int p = (r - c.rank + W) % W;
-          float f[Vec16<DT>::N];
-          Vec16<DT>::unpack(raw[p], f);
-#pragma unroll
-          for (int k = 0; k < Vec16<DT>::N; ++k) acc[k] = (r == 0) ? f[k] : acc[k] + f[k];
-        }
-        return Vec16<DT>::pack(acc);
-      };
-      unsigned long long i = s0 + threadIdx.x;
-      for (; i + static_cast<unsigned long long>(U - 1) * blockDim.x < s1;
-           i += static_cast<unsigned long long>(U) * blockDim.x) {
-        uint4 raw[U][W];
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-#pragma unroll
-          for (int p = 0; p < W; ++p) {
-            const int src = (c.rank + p) % W;
-            raw[u][p] = ld_sys_v4(static_cast<const uint4*>(a.sym[src]) + c0 + i +
-                                  static_cast<unsigned long long>(u) * blockDim.x);
-          }
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-          out[i + static_cast<unsigned long long>(u) * blockDim.x] = reduce_one(raw[u]);
-      }
-      for (; i < s1; i += blockDim.x) {
-        uint4 raw[W];
-#pragma unroll
-        for (int p = 0; p < W; ++p) {
-          const int src = (c.rank + p) % W;
-          raw[p] = ld_sys_v4(static_cast<const uint4*>(a.sym[src]) + c0 + i);
-        }
-        out[i] = reduce_one(raw);
-      }
+      reduce_span<DT, W>(a, c0, s0, s1, [&](unsigned long long i, uint4 v) { out[i] = v; });
     }
     ok = rank_barrier_block(c, ch, e + 2, PH_BARRIER_END);
   }
@@ -491,30 +518,49 @@ __global__ void __launch_bounds__(kCollThreads)
   const uint32_t e = begin_epoch(c, ch);
   const unsigned long long nvec = a.nbytes / 16ull;
   const unsigned long long per_rank = nvec / W;
+  unsigned long long s0, s1;
+  slice_of(per_rank, gridDim.x, blockIdx.x, &s0, &s1);
+  if (a.variant & 1) {
+    // Push form: sym[] is the (symmetric or staging) OUTPUT; chunk p of the local `in` is
+    // stored into slot `rank` of rank p.  Plain stores need no request in the other direction.
+    // Peers must have finished with the previous contents of their output first.
+    bool ok = rank_barrier_block(c, ch, e + 1, PH_BARRIER_START);
+    if (ok) {
+      const uint4* in = static_cast<const uint4*>(a.in);
+#pragma unroll 1
+      for (int p = 0; p < W; ++p) {
+        const int dst = (c.rank + p) % W;
+        const uint4* sp = in + per_rank * dst;
+        uint4* dp = static_cast<uint4*>(a.sym[dst]) + per_rank * c.rank;
+        span_copy(
+            a.unroll, s0, s1, [&](unsigned long long i) { return sp[i]; },
+            [&](unsigned long long i, uint4 v) { st_sys_v4(dp + i, v); });
+      }
+      ok = rank_barrier_block(c, ch, e + 2, PH_BARRIER_END);  // its release orders the stores
+    }
+    // Slice b of every slot was written here by block b of the slot's rank.
+    if (ok && a.copy_out)
+      for_each_chunk_slice(nvec, per_rank, W, [&](unsigned long long v0, unsigned long long v1) {
+        copy_vec_slice(a.out, a.sym[c.rank], v0, v1);
+      });
+    end_epoch(c, ch, e + 2);
+    return;
+  }
   if (a.copy_in)
     for_each_chunk_slice(nvec, per_rank, W, [&](unsigned long long v0, unsigned long long v1) {
       copy_vec_slice(a.sym[c.rank], a.in, v0, v1);
     });
   bool ok = rank_barrier_block(c, ch, e + 1, PH_BARRIER_START);
   if (ok) {
-    unsigned long long s0, s1;
-    slice_of(per_rank, gridDim.x, blockIdx.x, &s0, &s1);
     uint4* out = static_cast<uint4*>(a.out);
 #pragma unroll 1
     for (int p = 0; p < W; ++p) {
       const int src = (c.rank + p) % W;
       const uint4* sp = static_cast<const uint4*>(a.sym[src]) + per_rank * c.rank;
       uint4* dp = out + per_rank * src;
-      unsigned long long i = s0 + threadIdx.x;
-      for (; i + 3ull * blockDim.x < s1; i += 4ull * blockDim.x) {
-        uint4 x0 = ld_sys_v4(sp + i), x1 = ld_sys_v4(sp + i + blockDim.x),
-              x2 = ld_sys_v4(sp + i + 2ull * blockDim.x), x3 = ld_sys_v4(sp + i + 3ull * blockDim.x);
-        dp[i] = x0;
-        dp[i + blockDim.x] = x1;
-        dp[i + 2ull * blockDim.x] = x2;
-        dp[i + 3ull * blockDim.x] = x3;
-      }
-      for (; i < s1; i += blockDim.x) dp[i] = ld_sys_v4(sp + i);
+      span_copy(
+          a.unroll, s0, s1, [&](unsigned long long i) { return ld_sys_v4(sp + i); },
+          [&](unsigned long long i, uint4 v) { dp[i] = v; });
     }
     ok = rank_barrier_block(c, ch, e + 2, PH_BARRIER_END);
   }

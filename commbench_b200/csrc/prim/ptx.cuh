@@ -188,7 +188,11 @@ __device__ __forceinline__ bool wait_flag_ge_sys(const uint32_t* flag, uint32_t 
       if (globaltimer_ns() - t0 > timeout_ns) break;
       if (status != nullptr && ld_volatile(status) != 0u) break;  // somebody already failed
     }
-    if (it > 256u) __nanosleep(64);
+    // A few back-to-back polls for the latency-bound case, then paced ones: system-scope
+    // polls from a whole grid of waiting CTAs measurably delay the peers' stores into this
+    // GPU (see the paced variant below), and the CTAs that finish a bandwidth loop first
+    // wait here while the others' data is still arriving.
+    if (it >= 16u) __nanosleep(it < 256u ? 128u : 384u);
   }
   report_status(status, CB_TIMEOUT_PEER_FLAG, phase, detail);
   return false;

@@ -113,7 +113,8 @@ def main(argv=None) -> int:
     if "allreduce" in suites:
         step = 2 if args.quick else 1
         sizes = [1 << p for p in range(12, 31, step)]           # 4 KB ... 1 GB
-        algos = ["oneshot", "twoshot"] + (["nvls"] if ctx.has_multicast else []) + ["auto"]
+        algos = ["oneshot", "twoshot", "twoshot_push"] + \
+            (["nvls"] if ctx.has_multicast else []) + ["auto"]
         if world == 1:
             algos = ["oneshot"]
         sym_full, _ = ctx.empty((sizes[-1] // 2,), torch.bfloat16)
@@ -134,8 +135,8 @@ def main(argv=None) -> int:
                     continue
                 sym.copy_(x)
                 sync_all()
-                if algo == "oneshot" or (algo == "auto" and coll.choose_all_reduce_algo(
-                        nbytes, world, ctx.has_multicast) == "oneshot"):
+                if algo == "oneshot" or (algo == "auto" and coll.plan_all_reduce(
+                        ctx, nbytes, True)["algo"] == "oneshot"):
                     out = torch.empty_like(x)
                     y = coll.all_reduce(ctx, sym, out=out, algo=algo)
                     fn = lambda a=algo: coll.all_reduce(ctx, sym, out=out, algo=a)
@@ -151,7 +152,7 @@ def main(argv=None) -> int:
                 ctx.check_status()
                 f = roofline.allreduce_bus_factor(world)
                 resolved = algo if algo != "auto" else \
-                    coll.choose_all_reduce_algo(nbytes, world, ctx.has_multicast)
+                    coll.plan_all_reduce(ctx, nbytes, True)["algo"]
                 link = roofline.nvlink_bytes("all_reduce", nbytes, world, nvls=(resolved == "nvls"))
                 record("all_reduce", algo, (n,), "bf16", correct=correct, max_err=err, time_ms=ms,
                        baseline_ms=base_ms, busbw_gbs=f * nbytes / (ms * 1e-3) / 1e9,
@@ -208,6 +209,8 @@ def main(argv=None) -> int:
                 ("all_to_all", "symmetric-in", lambda: coll.all_to_all(ctx, x_sym),
                  lambda: base.all_to_all(x), "all_to_all", nbytes),
                 ("all_to_all", "staged", lambda: coll.all_to_all(ctx, x),
+                 lambda: base.all_to_all(x), "all_to_all", nbytes),
+                ("all_to_all", "symmetric-out", lambda: coll.all_to_all(ctx, x, out=ag_out),
                  lambda: base.all_to_all(x), "all_to_all", nbytes),
             ):
                 a, b = ours(), theirs()

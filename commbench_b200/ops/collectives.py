@@ -34,6 +34,7 @@ import torch
 
 from .. import _native as N
 from ..config import get_config
+from . import tuning
 from ..runtime.context import CommContext, CommError, EmuContext
 
 _DT = {torch.bfloat16: N.DT_BF16, torch.float16: N.DT_F16, torch.float32: N.DT_F32}
@@ -84,8 +85,22 @@ def choose_all_reduce_algo(nbytes: int, world: int, has_multicast: bool) -> str:
     return "twoshot"
 
 
+def plan_all_reduce(ctx, nbytes: int, symmetric: bool) -> dict:
+    """What ``all_reduce(..., algo="auto")`` will run for this message: ``{"algo", "blocks",
+    "unroll"}`` (``blocks`` / ``unroll`` None where the size rule decides).  The measured table
+    wins where it has a row; a row that asks for NVLS without a bound multicast object (or for a
+    size that is not a multiple of 16 bytes) falls back to the size rule."""
+    row = tuning.lookup("all_reduce", ctx.world, nbytes, "symmetric" if symmetric else "staged")
+    algo = row.get("algo") or choose_all_reduce_algo(nbytes, ctx.world, ctx.has_multicast)
+    if algo == "nvls" and not (ctx.has_multicast and nbytes % 16 == 0):
+        return {"algo": choose_all_reduce_algo(nbytes, ctx.world, False), "blocks": None,
+                "unroll": None}
+    return {"algo": algo, "blocks": row.get("blocks"), "unroll": row.get("unroll")}
+
+
 def _fill_args(comm: N.CbComm, sym_ptrs, mc_ptr, inp_ptr, out_ptr, nbytes, *, copy_in=0,
-               copy_out=0, root=0, dtype=0, a2a=(0, 0, 0, 0, 0)) -> N.CollArgs:
+               copy_out=0, root=0, dtype=0, a2a=(0, 0, 0, 0, 0), unroll=0,
+               variant=0) -> N.CollArgs:
     a = N.CollArgs()
     a.comm = comm
     for r in range(N.MAX_RANKS):
@@ -96,6 +111,7 @@ def _fill_args(comm: N.CbComm, sym_ptrs, mc_ptr, inp_ptr, out_ptr, nbytes, *, co
     a.nbytes = nbytes
     a.copy_in, a.copy_out, a.root, a.dtype = copy_in, copy_out, root, dtype
     a.a2a_b, a.a2a_s_local, a.a2a_h, a.a2a_d, a.a2a_to_heads = a2a
+    a.unroll, a.variant = int(unroll or 0), int(variant)
     return a
 
 
@@ -141,9 +157,12 @@ def _pad16(n: int) -> int:
 # =============================================================== real contexts
 def all_reduce(ctx: CommContext, x: torch.Tensor, out: torch.Tensor | None = None,
                algo: str = "auto", max_blocks: int | None = None, stream=None,
-               blocks: int | None = None) -> torch.Tensor:
+               blocks: int | None = None, unroll: int | None = None) -> torch.Tensor:
     """Sum over ranks.  In place when ``out`` is None.  ``algo`` in
-    {"auto", "oneshot", "twoshot", "nvls"}.  ``blocks`` forces the grid size (tuning)."""
+    {"auto", "oneshot", "twoshot", "twoshot_push", "nvls"}; "auto" takes the measured table
+    (:mod:`.tuning`) where it has a row and the size rule of :func:`choose_all_reduce_algo`
+    otherwise.  ``blocks`` / ``unroll`` force the grid size and the 16-byte vectors each
+    thread keeps in flight."""
     _check_local(x, "x")
     out = x if out is None else out
     _check_local(out, "out")
@@ -151,20 +170,27 @@ def all_reduce(ctx: CommContext, x: torch.Tensor, out: torch.Tensor | None = Non
     if nbytes == 0:
         return out
     cfg = get_config()
+    sym = ctx.find_block(x) if nbytes % 16 == 0 else None
     if algo == "auto":
-        algo = choose_all_reduce_algo(nbytes, ctx.world, ctx.has_multicast)
+        plan = plan_all_reduce(ctx, nbytes, sym is not None)
+        algo = plan["algo"]
+        if blocks is None and max_blocks is None:
+            blocks = plan["blocks"]
+        if unroll is None:
+            unroll = plan["unroll"]
     if algo == "nvls" and not ctx.has_multicast:
         raise CommError("algo='nvls' needs a bound multicast object (not available here)")
+    if algo not in ("oneshot", "twoshot", "twoshot_push", "nvls"):
+        raise CommError(f"unknown all-reduce algorithm {algo!r}")
     if blocks is None:
         # One-shot is latency bound: every CTA reads its slice from all W ranks, so slices are
         # kept small; the chunked algorithms move nbytes / W per rank.
         grain = cfg.ar_oneshot_grain_bytes if algo == "oneshot" else cfg.ar_chunk_grain_bytes
         cap = max_blocks or cfg.coll_max_blocks
-        if max_blocks is None and algo == "twoshot" and nbytes >= (16 << 20):
+        if max_blocks is None and algo.startswith("twoshot") and nbytes >= (16 << 20):
             cap = cfg.coll_max_blocks_large      # pull-based: more loads in flight pay off
         blocks = pick_blocks(nbytes, cap, grain)
     dt = _dtype_code(x)
-    sym = ctx.find_block(x) if nbytes % 16 == 0 else None
     if algo == "oneshot":
         # Result must not land in memory peers read: stage unless x is symmetric and out is not x.
         if sym is not None and out.data_ptr() != x.data_ptr():
@@ -175,21 +201,23 @@ def all_reduce(ctx: CommContext, x: torch.Tensor, out: torch.Tensor | None = Non
                            copy_in=1, dtype=dt)
         _launch(ctx, N.OP_AR_ONESHOT, a, blocks, stream)
         return out
-    op = N.OP_AR_TWOSHOT if algo == "twoshot" else N.OP_AR_NVLS
+    op = N.OP_AR_NVLS if algo == "nvls" else N.OP_AR_TWOSHOT
+    var = 1 if algo == "twoshot_push" else 0
     if sym is not None and (algo != "nvls" or sym[1]):
         same = out.data_ptr() == x.data_ptr()
         a = _fill_args(ctx.comm, sym[0], sym[1], x.data_ptr(), out.data_ptr(), nbytes,
-                       copy_in=0, copy_out=0 if same else 1, dtype=dt)
+                       copy_in=0, copy_out=0 if same else 1, dtype=dt, unroll=unroll, variant=var)
     else:
         st = ctx.named("coll_stage", _pad16(nbytes))
         a = _fill_args(ctx.comm, st.peer_ptrs, st.mc_ptr, x.data_ptr(), out.data_ptr(), nbytes,
-                       copy_in=1, copy_out=1, dtype=dt)
+                       copy_in=1, copy_out=1, dtype=dt, unroll=unroll, variant=var)
     _launch(ctx, op, a, blocks, stream)
     return out
 
 
 def all_gather(ctx: CommContext, x: torch.Tensor, out: torch.Tensor | None = None,
-               max_blocks: int | None = None, stream=None) -> torch.Tensor:
+               max_blocks: int | None = None, stream=None, blocks: int | None = None,
+               unroll: int | None = None, multicast: bool | None = None) -> torch.Tensor:
     """Concatenates every rank's ``x`` along dim 0.  If ``out`` lives in the symmetric heap the
     shards are pushed straight into every rank's copy (one multimem.st per vector when NVLS
     is bound); otherwise shards are staged and pulled."""
@@ -202,28 +230,39 @@ def all_gather(ctx: CommContext, x: torch.Tensor, out: torch.Tensor | None = Non
     if out.numel() * out.element_size() != ctx.world * nbytes:
         raise CommError("all_gather: out has the wrong size")
     cfg = get_config()
-    blocks = pick_blocks(nbytes, max_blocks or _default_cap(cfg, nbytes))
     osym = ctx.find_block(out)
-    if osym is not None and nbytes % 16 == 0:
+    push = osym is not None and nbytes % 16 == 0
+    row = tuning.lookup("all_gather", ctx.world, nbytes, "push" if push else "pull")
+    if blocks is None:
+        blocks = (row.get("blocks") if max_blocks is None else None) or \
+            pick_blocks(nbytes, max_blocks or _default_cap(cfg, nbytes))
+    if unroll is None:
+        unroll = row.get("unroll")
+    if push:
         # One multicast store replaces W-1 peer stores; between two ranks it replaces one and
         # was measured slower than plain stores for large shards.
-        mc = osym[1] if (ctx.world > 2 or nbytes < cfg.ar_nvls_max_bytes_two_ranks) else 0
-        a = _fill_args(ctx.comm, osym[0], mc, x.data_ptr(), out.data_ptr(), nbytes)
+        use_mc = multicast if multicast is not None else row.get("multicast")
+        if use_mc is None:
+            use_mc = ctx.world > 2 or nbytes < cfg.ar_nvls_max_bytes_two_ranks
+        mc = osym[1] if use_mc else 0
+        a = _fill_args(ctx.comm, osym[0], mc, x.data_ptr(), out.data_ptr(), nbytes, unroll=unroll)
         _launch(ctx, N.OP_AG_PUSH, a, blocks, stream)
         return out
     xsym = ctx.find_block(x)
     if xsym is not None:
-        a = _fill_args(ctx.comm, xsym[0], 0, x.data_ptr(), out.data_ptr(), nbytes)
+        a = _fill_args(ctx.comm, xsym[0], 0, x.data_ptr(), out.data_ptr(), nbytes, unroll=unroll)
     else:
         st = ctx.named("coll_stage", _pad16(nbytes))
-        a = _fill_args(ctx.comm, st.peer_ptrs, 0, x.data_ptr(), out.data_ptr(), nbytes, copy_in=1)
+        a = _fill_args(ctx.comm, st.peer_ptrs, 0, x.data_ptr(), out.data_ptr(), nbytes, copy_in=1,
+                       unroll=unroll)
     _launch(ctx, N.OP_AG_PULL, a, blocks, stream)
     return out
 
 
 def reduce_scatter(ctx: CommContext, x: torch.Tensor, out: torch.Tensor | None = None,
                    use_nvls: bool | None = None, max_blocks: int | None = None,
-                   stream=None) -> torch.Tensor:
+                   stream=None, blocks: int | None = None,
+                   unroll: int | None = None) -> torch.Tensor:
     """``x`` holds W equal chunks along dim 0; rank r receives the sum of chunk r."""
     _check_local(x, "x")
     nbytes = x.numel() * x.element_size()
@@ -234,9 +273,17 @@ def reduce_scatter(ctx: CommContext, x: torch.Tensor, out: torch.Tensor | None =
                           device=x.device)
     _check_local(out, "out")
     cfg = get_config()
-    blocks = pick_blocks(nbytes // ctx.world, max_blocks or _default_cap(cfg, nbytes // ctx.world))
     dt = _dtype_code(x)
     sym = ctx.find_block(x)
+    row = tuning.lookup("reduce_scatter", ctx.world, nbytes,
+                        "symmetric" if sym is not None else "staged")
+    if blocks is None:
+        blocks = (row.get("blocks") if max_blocks is None else None) or \
+            pick_blocks(nbytes // ctx.world, max_blocks or _default_cap(cfg, nbytes // ctx.world))
+    if unroll is None:
+        unroll = row.get("unroll")
+    if use_nvls is None:
+        use_nvls = row.get("nvls")
     if use_nvls is None:
         # Between two ranks the switch reduction adds a hop and saves no link bytes: above a few
         # MB plain peer loads are faster (measured), as for all-reduce.
@@ -245,18 +292,24 @@ def reduce_scatter(ctx: CommContext, x: torch.Tensor, out: torch.Tensor | None =
         want_nvls = use_nvls and ctx.has_multicast
     if sym is not None:
         a = _fill_args(ctx.comm, sym[0], sym[1] if want_nvls else 0, x.data_ptr(), out.data_ptr(),
-                       nbytes, dtype=dt)
+                       nbytes, dtype=dt, unroll=unroll)
     else:
         st = ctx.named("coll_stage", nbytes)
         a = _fill_args(ctx.comm, st.peer_ptrs, st.mc_ptr if want_nvls else 0, x.data_ptr(),
-                       out.data_ptr(), nbytes, copy_in=1, dtype=dt)
+                       out.data_ptr(), nbytes, copy_in=1, dtype=dt, unroll=unroll)
     _launch(ctx, N.OP_RS, a, blocks, stream)
     return out
 
 
 def all_to_all(ctx: CommContext, x: torch.Tensor, out: torch.Tensor | None = None,
-               max_blocks: int | None = None, stream=None) -> torch.Tensor:
-    """Flat exchange of W equal chunks along dim 0 (``all_to_all_single`` semantics)."""
+               max_blocks: int | None = None, stream=None, blocks: int | None = None,
+               unroll: int | None = None, push: bool | None = None) -> torch.Tensor:
+    """Flat exchange of W equal chunks along dim 0 (``all_to_all_single`` semantics).
+
+    Pull form: every rank loads its chunk out of each peer's (symmetric or staged) input.
+    Push form (``push=True``; the default when ``out`` lives in the symmetric heap): every rank
+    stores chunk p of its local ``x`` straight into rank p's output - no staging copy, and
+    stores need no request packet in the opposite direction."""
     _check_local(x, "x")
     nbytes = x.numel() * x.element_size()
     if x.shape[0] % ctx.world != 0 or (nbytes // ctx.world) % 16 != 0:
@@ -264,13 +317,33 @@ def all_to_all(ctx: CommContext, x: torch.Tensor, out: torch.Tensor | None = Non
     out = torch.empty_like(x) if out is None else out
     _check_local(out, "out")
     cfg = get_config()
-    blocks = pick_blocks(nbytes, max_blocks or _default_cap(cfg, nbytes))
     sym = ctx.find_block(x)
-    if sym is not None:
-        a = _fill_args(ctx.comm, sym[0], 0, x.data_ptr(), out.data_ptr(), nbytes)
+    osym = ctx.find_block(out)
+    kind = "out_symmetric" if osym is not None else ("symmetric" if sym is not None else "staged")
+    row = tuning.lookup("all_to_all", ctx.world, nbytes, kind)
+    if push is None:
+        push = row.get("push")
+    if push is None:
+        push = osym is not None
+    if blocks is None:
+        blocks = (row.get("blocks") if max_blocks is None else None) or \
+            pick_blocks(nbytes, max_blocks or _default_cap(cfg, nbytes))
+    if unroll is None:
+        unroll = row.get("unroll")
+    if push:
+        if osym is not None:
+            a = _fill_args(ctx.comm, osym[0], 0, x.data_ptr(), out.data_ptr(), nbytes,
+                           unroll=unroll, variant=1)
+        else:
+            st = ctx.named("coll_stage", nbytes)
+            a = _fill_args(ctx.comm, st.peer_ptrs, 0, x.data_ptr(), out.data_ptr(), nbytes,
+                           copy_out=1, unroll=unroll, variant=1)
+    elif sym is not None:
+        a = _fill_args(ctx.comm, sym[0], 0, x.data_ptr(), out.data_ptr(), nbytes, unroll=unroll)
     else:
         st = ctx.named("coll_stage", nbytes)
-        a = _fill_args(ctx.comm, st.peer_ptrs, 0, x.data_ptr(), out.data_ptr(), nbytes, copy_in=1)
+        a = _fill_args(ctx.comm, st.peer_ptrs, 0, x.data_ptr(), out.data_ptr(), nbytes, copy_in=1,
+                       unroll=unroll)
     _launch(ctx, N.OP_A2A_FLAT, a, blocks, stream)
     return out
 
@@ -351,22 +424,24 @@ def _emu_blocks(nbytes: int) -> int:
 
 
 def emu_all_reduce(ctx: EmuContext, xs: list[torch.Tensor], algo: str = "oneshot",
-                   blocks: int | None = None) -> list[torch.Tensor]:
+                   blocks: int | None = None, unroll: int = 0) -> list[torch.Tensor]:
     W = ctx.world
     nbytes = xs[0].numel() * xs[0].element_size()
     stage = ctx.alloc(_pad16(nbytes))
     outs = [torch.empty_like(x) for x in xs]
     sym = [s.data_ptr() for s in stage]
-    op = {"oneshot": N.OP_AR_ONESHOT, "twoshot": N.OP_AR_TWOSHOT}[algo]
+    op = {"oneshot": N.OP_AR_ONESHOT, "twoshot": N.OP_AR_TWOSHOT,
+          "twoshot_push": N.OP_AR_TWOSHOT}[algo]
     args = [_fill_args(ctx.comms[r], sym, 0, xs[r].data_ptr(), outs[r].data_ptr(), nbytes,
-                       copy_in=1, copy_out=1, dtype=_dtype_code(xs[r])) for r in range(W)]
+                       copy_in=1, copy_out=1, dtype=_dtype_code(xs[r]), unroll=unroll,
+                       variant=1 if algo == "twoshot_push" else 0) for r in range(W)]
     _launch_emu(ctx, op, args, blocks or _emu_blocks(nbytes))
     ctx._stage = stage
     return outs
 
 
 def emu_all_gather(ctx: EmuContext, xs: list[torch.Tensor], push: bool = False,
-                   blocks: int | None = None) -> list[torch.Tensor]:
+                   blocks: int | None = None, unroll: int = 0) -> list[torch.Tensor]:
     W = ctx.world
     nbytes = xs[0].numel() * xs[0].element_size()
     oshape = (W * xs[0].shape[0],) + tuple(xs[0].shape[1:])
@@ -374,8 +449,8 @@ def emu_all_gather(ctx: EmuContext, xs: list[torch.Tensor], push: bool = False,
         outs_raw = ctx.alloc(W * nbytes)
         outs = [o[:W * nbytes].view(xs[0].dtype).view(oshape) for o in outs_raw]
         sym = [o.data_ptr() for o in outs_raw]
-        args = [_fill_args(ctx.comms[r], sym, 0, xs[r].data_ptr(), outs[r].data_ptr(), nbytes)
-                for r in range(W)]
+        args = [_fill_args(ctx.comms[r], sym, 0, xs[r].data_ptr(), outs[r].data_ptr(), nbytes,
+                           unroll=unroll) for r in range(W)]
         _launch_emu(ctx, N.OP_AG_PUSH, args, blocks or _emu_blocks(nbytes))
         ctx._stage = outs_raw
         return outs
@@ -383,14 +458,14 @@ def emu_all_gather(ctx: EmuContext, xs: list[torch.Tensor], push: bool = False,
     outs = [torch.empty(oshape, dtype=xs[0].dtype, device=xs[0].device) for _ in range(W)]
     sym = [s.data_ptr() for s in stage]
     args = [_fill_args(ctx.comms[r], sym, 0, xs[r].data_ptr(), outs[r].data_ptr(), nbytes,
-                       copy_in=1) for r in range(W)]
+                       copy_in=1, unroll=unroll) for r in range(W)]
     _launch_emu(ctx, N.OP_AG_PULL, args, blocks or _emu_blocks(nbytes))
     ctx._stage = stage
     return outs
 
 
 def emu_reduce_scatter(ctx: EmuContext, xs: list[torch.Tensor],
-                       blocks: int | None = None) -> list[torch.Tensor]:
+                       blocks: int | None = None, unroll: int = 0) -> list[torch.Tensor]:
     W = ctx.world
     nbytes = xs[0].numel() * xs[0].element_size()
     stage = ctx.alloc(nbytes)
@@ -398,21 +473,22 @@ def emu_reduce_scatter(ctx: EmuContext, xs: list[torch.Tensor],
     outs = [torch.empty(oshape, dtype=xs[0].dtype, device=xs[0].device) for _ in range(W)]
     sym = [s.data_ptr() for s in stage]
     args = [_fill_args(ctx.comms[r], sym, 0, xs[r].data_ptr(), outs[r].data_ptr(), nbytes,
-                       copy_in=1, dtype=_dtype_code(xs[r])) for r in range(W)]
+                       copy_in=1, dtype=_dtype_code(xs[r]), unroll=unroll) for r in range(W)]
     _launch_emu(ctx, N.OP_RS, args, blocks or _emu_blocks(nbytes // W))
     ctx._stage = stage
     return outs
 
 
-def emu_all_to_all(ctx: EmuContext, xs: list[torch.Tensor],
-                   blocks: int | None = None) -> list[torch.Tensor]:
+def emu_all_to_all(ctx: EmuContext, xs: list[torch.Tensor], blocks: int | None = None,
+                   unroll: int = 0, push: bool = False) -> list[torch.Tensor]:
     W = ctx.world
     nbytes = xs[0].numel() * xs[0].element_size()
     stage = ctx.alloc(nbytes)
     outs = [torch.empty_like(x) for x in xs]
     sym = [s.data_ptr() for s in stage]
     args = [_fill_args(ctx.comms[r], sym, 0, xs[r].data_ptr(), outs[r].data_ptr(), nbytes,
-                       copy_in=1) for r in range(W)]
+                       copy_in=0 if push else 1, copy_out=1 if push else 0, unroll=unroll,
+                       variant=1 if push else 0) for r in range(W)]
     _launch_emu(ctx, N.OP_A2A_FLAT, args, blocks or _emu_blocks(nbytes))
     ctx._stage = stage
     return outs

@@ -15,7 +15,7 @@ def _inputs(world, shape, dtype, seed=0):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("algo", ["oneshot", "twoshot"])
+@pytest.mark.parametrize("algo", ["oneshot", "twoshot", "twoshot_push"])
 @pytest.mark.parametrize("numel", [8, 1000, 4096, 262144 + 24])
 def test_emu_all_reduce(native_lib, world, algo, numel):
     from commbench_b200.ops import collectives as coll
@@ -79,13 +79,14 @@ def test_emu_all_gather_unaligned_shard(native_lib):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_emu_reduce_scatter(native_lib, world):
+@pytest.mark.parametrize("unroll", [0, 1, 2, 8])
+def test_emu_reduce_scatter(native_lib, world, unroll):
     from commbench_b200.ops import collectives as coll
     from commbench_b200.runtime.context import EmuContext
 
     ctx = EmuContext(world)
     xs = _inputs(world, (world * 64, 72), torch.bfloat16)
-    outs = coll.emu_reduce_scatter(ctx, xs)
+    outs = coll.emu_reduce_scatter(ctx, xs, unroll=unroll)
     ctx.check_status()
     total = sum(x.float() for x in xs)
     for r, o in enumerate(outs):
@@ -93,13 +94,14 @@ def test_emu_reduce_scatter(native_lib, world):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_emu_all_to_all_flat(native_lib, world):
+@pytest.mark.parametrize("push,unroll", [(False, 0), (False, 8), (True, 0), (True, 2)])
+def test_emu_all_to_all_flat(native_lib, world, push, unroll):
     from commbench_b200.ops import collectives as coll
     from commbench_b200.runtime.context import EmuContext
 
     ctx = EmuContext(world)
     xs = _inputs(world, (world * 24, 64), torch.bfloat16)
-    outs = coll.emu_all_to_all(ctx, xs)
+    outs = coll.emu_all_to_all(ctx, xs, push=push, unroll=unroll)
     ctx.check_status()
     for r in range(world):
         ref = torch.cat([xs[p][r * 24:(r + 1) * 24] for p in range(world)], dim=0)
@@ -195,3 +197,38 @@ def test_collectives_are_bit_stable_under_start_jitter(native_lib, world, monkey
         gathered = coll.emu_all_gather(ctx, xs, push=True)
         assert torch.equal(gathered[world - 1], torch.cat(xs))
         ctx.check_status()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("algo", ["twoshot", "twoshot_push"])
+@pytest.mark.parametrize("unroll", [1, 2, 4, 8])
+def test_emu_all_reduce_vectors_in_flight(native_lib, world, algo, unroll):
+    """Every unroll depth of the pull loops gives the same bits as the default one, on a size
+    with full iterations, a remainder and a ragged tail."""
+    from commbench_b200.ops import collectives as coll
+    from commbench_b200.runtime.context import EmuContext
+
+    ctx = EmuContext(world)
+    xs = _inputs(world, (3 * 512 * 8 * 8 + 44,), torch.bfloat16)
+    base = coll.emu_all_reduce(ctx, xs, algo="twoshot", blocks=2)
+    outs = coll.emu_all_reduce(ctx, xs, algo=algo, blocks=2, unroll=unroll)
+    ctx.check_status()
+    for o in outs:
+        assert torch.equal(o, base[0])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("unroll", [2, 4, 8])
+def test_emu_all_gather_vectors_in_flight(native_lib, unroll):
+    from commbench_b200.ops import collectives as coll
+    from commbench_b200.runtime.context import EmuContext
+
+    ctx = EmuContext(4)
+    xs = _inputs(4, (5 * 512 * 8 + 64,), torch.bfloat16)
+    ref = torch.cat(xs)
+    for push in (False, True):
+        outs = coll.emu_all_gather(ctx, xs, push=push, unroll=unroll, blocks=1)
+        ctx.check_status()
+        for o in outs:
+            assert torch.equal(o.flatten(), ref)

@@ -21,7 +21,7 @@ class Config:
     ar_nvls_min_bytes: int = 16                 # multicast bound, at or above: NVLS
     ar_nvls_max_bytes_two_ranks: int = 8 << 20  # with 2 ranks, NVLS only below this size
     coll_max_blocks: int = 64                   # CTAs per collective kernel (<= one wave)
-    coll_max_blocks_large: int = 148            # two-shot all-reduce of 16 MB and more
+    coll_max_blocks_large: int = 128            # bandwidth collectives of 16 MB and more
     ar_oneshot_grain_bytes: int = 8 * 1024      # message bytes per CTA, one-shot all-reduce
     ar_chunk_grain_bytes: int = 64 * 1024       # message bytes per CTA, two-shot / NVLS
     # --- fused GEMMs -------------------------------------------------------

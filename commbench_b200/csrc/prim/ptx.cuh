@@ -192,7 +192,7 @@ __device__ __forceinline__ bool wait_flag_ge_sys(const uint32_t* flag, uint32_t 
     // polls from a whole grid of waiting CTAs measurably delay the peers' stores into this
     // GPU (see the paced variant below), and the CTAs that finish a bandwidth loop first
     // wait here while the others' data is still arriving.
-    if (it >= 16u) __nanosleep(it < 256u ? 128u : 384u);
+    if (it >= 16u) __nanosleep(it < 64u ? 128u : (it < 256u ? 512u : 1024u));
   }
   report_status(status, CB_TIMEOUT_PEER_FLAG, phase, detail);
   return false;

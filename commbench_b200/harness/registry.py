@@ -92,25 +92,31 @@ def examples_covered() -> set[str]:
 # where one is shipped, the generate/build/run task that poses the same exercise.
 API: dict = {
     "all_reduce": ("ops.collectives.all_reduce (one-shot / two-shot / NVLS by size)",
-                   "gloo_allreduce, oneshot_allreduce_virtual_ranks"),
+                   "gloo_allreduce, oneshot_allreduce_virtual_ranks, nvls_all_reduce, "
+                   "twoshot_allreduce_tuned"),
     "internode_all_reduce": ("ops.transport.PutSignalAllReduce", None),
-    "all_gather": ("ops.collectives.all_gather (pull / push / multimem)", None),
-    "reduce_scatter": ("ops.collectives.reduce_scatter (pull / multimem.ld_reduce)", None),
+    "all_gather": ("ops.collectives.all_gather (pull / push / multimem)",
+                   "all_gather_last_dim, nvls_all_gather"),
+    "reduce_scatter": ("ops.collectives.reduce_scatter (pull / multimem.ld_reduce)",
+                       "reduce_scatter_blocks, nvls_reduce_scatter"),
     "all_to_all": ("ops.collectives.all_to_all, all_to_all_4d; ops.p2p.ulysses_all_to_all_nccl",
-                   "ulysses_all_to_all"),
+                   "ulysses_all_to_all, alltoall_4d_symmetric"),
     "broadcast": ("ops.collectives.broadcast; ops.p2p.WeightBroadcaster", "weight_broadcast"),
-    "barrier": ("ops.collectives.barrier (flag matrix / multimem.red)", None),
-    "ag_gemm": ("ops.tp.AgGemm; parallel.tp.ColumnParallelLinear", None),
-    "gemm_rs": ("ops.tp.GemmRs; parallel.tp.RowParallelLinear", None),
-    "gemm_ar": ("ops.tp.GemmAr", None),
+    "barrier": ("ops.collectives.barrier (flag matrix / multimem.red)", "nvls_barrier_latency"),
+    "ag_gemm": ("ops.tp.AgGemm; parallel.tp.ColumnParallelLinear",
+                "ag_gemm_fused, ag_gemm_fp8_fused, ag_gemm_virtual_ranks"),
+    "gemm_rs": ("ops.tp.GemmRs; parallel.tp.RowParallelLinear",
+                "gemm_rs_fused, gemm_rs_virtual_ranks"),
+    "gemm_ar": ("ops.tp.GemmAr", "gemm_ar_fused"),
     "tp_qknorm": ("ops.fused.TPQKNorm", None),
     "gemm": ("ops.gemm.gemm, gemm_fp8_blockscaled", None),
     "moe_layer": ("ops.moe.MoELayer; parallel.ep.ExpertParallelMoE; ops.p2p.all_gatherv / reduce_scatterv",
-                  "moe_agrs_dispatch"),
+                  "moe_agrs_dispatch, moe_dispatch_gemm"),
     "moe_dispatch_layout": ("ops.moe.dispatch_layout, router_topk, expert_sort", "moe_dispatch_layout"),
     "eplb_rebalance": ("ops.p2p.rearrange_expert_weights_inplace", "eplb_rebalance"),
-    "ring_attention": ("ops.cp.RingAttention; parallel.cp.ContextParallelAttention", None),
-    "ulysses_attention": ("ops.cp.ulysses_attention", None),
+    "ring_attention": ("ops.cp.RingAttention; parallel.cp.ContextParallelAttention",
+                       "ring_attention_kernel"),
+    "ulysses_attention": ("ops.cp.UlyssesAttention, ulysses_attention", "ulysses_attention_kernel"),
     "flash_attention": ("ops.cp.flash_attention", None),
     "p2p_copy": ("ops.util.peer_copy_bandwidth, memcpy_bandwidth, ipc_export / ipc_import", "d2d_copy_kernel"),
     "p2p_pingpong": ("ops.util.pingpong_latency", None),
@@ -149,6 +155,19 @@ EXAMPLE_TASK: dict = {
     "example109": "oneshot_allreduce_virtual_ranks", "example020": "ulysses_all_to_all",
     "example058": "ulysses_all_to_all", "example087": "weight_broadcast", "example084": "moe_agrs_dispatch",
     "example042": "moe_dispatch_layout", "example074": "d2d_copy_kernel", "example077": "d2d_copy_kernel",
+    "example043": "nvls_all_reduce", "example048": "nvls_all_reduce", "example060": "nvls_all_reduce",
+    "example045": "nvls_all_gather", "example046": "nvls_all_gather", "example059": "nvls_all_gather",
+    "example050": "nvls_reduce_scatter", "example062": "nvls_reduce_scatter",
+    "example091": "nvls_reduce_scatter", "example017": "nvls_barrier_latency",
+    "example049": "alltoall_4d_symmetric", "example061": "alltoall_4d_symmetric",
+    "example051": "ag_gemm_fused", "example063": "ag_gemm_fused",
+    "example052": "ag_gemm_fp8_fused", "example064": "ag_gemm_fp8_fused",
+    "example054": "gemm_rs_fused", "example066": "gemm_rs_fused",
+    "example053": "gemm_ar_fused", "example065": "gemm_ar_fused",
+    "example056": "moe_dispatch_gemm", "example068": "moe_dispatch_gemm",
+    "example057": "ring_attention_kernel", "example069": "ring_attention_kernel",
+    "example070": "ulysses_attention_kernel",
+    "example031": "twoshot_allreduce_tuned", "example097": "twoshot_allreduce_tuned",
 }
 EXAMPLE_API: dict = {
     "example004": "ops.transport.Context.device_info", "example029": "ops.transport.Context.device_info",

@@ -28,12 +28,14 @@ from . import collectives as coll
 from . import tuning
 
 
-def _grid_candidates(per_cta_bytes_total: int, cap: int = 148) -> list[int]:
+def _grid_candidates(per_cta_bytes_total: int, cap: int = 128) -> list[int]:
     """Grid sizes worth trying for a message whose per-rank share is ``per_cta_bytes_total``
-    bytes: no CTA gets less than 8 KB."""
+    bytes: no CTA gets less than 8 KB.  Grids stop at 128 CTAs: a collective that fills all
+    148 SMs measured bimodal (it leaves no SM to whatever else the stream runs, and its
+    waiting CTAs are the most pollers a GPU can have)."""
     most = max(1, min(cap, per_cta_bytes_total // 8192))
     least = min(most, per_cta_bytes_total // (2 << 20))     # nor more than 2 MB
-    out = [b for b in (4, 8, 16, 32, 48, 64, 96, 128, 148) if least <= b <= most]
+    out = [b for b in (4, 8, 16, 32, 64, 96, 128) if least <= b <= most]
     if not out:
         out = [most]
     return out

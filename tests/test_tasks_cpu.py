@@ -17,7 +17,26 @@ FAMILIES = {"A", "B", "C", "D", "E", "F", "G", "H", "I"}
 
 def test_task_set_covers_several_families():
     fams = {CR.load_task(os.path.join(TASKS, t)).get("family") for t in ALL}
-    assert len(ALL) >= 10 and {"A", "B", "C", "G"} <= fams and fams <= FAMILIES | {None}
+    assert len(ALL) >= 40 and {"A", "B", "C", "D", "F", "G", "H", "I"} <= fams
+    assert fams <= FAMILIES | {None}
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("task", ["nvls_all_reduce", "ag_gemm_virtual_ranks"])
+def test_gpu_task_skips_cleanly_without_enough_gpus(task, tmp_path):
+    """A multi-GPU task launched on a machine that cannot run it prints Correctness SKIP and
+    exits 0 before it creates a process group or a symmetric heap."""
+    import torch
+
+    folder = os.path.join(TASKS, task)
+    spec = CR.load_task(folder)
+    if torch.cuda.is_available() and torch.cuda.device_count() >= spec["world"]:
+        pytest.skip("this machine can run the task")
+    r = CR.compile_and_run(folder, CR.find_ref_file(folder), work_dir=str(tmp_path))
+    assert r.run_success, r.output[-2000:]
+    assert (r.result_json or {}).get("Correctness") == "SKIP"
+    assert CR.analyze_result(r)[0]
+    shutil.rmtree(os.path.join(folder, "__pycache__"), ignore_errors=True)
 
 
 @pytest.mark.parametrize("task", ALL)

@@ -5,6 +5,8 @@
     python -m commbench_b200.harness.profile_case attn   [--seq 8192 --heads 16]
     python -m commbench_b200.harness.profile_case quant
     python -m commbench_b200.harness.profile_case moe    [--tokens 4096]   # per-stage event times
+    python -m commbench_b200.harness.profile_case ag_gemm | gemm_rs | gemm_ar  [--world 2]
+                                  # the fused kernels, virtual ranks inside ONE cooperative launch
 
 Each case allocates inputs larger than the 126 MB L2 but well under a few GB, runs two warm-up
 launches and ``--launches`` measured ones (default 3), prints the CUDA-event time and exits.
@@ -36,7 +38,9 @@ def _time(fn, launches: int) -> float:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "gemm_fp8", "attn", "quant", "moe"])
+    ap.add_argument("case", choices=["gemm", "gemm_fp8", "attn", "quant", "moe", "ag_gemm",
+                                     "gemm_rs", "gemm_ar"])
+    ap.add_argument("--world", type=int, default=2, help="virtual ranks of the fused cases")
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -73,6 +77,29 @@ def main(argv=None) -> int:
         ms = _time(lambda: flash_attention(q, k, v, causal=True), a.launches)
         out.update(shape=[1, a.seq, a.heads, a.heads // 4, 128], ms=ms,
                    tflops=4.0 * a.seq * a.seq * 128 * a.heads / 2 / ms / 1e9)
+    elif a.case in ("ag_gemm", "gemm_rs", "gemm_ar"):
+        # W virtual ranks on this one GPU share its SMs, so the rate to compare with is the
+        # plain GEMM's on 148 / W SMs; what the capture shows is the kernel's own behaviour
+        # (tensor pipe, DRAM bytes against the algorithmic bytes, stalls on flags).
+        from ..ops.tp import AgGemm, GemmAr, GemmRs
+        from ..runtime.context import EmuContext
+
+        W = a.world
+        ctx = EmuContext(W)
+        m, n, k = a.m // 2, a.n // 2, a.k          # 4096 x 4096 x 4096 by default
+        if a.case == "ag_gemm":
+            op = AgGemm(ctx, max_m=m, k=k)
+            A = [torch.randn(m // W, k, device=dev, generator=g).bfloat16() for _ in range(W)]
+            B = [(torch.randn(n, k, device=dev, generator=g) * 0.05).bfloat16() for _ in range(W)]
+            flops = 2.0 * W * m * n * k
+        else:
+            op = (GemmRs if a.case == "gemm_rs" else GemmAr)(ctx, m, n)
+            A = [torch.randn(m, k // W, device=dev, generator=g).bfloat16() for _ in range(W)]
+            B = [(torch.randn(n, k // W, device=dev, generator=g) * 0.05).bfloat16() for _ in range(W)]
+            flops = 2.0 * m * n * k
+        ms = _time(lambda: op(A, B), a.launches)
+        ctx.check_status()
+        out.update(world=W, shape=[m, n, k], ms=ms, tflops_all_ranks=flops / ms / 1e9)
     elif a.case == "quant":
         from ..ops.gemm import dequantize_blockscaled, quantize_blockscaled
 

@@ -10,6 +10,8 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
     config.addinivalue_line("markers", "multigpu: needs at least 2 CUDA devices")
+    config.addinivalue_line("markers", "slow: spawns torchrun ranks on CPU, 15-25 s each "
+                                       "(quick loop: -m 'not gpu and not slow')")
 
 
 def pytest_collection_modifyitems(config, items):

@@ -61,7 +61,7 @@ def main():
 
     @guarded("all_reduce")
     def t_all_reduce():
-        algos = ["oneshot", "twoshot"] + (["nvls"] if ctx.has_multicast else [])
+        algos = ["oneshot", "twoshot", "twoshot_push"] + (["nvls"] if ctx.has_multicast else [])
         for numel in (8, 2048, 1 << 16, (1 << 20) + 8, 1 << 24):
             x = uniform((numel,), rank)
             ref = sum(t.float() for t in gather_all(x))
@@ -84,6 +84,18 @@ def main():
         y = coll.all_reduce(ctx, xf.clone(), algo="auto")
         ctx.check_status()
         report("all_reduce/fp32", torch.allclose(y.double(), ref, atol=1e-5, rtol=1e-5))
+        # launch-shape knobs: every grid size and depth gives the same bits as the default
+        t.copy_(uniform((1 << 20,), 300 + rank))
+        keep = t.clone()
+        torch.cuda.synchronize(); dist.barrier()
+        base = coll.all_reduce(ctx, t, algo="twoshot").clone()
+        same = True
+        for algo, blocks, unroll in (("twoshot", 7, 2), ("twoshot_push", 32, 8), ("twoshot_push", 128, 1)):
+            t.copy_(keep)
+            torch.cuda.synchronize(); dist.barrier()
+            same = same and torch.equal(coll.all_reduce(ctx, t, algo=algo, blocks=blocks, unroll=unroll), base)
+            ctx.check_status()
+        report("all_reduce/launch_shapes_bit_identical", same)
 
     @guarded("all_gather")
     def t_all_gather():
@@ -118,6 +130,13 @@ def main():
         y = coll.all_to_all(ctx, x)
         ctx.check_status()
         report("all_to_all/flat", torch.equal(y, ref))
+        y = coll.all_to_all(ctx, x, push=True, unroll=8)
+        ctx.check_status()
+        report("all_to_all/flat_push_staged", torch.equal(y, ref))
+        so, _ = ctx.empty(tuple(x.shape), torch.bfloat16)
+        coll.all_to_all(ctx, x, out=so)
+        ctx.check_status()
+        report("all_to_all/flat_push_symmetric_out", torch.equal(so, ref))
         B, Sl, H, D = 1, 96, 8 * world, 128
         q = uniform((B, Sl, H, D), 50 + rank)
         full = torch.cat(gather_all(q), dim=1)
@@ -208,6 +227,21 @@ def main():
             ctx.check_status()
             err = ((y.float() - ref).abs().max() / (ref.abs().max() + 1e-6)).item()
             report(f"moe/{it}", err < 3e-2, err)
+        # routed block with a logical -> physical expert map: skew the load, rebalance, and the
+        # output for the same tokens must not change (experts moved, the function did not)
+        from commbench_b200.parallel.ep import ExpertParallelMoE
+
+        blk = ExpertParallelMoE(ctx, T, H, I, E, K, capacity_factor=4.0, seed=4)
+        logits = torch.randn(T, E, device="cuda", generator=g)
+        logits[:, :E // world] += 1.0                    # rank 0's experts are hot
+        y0 = blk(x, router_logits=logits).clone()
+        ctx.check_status()
+        info = blk.rebalance()
+        y1 = blk(x, router_logits=logits).clone()
+        ctx.check_status()
+        err = ((y1.float() - y0.float()).abs().max() / (y0.float().abs().max() + 1e-6)).item()
+        report("ep/rebalance_keeps_output", err < 1e-2 and info["moved"] > 0 and
+               info["imbalance_after"] < info["imbalance_before"], [err, info])
 
     @guarded("attention")
     def t_attention():

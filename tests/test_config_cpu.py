@@ -41,3 +41,16 @@ def test_every_field_is_documented_by_a_typed_default():
     for f in dataclasses.fields(CFG.Config):
         assert isinstance(f.default, (bool, int, float)), f.name
         assert CFG._coerce("1", type(f.default)) in (True, 1, 1.0)
+
+
+def test_expert_placement_is_balanced_and_deterministic():
+    from commbench_b200.parallel.ep import balanced_placement, imbalance
+
+    load = [100, 90, 80, 70, 1, 1, 1, 1]
+    start = list(range(8))
+    new = balanced_placement(load, 4)
+    assert sorted(new) == start and new == balanced_placement(load, 4)
+    assert imbalance(load, start, 4) > 2.0 and imbalance(load, new, 4) < 1.2
+    # every rank keeps exactly E / W slots
+    assert all(len(new[r * 2:(r + 1) * 2]) == 2 for r in range(4))
+    assert imbalance([0] * 8, start, 4) == 1.0

@@ -242,6 +242,7 @@ def test_transient_model_errors_are_retried():
         ED.call_with_retry(lambda: (_ for _ in ()).throw(ValueError("bad")), sleep=sleeps.append)
 
 
+@pytest.mark.slow
 @pytest.mark.timeout(300)
 def test_shipped_gloo_task_reference_passes_its_own_check():
     """The shipped all-reduce task: the reference file, run as a candidate on two gloo ranks."""

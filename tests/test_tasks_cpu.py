@@ -64,6 +64,7 @@ def test_skeleton_and_reference_build(task, tmp_path):
         assert r.compile_success, r.compile_output[-2000:]
 
 
+@pytest.mark.slow
 @pytest.mark.timeout(600)
 @pytest.mark.parametrize("task", CPU)
 def test_cpu_task_reference_passes_and_skeleton_does_not(task, tmp_path):

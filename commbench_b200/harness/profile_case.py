@@ -49,7 +49,9 @@ def main(argv=None) -> int:
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--launches", type=int, default=3)
     ap.add_argument("--bn", type=int, default=0,
-                    help="gemm tile selector (0 = chosen from the shape; 512 = CTA pair, 256x256)")
+                    help="gemm tile selector (0 = chosen from the shape; 512 = CTA pair, 256x256); "
+                         "the fused cases take it too (256 = one CTA per 128x256 tile: the form "
+                         "a profiler can replay, a cooperative launch without clusters)")
     a = ap.parse_args(argv)
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -97,9 +99,10 @@ def main(argv=None) -> int:
             A = [torch.randn(m, k // W, device=dev, generator=g).bfloat16() for _ in range(W)]
             B = [(torch.randn(n, k // W, device=dev, generator=g) * 0.05).bfloat16() for _ in range(W)]
             flops = 2.0 * m * n * k
-        ms = _time(lambda: op(A, B), a.launches)
+        kw = {"bn": a.bn} if a.bn else {}
+        ms = _time(lambda: op(A, B, **kw), a.launches)
         ctx.check_status()
-        out.update(world=W, shape=[m, n, k], ms=ms, tflops_all_ranks=flops / ms / 1e9)
+        out.update(world=W, shape=[m, n, k], bn=a.bn, ms=ms, tflops_all_ranks=flops / ms / 1e9)
     elif a.case == "quant":
         from ..ops.gemm import dequantize_blockscaled, quantize_blockscaled
 

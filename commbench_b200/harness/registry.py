@@ -153,7 +153,7 @@ EXAMPLE_TASK: dict = {
     "example032": "atomic_ticket_counter",
     "example022": "gloo_allreduce", "example105": "oneshot_allreduce_virtual_ranks",
     "example109": "oneshot_allreduce_virtual_ranks", "example020": "ulysses_all_to_all",
-    "example058": "ulysses_all_to_all", "example087": "weight_broadcast", "example084": "moe_agrs_dispatch",
+    "example058": "ulysses_attention_kernel", "example087": "weight_broadcast", "example084": "moe_agrs_dispatch",
     "example042": "moe_dispatch_layout", "example074": "d2d_copy_kernel", "example077": "d2d_copy_kernel",
     "example043": "nvls_all_reduce", "example048": "nvls_all_reduce", "example060": "nvls_all_reduce",
     "example045": "nvls_all_gather", "example046": "nvls_all_gather", "example059": "nvls_all_gather",

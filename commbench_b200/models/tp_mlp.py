@@ -90,12 +90,36 @@ class TPMLP:
         return y
 
     # ---------------------------------------------------------------- end to end
-    def _forward_host_pipelined(self, x_host_pinned: torch.Tensor, chunks: int) -> torch.Tensor:
-        """One rank, fused path: the host-to-device copy of the tokens is cut into row chunks on
-        a copy stream and the first GEMM of chunk i runs while chunk i+1 is still on the wire;
-        the second GEMM runs once over all rows."""
+    def _rows_forward(self, x_rows: torch.Tensor, h: torch.Tensor, y: torch.Tensor, fused: bool):
+        """The whole block on a group of local rows (W > 1): y = MLP(x_rows), with the gathered
+        intermediate in ``h`` ([W * rows, I/W])."""
+        import torch.distributed as dist
+
+        if fused:
+            self.ag(x_rows, self.w1, out=h)
+            if self.activation == "silu":
+                torch.nn.functional.silu(h, inplace=True)
+            self.rs(h, self.w2, out=y)
+            return
+        x_full = torch.empty(x_rows.shape[0] * self.world, self.hidden, dtype=x_rows.dtype,
+                             device=x_rows.device)
+        dist.all_gather_into_tensor(x_full, x_rows)
+        torch.matmul(x_full, self.w1.t(), out=h)
+        if self.activation == "silu":
+            torch.nn.functional.silu(h, inplace=True)
+        dist.reduce_scatter_tensor(y, torch.matmul(h, self.w2.t()))
+
+    def _forward_host_pipelined(self, x_host_pinned: torch.Tensor, chunks: int,
+                                fused: bool) -> torch.Tensor:
+        """The host-to-device copy of the tokens is cut into row chunks on a copy stream and the
+        work on chunk i runs while chunk i+1 is still on the wire.  One rank: the first GEMM runs
+        per chunk, the second once over all rows.  Several ranks: the whole block runs per chunk
+        (chunk c of every rank is gathered, multiplied, reduced and scattered back: exactly
+        y[c] = MLP(x[c]) for every rank).  The same schedule serves the fused kernels and the
+        unfused NCCL + cuBLAS composition."""
         n = x_host_pinned.shape[0]
         rows = n // chunks
+        W = self.world
         main = torch.cuda.current_stream()
         if self._copy_stream is None:
             self._copy_stream = torch.cuda.Stream()
@@ -108,22 +132,45 @@ class TPMLP:
                 xd[c * rows:(c + 1) * rows].copy_(x_host_pinned[c * rows:(c + 1) * rows],
                                                   non_blocking=True)
                 self._copy_events[c].record(cs)
-        h = self.h[:n]
+        h = self.h[:n * W]
+        y = self.y[:n]
         for c in range(chunks):
             main.wait_event(self._copy_events[c])
-            gemm(xd[c * rows:(c + 1) * rows], self.w1, out=h[c * rows:(c + 1) * rows])
-        if self.activation == "silu":
-            torch.nn.functional.silu(h, inplace=True)
-        y = self.y[:n]
-        gemm(h, self.w2, out=y)
+            xc = xd[c * rows:(c + 1) * rows]
+            if W == 1:
+                if fused:
+                    gemm(xc, self.w1, out=h[c * rows:(c + 1) * rows])
+                else:
+                    torch.matmul(xc, self.w1.t(), out=h[c * rows:(c + 1) * rows])
+            else:
+                self._rows_forward(xc, h[c * rows * W:(c + 1) * rows * W],
+                                   y[c * rows:(c + 1) * rows], fused)
+        if W == 1:
+            if self.activation == "silu":
+                torch.nn.functional.silu(h, inplace=True)
+            if fused:
+                gemm(h, self.w2, out=y)
+            else:
+                torch.matmul(h, self.w2.t(), out=y)
         return y
+
+    def host_chunks(self, n_local: int) -> int:
+        """Row chunks of the pipelined end-to-end path.  One rank: four (only the first GEMM is
+        cut).  Several ranks: two, as long as every launch keeps 4096 gathered rows and 1024
+        local rows - smaller launches lose more to partly filled tile waves than the overlap
+        of the copy gains."""
+        if self.world == 1:
+            return 4 if n_local % 1024 == 0 and n_local >= 8192 else 1
+        if n_local % 512 == 0 and n_local // 2 >= 1024 and (n_local // 2) * self.world >= 4096:
+            return 2
+        return 1
 
     def forward_host(self, x_host_pinned: torch.Tensor, fused: bool = True) -> float:
         """Tokens arrive in pinned host memory; returns mean(|y|) read back to the host."""
         n = x_host_pinned.shape[0]
-        chunks = 4
-        if fused and self.world == 1 and n % (chunks * 256) == 0 and n // chunks >= 1024:
-            y = self._forward_host_pipelined(x_host_pinned, chunks)
+        chunks = self.host_chunks(n)
+        if chunks > 1:
+            y = self._forward_host_pipelined(x_host_pinned, chunks, fused)
         else:
             xd = self._x_dev[:n]
             xd.copy_(x_host_pinned, non_blocking=True)

@@ -363,6 +363,20 @@ def main():
         dist.all_reduce(full)
         report("tp/row_scatter", close(y, full[rank * (T // world):(rank + 1) * (T // world)]))
         report("tp/row_replicated", close(yr, full))
+        # ---- flagship block end to end: pinned host tokens in, metric out; the chunk-pipelined
+        # schedule must give the metric of the single-shot forward, fused and unfused
+        from commbench_b200.models.tp_mlp import TPMLP
+
+        Tm = 4096 * world if world <= 4 else 1024 * world
+        mlp = TPMLP(ctx, hidden=1024, intermediate=512 * world, max_tokens=Tm, seed=9)
+        xh = (torch.randn(Tm // world, 1024, generator=torch.Generator().manual_seed(40 + rank)) * 0.5
+              ).bfloat16().pin_memory()
+        want = mlp.forward(xh.cuda()).float().abs().mean().item()
+        got_f = mlp.forward_host(xh, fused=True)
+        got_u = mlp.forward_host(xh, fused=False)
+        ctx.check_status()
+        report("tp_mlp/forward_host", abs(got_f - want) <= 2e-3 * abs(want) and
+               abs(got_u - want) <= 2e-2 * abs(want), [mlp.host_chunks(Tm // world), want, got_f, got_u])
 
     t_moe(); t_attention(); t_p2p(); t_parallel()
     t_all_reduce(); t_all_gather(); t_reduce_scatter(); t_all_to_all(); t_broadcast()

@@ -52,7 +52,22 @@ struct AgGemmParams {
   const uint32_t* a_sf_local;
   uint32_t* a_sf_full_peer[2][CB_MAX_RANKS];
   int sf_kgroups;
+  // Optional gate on the LOCAL rows: word r / src_ready_rows of `src_ready` reaches
+  // `src_ready_target` once local row r is in memory (a host-to-device copy still in flight
+  // when the kernel starts publishes its progress there).  nullptr: the rows are all there.
+  const uint32_t* src_ready;
+  uint32_t src_ready_target;
+  int src_ready_rows;
+  int block_rows;  // rows of one row block (the tile height)
 };
+
+// Waits until every row of local row block `rb` has landed (bounded; paced polls).
+__device__ __forceinline__ bool ag_src_wait(const AgGemmParams& p, int rb) {
+  if (p.src_ready == nullptr) return true;
+  const int last_row = (rb + 1) * p.block_rows - 1;
+  return wait_flag_ge_sys_paced(p.src_ready + last_row / p.src_ready_rows, p.src_ready_target,
+                                p.timeout_ns, p.status, PH_AG_ROWS, 0x4000u + rb, 500u);
+}
 
 struct AgRt {
   const AgGemmParams* p;
@@ -73,7 +88,8 @@ struct AgPolicy {
     const int local_tiles = bpr * p.g.num_n_blocks;
     int i;
     if (tile < local_tiles) {
-      raster_tile(tile, bpr, p.g.num_n_blocks, bpr, &i, n);
+      // Rows still arriving from the host: row-block-major, so that the math follows the copy.
+      raster_tile(tile, bpr, p.g.num_n_blocks, p.src_ready != nullptr ? 1 : bpr, &i, n);
       *m = p.rank * bpr + i;
     } else {
       raster_tile(tile - local_tiles, (p.world - 1) * bpr, p.g.num_n_blocks, p.world - 1, &i, n);
@@ -95,7 +111,15 @@ struct AgPolicy {
   }
   __device__ static bool wait_a_ready(const AgRt& r, int m_blk, volatile int* abort_flag) {
     const AgGemmParams& p = *r.p;
-    if (is_local(p, m_blk)) return true;
+    if (is_local(p, m_blk)) {
+      if (p.src_ready == nullptr) return true;
+      if (!ag_src_wait(p, m_blk - p.rank * p.blocks_per_rank)) {
+        *abort_flag = 1;
+        return false;
+      }
+      fence_proxy_async();  // written by a copy engine; read by our TMA loads
+      return true;
+    }
     const uint32_t* f = p.flags_local + r.parity * kAgMaxRowBlocks + m_blk;
     if (!wait_flag_ge_sys(f, static_cast<uint32_t>(p.parts), p.timeout_ns, p.status, PH_AG_ROWS,
                           m_blk)) {
@@ -142,6 +166,11 @@ __device__ __forceinline__ void ag_comm_cta(const AgGemmParams& p, uint32_t pari
   for (int item = comm_cta; item < p.blocks_per_rank * p.parts; item += p.num_comm_ctas) {
     const int rb = item / p.parts;
     const int part = item % p.parts;
+    if (p.src_ready != nullptr) {
+      // A time-out is recorded in the status word; the CTA carries on (bounded) either way.
+      if (threadIdx.x == 0) (void)ag_src_wait(p, rb);
+      __syncthreads();
+    }
     unsigned long long v_begin = per_part * part, v_end = v_begin + per_part;
     if (v_begin > rb_vecs) v_begin = rb_vecs;
     if (v_end > rb_vecs) v_end = rb_vecs;
@@ -296,6 +325,11 @@ struct CbAgGemmDesc {
   const void* a_sf_local;                 // [ceil(K/512)][M / world]
   void* a_sf_full_peer[2][CB_MAX_RANKS];  // [ceil(K/512)][M] per parity and rank
   const void* b_sf;                       // [ceil(K/512)][N]
+  // Optional: uint32 words that reach `src_ready_target` as the local rows land, one word per
+  // `src_ready_rows` rows (nullptr: a_local is complete when the kernel starts).
+  const void* src_ready;
+  unsigned int src_ready_target;
+  int src_ready_rows;
 };
 
 static int build_ag_params(const CbAgGemmDesc& d, AgGemmParams* p) {
@@ -374,6 +408,14 @@ static int build_ag_params(const CbAgGemmDesc& d, AgGemmParams* p) {
   p->seq.done_ctas = static_cast<uint32_t*>(d.seq) + 1;
   p->status = static_cast<uint32_t*>(d.status);
   p->timeout_ns = d.timeout_ns;
+  p->block_rows = bm;
+  p->src_ready = static_cast<const uint32_t*>(d.src_ready);
+  p->src_ready_target = d.src_ready_target;
+  p->src_ready_rows = d.src_ready_rows > 0 ? d.src_ready_rows : bm;
+  if (d.src_ready != nullptr && d.src_ready_rows < 1) {
+    set_last_error("ag_gemm: src_ready needs src_ready_rows >= 1");
+    return -1;
+  }
   p->a_sf_local = mx ? static_cast<const uint32_t*>(d.a_sf_local) : nullptr;
   for (int par = 0; par < 2; ++par)
     for (int r = 0; r < CB_MAX_RANKS; ++r)

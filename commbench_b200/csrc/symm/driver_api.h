@@ -35,6 +35,7 @@ struct DriverApi {
                                         CUmulticastGranularity_flags);
   CUresult (*cuDeviceGet)(CUdevice*, int);
   CUresult (*cuDeviceGetAttribute)(int*, CUdevice_attribute, CUdevice);
+  CUresult (*cuStreamWriteValue32)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
   CUresult (*cuTensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                      const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                      const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,

@@ -70,6 +70,7 @@ const DriverApi& driver_api() {
     CB_GET(cuDeviceGet);
     CB_GET(cuDeviceGetAttribute);
     CB_GET(cuTensorMapEncodeTiled);
+    CB_GET(cuStreamWriteValue32);
 #undef CB_GET
     api.ok = all;
   });
@@ -128,6 +129,25 @@ using namespace cb;
 extern "C" {
 
 const char* cb_last_error() { return g_last_error.c_str(); }
+
+// Stream memory operation: `value` is written to the 4-byte aligned device word `dev_ptr` when
+// the stream reaches this point - by the copy engine's front end, without a kernel, so it
+// completes even while a persistent kernel occupies every SM.  Used to publish "the rows copied
+// so far have landed" to a kernel that is already running.
+int cb_stream_write_u32(void* stream, void* dev_ptr, unsigned int value) {
+  const DriverApi& d = driver_api();
+  if (!d.ok) {
+    set_last_error("driver API unavailable:" + d.why);
+    return -1;
+  }
+  CUresult r = d.cuStreamWriteValue32(static_cast<CUstream>(stream),
+                                      reinterpret_cast<CUdeviceptr>(dev_ptr), value, 0);
+  if (r != CUDA_SUCCESS) {
+    set_last_error(cu_err("cuStreamWriteValue32", r));
+    return -1;
+  }
+  return 0;
+}
 
 // 1 when this device supports NVSwitch multicast objects, 0 when not, <0 on error.
 int cb_symm_multicast_supported(int device) {

@@ -21,7 +21,7 @@ from __future__ import annotations
 import torch
 
 from ..ops.gemm import gemm
-from ..ops.tp import AgGemm, GemmRs
+from ..ops.tp import AgGemm, GemmRs, stream_write_u32
 
 
 class TPMLP:
@@ -51,6 +51,8 @@ class TPMLP:
         self.launches_per_step = 2
         self._copy_stream = None
         self._copy_events = None
+        self._ready = None          # per-256-row "has landed" words of the gated end-to-end path
+        self._ready_seq = 0
 
     # ---------------------------------------------------------------- fused path
     def forward(self, x_local: torch.Tensor) -> torch.Tensor:
@@ -154,6 +156,40 @@ class TPMLP:
                 torch.matmul(h, self.w2.t(), out=y)
         return y
 
+    GATE_ROWS = 256
+
+    def _forward_host_gated(self, x_host_pinned: torch.Tensor) -> torch.Tensor:
+        """Several ranks, fused path: the AG->GEMM kernel is launched at once and consumes the
+        local rows as the host-to-device copy delivers them.  The copy runs on its own stream in
+        256-row pieces, each followed by a stream memory operation that publishes "these rows have
+        landed"; the kernel's communication CTAs push, and its tensor-core CTAs multiply, a
+        row block as soon as its word is set.  One launch per GEMM, whatever the piece count."""
+        n = x_host_pinned.shape[0]
+        g = self.GATE_ROWS
+        main = torch.cuda.current_stream()
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream()
+            self._copy_events = [torch.cuda.Event() for _ in range(16)]
+        if self._ready is None:
+            self._ready = torch.zeros(self.max_tokens // self.world // g + 1, dtype=torch.int32,
+                                      device=self._x_dev.device)
+            torch.cuda.synchronize(self._x_dev.device)
+        cs = self._copy_stream
+        cs.wait_stream(main)           # the previous step's kernels are done with the staging rows
+        self._ready_seq += 1
+        xd = self._x_dev[:n]
+        with torch.cuda.stream(cs):
+            for c in range(n // g):
+                xd[c * g:(c + 1) * g].copy_(x_host_pinned[c * g:(c + 1) * g], non_blocking=True)
+                stream_write_u32(self._ready[c:c + 1], self._ready_seq, cs)
+        h = self.h[:n * self.world]
+        y = self.y[:n]
+        self.ag(xd, self.w1, out=h, src_ready=(self._ready, self._ready_seq, g))
+        if self.activation == "silu":
+            torch.nn.functional.silu(h, inplace=True)
+        self.rs(h, self.w2, out=y)
+        return y
+
     def host_chunks(self, n_local: int) -> int:
         """Row chunks of the pipelined end-to-end path.  One rank: four (only the first GEMM is
         cut).  Several ranks: two, as long as every launch keeps 4096 gathered rows and 1024
@@ -169,7 +205,9 @@ class TPMLP:
         """Tokens arrive in pinned host memory; returns mean(|y|) read back to the host."""
         n = x_host_pinned.shape[0]
         chunks = self.host_chunks(n)
-        if chunks > 1:
+        if fused and self.world > 1 and n % self.GATE_ROWS == 0 and n >= 2 * self.GATE_ROWS:
+            y = self._forward_host_gated(x_host_pinned)
+        elif chunks > 1:
             y = self._forward_host_pipelined(x_host_pinned, chunks, fused)
         else:
             xd = self._x_dev[:n]

@@ -40,6 +40,7 @@ class _AgDesc(C.Structure):
         ("flags_peer", _P8), ("flags_mc", C.c_void_p),
         ("seq", C.c_void_p), ("status", C.c_void_p), ("timeout_ns", C.c_ulonglong),
         ("a_sf_local", C.c_void_p), ("a_sf_full_peer", _P8 * 2), ("b_sf", C.c_void_p),
+        ("src_ready", C.c_void_p), ("src_ready_target", C.c_uint), ("src_ready_rows", C.c_int),
     ]
 
 
@@ -212,11 +213,17 @@ class AgGemm(_FusedBase):
     @traced("cb200.ag_gemm")
     def __call__(self, a_local, b, out=None, alpha: float = 1.0, bn: int | None = None,
                  comm_ctas: int | None = None, parts: int | None = None, use_mc: bool = True,
-                 stream=None, a_sf=None, b_sf=None):
+                 stream=None, a_sf=None, b_sf=None, src_ready=None):
         """``a_sf`` / ``b_sf``: packed power-of-two block scales of fp8 operands
         (``ops.gemm.quantize_blockscaled_pow2``; ``a_sf`` of the LOCAL rows): the tensor cores
         apply them (``bn`` is then 192, CTA pairs on 256 x 192 tiles) and the scale words of a
-        row block travel to the peers with its rows."""
+        row block travel to the peers with its rows.
+
+        ``src_ready = (words, target, rows_per_word)``: the local rows may still be arriving
+        (a host-to-device copy in flight on another stream) when the kernel starts; int32 word
+        ``r // rows_per_word`` of the CUDA tensor ``words`` reaches ``target`` once local row r
+        has landed (:func:`stream_write_u32` after each chunk of the copy).  The kernel pushes
+        and multiplies each row block as soon as its rows are there (real ranks only)."""
         cfg = get_config()
         auto_comm = comm_ctas is None
         if comm_ctas is None:
@@ -262,12 +269,30 @@ class AgGemm(_FusedBase):
                 out = torch.empty((M, Nn), dtype=torch.bfloat16, device=a0.device)
             descs = (_AgDesc * 1)(self._desc(self.ctx.rank, a_local, b, out, M, Nn, K, alpha, bn,
                                              comm_ctas, parts, use_mc, a_sf, b_sf))
+            if src_ready is not None:
+                words, target, rows_per_word = src_ready
+                if words.dtype != torch.int32 or not words.is_cuda or \
+                        words.numel() * rows_per_word < Ml:
+                    raise CommError("src_ready: int32 CUDA words covering every local row")
+                descs[0].src_ready = words.data_ptr()
+                descs[0].src_ready_target = int(target) & 0xffffffff
+                descs[0].src_ready_rows = int(rows_per_word)
             rc = self.lib.cb_ag_gemm(descs, 1, None, N.stream_ptr(stream))
             result = out
         if rc != 0:
             raise CommError(f"ag_gemm failed: {N.last_error()}")
         self.calls += 1
         return result
+
+
+def stream_write_u32(word: torch.Tensor, value: int, stream=None) -> None:
+    """Writes ``value`` into the one-element int32 CUDA tensor ``word`` when ``stream`` (default:
+    the current stream) reaches this point - a stream memory operation, no kernel, so it
+    completes even while a persistent kernel occupies every SM."""
+    lib = N.load()
+    if lib.cb_stream_write_u32(N.stream_ptr(stream), C.c_void_p(word.data_ptr()),
+                               C.c_uint(int(value) & 0xffffffff)) != 0:
+        raise CommError(f"stream_write_u32 failed: {N.last_error()}")
 
 
 class GemmRs(_FusedBase):

@@ -119,3 +119,44 @@ def test_tp_mlp_end_to_end_pipelined_matches_single_shot(native_lib):
     assert abs(got_u - want) <= 2e-2 * abs(want)
     ctx.check_status()
     ctx.close()
+
+
+@pytest.mark.parametrize("kernel_first", [False, True])
+def test_ag_gemm_consumes_rows_as_a_host_copy_delivers_them(native_lib, kernel_first):
+    """The AG->GEMM kernel gated on per-256-row "has landed" words that a copy stream publishes
+    with stream memory operations after each piece of a host-to-device copy.  With
+    ``kernel_first`` the kernel is already running (and waiting, bounded) when the copies are
+    enqueued: it must pick the rows up as they arrive and give the exact product."""
+    from commbench_b200.ops.tp import AgGemm, stream_write_u32
+    from commbench_b200.runtime.context import CommContext
+
+    ctx = CommContext(heap_bytes=128 << 20)
+    M, K, Nn, g = 2048, 1024, 768, 256
+    op = AgGemm(ctx, max_m=M, k=K)
+    gen = torch.Generator().manual_seed(5)
+    a_host = (torch.randn(M, K, generator=gen) * 0.25).bfloat16().pin_memory()
+    b = _rand((Nn, K), 6)
+    a_dev = torch.zeros(M, K, device="cuda", dtype=torch.bfloat16)
+    ready = torch.zeros(M // g, device="cuda", dtype=torch.int32)
+    side = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    for seq in (1, 2):                                   # a second step reuses buffers and words
+        a_dev.zero_()
+        torch.cuda.synchronize()
+
+        def copies():
+            with torch.cuda.stream(side):
+                for c in range(M // g):
+                    a_dev[c * g:(c + 1) * g].copy_(a_host[c * g:(c + 1) * g], non_blocking=True)
+                    stream_write_u32(ready[c:c + 1], seq, side)
+
+        if not kernel_first:
+            copies()
+        out = op(a_dev, b, src_ready=(ready, seq, g))
+        if kernel_first:
+            copies()
+        torch.cuda.synchronize()
+        ctx.check_status()
+        ref = a_host.cuda().float() @ b.float().t()
+        assert ((out.float() - ref).abs().max() / ref.abs().max()).item() < 2e-2
+    ctx.close()

@@ -40,8 +40,10 @@ class TPMLP:
         self.w1 = (torch.randn(self.i_local, hidden, device=dev, generator=g) * 0.02).bfloat16()
         self.w2 = (torch.randn(hidden, self.i_local, device=dev, generator=g) * 0.02).bfloat16()
         self.activation = activation
+        # One rank: the all-gather half of AG->GEMM is empty, but the kernel's gate on rows that
+        # are still arriving from the host is what the end-to-end path wants.
+        self.ag = AgGemm(ctx, max_m=max_tokens, k=hidden)
         if self.world > 1:
-            self.ag = AgGemm(ctx, max_m=max_tokens, k=hidden)
             self.rs = GemmRs(ctx, max_m=max_tokens, max_n=hidden)
         self.h = torch.empty(max_tokens, self.i_local, dtype=torch.bfloat16, device=dev)
         self.y = torch.empty(max_tokens // self.world, hidden, dtype=torch.bfloat16, device=dev)
@@ -159,7 +161,7 @@ class TPMLP:
     GATE_ROWS = 256
 
     def _forward_host_gated(self, x_host_pinned: torch.Tensor) -> torch.Tensor:
-        """Several ranks, fused path: the AG->GEMM kernel is launched at once and consumes the
+        """Fused path: the AG->GEMM kernel is launched at once and consumes the
         local rows as the host-to-device copy delivers them.  The copy runs on its own stream in
         256-row pieces, each followed by a stream memory operation that publishes "these rows have
         landed"; the kernel's communication CTAs push, and its tensor-core CTAs multiply, a
@@ -187,7 +189,10 @@ class TPMLP:
         self.ag(xd, self.w1, out=h, src_ready=(self._ready, self._ready_seq, g))
         if self.activation == "silu":
             torch.nn.functional.silu(h, inplace=True)
-        self.rs(h, self.w2, out=y)
+        if self.world == 1:
+            gemm(h, self.w2, out=y)
+        else:
+            self.rs(h, self.w2, out=y)
         return y
 
     def host_chunks(self, n_local: int) -> int:
@@ -205,7 +210,7 @@ class TPMLP:
         """Tokens arrive in pinned host memory; returns mean(|y|) read back to the host."""
         n = x_host_pinned.shape[0]
         chunks = self.host_chunks(n)
-        if fused and self.world > 1 and n % self.GATE_ROWS == 0 and n >= 2 * self.GATE_ROWS:
+        if fused and n % self.GATE_ROWS == 0 and n >= 2 * self.GATE_ROWS:
             y = self._forward_host_gated(x_host_pinned)
         elif chunks > 1:
             y = self._forward_host_pipelined(x_host_pinned, chunks, fused)

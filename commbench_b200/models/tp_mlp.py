@@ -163,27 +163,30 @@ class TPMLP:
     def _forward_host_gated(self, x_host_pinned: torch.Tensor) -> torch.Tensor:
         """Fused path: the AG->GEMM kernel is launched at once and consumes the
         local rows as the host-to-device copy delivers them.  The copy runs on its own stream in
-        256-row pieces, each followed by a stream memory operation that publishes "these rows have
-        landed"; the kernel's communication CTAs push, and its tensor-core CTAs multiply, a
-        row block as soon as its word is set.  One launch per GEMM, whatever the piece count."""
+        pieces of 256 rows or more (16 pieces at most), each followed by a stream memory operation
+        that publishes "these rows have landed"; the kernel's communication CTAs push, and its
+        tensor-core CTAs multiply, a row block as soon as its word is set.  One launch per GEMM,
+        whatever the piece count.  The kernels are enqueued BEFORE the copies, so the host's time
+        to enqueue the pieces overlaps the first pieces' transfer."""
         n = x_host_pinned.shape[0]
         g = self.GATE_ROWS
+        while n // g > 16 and n % (2 * g) == 0:
+            g *= 2
         main = torch.cuda.current_stream()
         if self._copy_stream is None:
             self._copy_stream = torch.cuda.Stream()
             self._copy_events = [torch.cuda.Event() for _ in range(16)]
         if self._ready is None:
-            self._ready = torch.zeros(self.max_tokens // self.world // g + 1, dtype=torch.int32,
-                                      device=self._x_dev.device)
+            self._ready = torch.zeros(self.max_tokens // self.world // self.GATE_ROWS + 1,
+                                      dtype=torch.int32, device=self._x_dev.device)
             torch.cuda.synchronize(self._x_dev.device)
         cs = self._copy_stream
-        cs.wait_stream(main)           # the previous step's kernels are done with the staging rows
+        # The previous step's kernels are done with the staging rows before they are overwritten;
+        # the copy stream must NOT wait for the kernels enqueued below, which wait for it.
+        self._copy_events[0].record(main)
+        cs.wait_event(self._copy_events[0])
         self._ready_seq += 1
         xd = self._x_dev[:n]
-        with torch.cuda.stream(cs):
-            for c in range(n // g):
-                xd[c * g:(c + 1) * g].copy_(x_host_pinned[c * g:(c + 1) * g], non_blocking=True)
-                stream_write_u32(self._ready[c:c + 1], self._ready_seq, cs)
         h = self.h[:n * self.world]
         y = self.y[:n]
         self.ag(xd, self.w1, out=h, src_ready=(self._ready, self._ready_seq, g))
@@ -193,6 +196,10 @@ class TPMLP:
             gemm(h, self.w2, out=y)
         else:
             self.rs(h, self.w2, out=y)
+        with torch.cuda.stream(cs):
+            for c in range(n // g):
+                xd[c * g:(c + 1) * g].copy_(x_host_pinned[c * g:(c + 1) * g], non_blocking=True)
+                stream_write_u32(self._ready[c:c + 1], self._ready_seq, cs)
         return y
 
     def host_chunks(self, n_local: int) -> int:

@@ -59,14 +59,21 @@ struct AgGemmParams {
   uint32_t src_ready_target;
   int src_ready_rows;
   int block_rows;  // rows of one row block (the tile height)
+  int gate_group;  // row blocks per raster panel of the local tiles while gated
+  unsigned int gate_poll_ns;
 };
 
-// Waits until every row of local row block `rb` has landed (bounded; paced polls).
+// Waits until every row of local row block `rb` has landed (bounded).  Polls are 20 us apart:
+// with one lane of each of 148 CTAs polling the word every 500 ns, the stream memory operations
+// that write those words - and the host-to-device copy queued behind them - crawled (a 2.6 ms
+// copy took 14-17 ms); at 4 us it still took 5-8 ms; at 20 us the copy runs at full speed and a
+// gated 8192 x 28672 x 8192 GEMM ends 0.8 ms after its 2.6 ms copy (5.5 ms back to back).  A piece
+// of the copy takes 80 us or more, so slow polls cost little.
 __device__ __forceinline__ bool ag_src_wait(const AgGemmParams& p, int rb) {
   if (p.src_ready == nullptr) return true;
   const int last_row = (rb + 1) * p.block_rows - 1;
   return wait_flag_ge_sys_paced(p.src_ready + last_row / p.src_ready_rows, p.src_ready_target,
-                                p.timeout_ns, p.status, PH_AG_ROWS, 0x4000u + rb, 500u);
+                                p.timeout_ns, p.status, PH_AG_ROWS, 0x4000u + rb, p.gate_poll_ns);
 }
 
 struct AgRt {
@@ -88,8 +95,8 @@ struct AgPolicy {
     const int local_tiles = bpr * p.g.num_n_blocks;
     int i;
     if (tile < local_tiles) {
-      // Rows still arriving from the host: row-block-major, so that the math follows the copy.
-      raster_tile(tile, bpr, p.g.num_n_blocks, p.src_ready != nullptr ? 1 : bpr, &i, n);
+      // Rows still arriving from the host: narrow panels, so that the math follows the copy.
+      raster_tile(tile, bpr, p.g.num_n_blocks, p.src_ready != nullptr ? p.gate_group : bpr, &i, n);
       *m = p.rank * bpr + i;
     } else {
       raster_tile(tile - local_tiles, (p.world - 1) * bpr, p.g.num_n_blocks, p.world - 1, &i, n);
@@ -332,6 +339,8 @@ struct CbAgGemmDesc {
   int src_ready_rows;
 };
 
+static unsigned int g_gate_poll_ns = 20000u;
+
 static int build_ag_params(const CbAgGemmDesc& d, AgGemmParams* p) {
   const int esz = d.fp8 ? 1 : 2;
   const int BK = d.fp8 ? 128 : 64;
@@ -409,6 +418,17 @@ static int build_ag_params(const CbAgGemmDesc& d, AgGemmParams* p) {
   p->status = static_cast<uint32_t*>(d.status);
   p->timeout_ns = d.timeout_ns;
   p->block_rows = bm;
+  {
+    // Every panel of local row blocks streams all of B once.  B that fits in L2 (126 MB) can be
+    // walked one row block at a time; a larger B gets wider panels so that its re-reads stay a
+    // small fraction of the HBM bandwidth (one row block at a time and a 470 MB B was 15 GB of
+    // reads per GEMM).
+    const double b_mb = static_cast<double>(d.N) * d.K * esz / (1 << 20);
+    int gg = b_mb <= 96.0 ? 1 : (b_mb <= 256.0 ? 2 : 4);
+    if (gg > p->blocks_per_rank) gg = p->blocks_per_rank;
+    p->gate_group = gg;
+  }
+  p->gate_poll_ns = g_gate_poll_ns;
   p->src_ready = static_cast<const uint32_t*>(d.src_ready);
   p->src_ready_target = d.src_ready_target;
   p->src_ready_rows = d.src_ready_rows > 0 ? d.src_ready_rows : bm;
@@ -433,6 +453,9 @@ static int build_ag_params(const CbAgGemmDesc& d, AgGemmParams* p) {
   }
   return 0;
 }
+
+// Nanoseconds between polls of the local-rows gate (tuning; default 20000).
+void cb_ag_gemm_set_gate_poll_ns(unsigned int ns) { g_gate_poll_ns = ns; }
 
 int cb_sizeof_ag_gemm_params() { return static_cast<int>(sizeof(AgGemmParams)); }
 

@@ -377,6 +377,10 @@ def main():
         ctx.check_status()
         report("tp_mlp/forward_host", abs(got_f - want) <= 2e-3 * abs(want) and
                abs(got_u - want) <= 2e-2 * abs(want), [mlp.host_chunks(Tm // world), want, got_f, got_u])
+        mlp.gate_host_copy = True      # AG->GEMM launched while the tokens are still on the wire
+        got_g = [mlp.forward_host(xh, fused=True) for _ in range(3)]
+        ctx.check_status()
+        report("tp_mlp/forward_host_gated", all(abs(g - want) <= 2e-3 * abs(want) for g in got_g), got_g)
 
     t_moe(); t_attention(); t_p2p(); t_parallel()
     t_all_reduce(); t_all_gather(); t_reduce_scatter(); t_all_to_all(); t_broadcast()

@@ -27,6 +27,7 @@ class Config:
     # --- fused GEMMs -------------------------------------------------------
     ag_gemm_comm_ctas: int = 8                  # CTAs reserved for pushing the local A shard
     gemm_ar_oneshot_max_m: int = 0              # rows at or below use the one-shot epilogue (0: never)
+    gemm_ar_split_max_world: int = 4            # up to this many ranks "auto" runs GEMM + all-reduce as two launches
     fused_poll_ns: int = 300                    # pause between polls of a peer-written flag
     # --- attention -------------------------------------------------------
     attn_impl: int = 4                          # flash-attention kernel: 4 (P kept in TMEM) or 1

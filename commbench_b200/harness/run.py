@@ -404,9 +404,11 @@ def main(argv=None) -> int:
             ar = GemmAr(ctx, 1024, Nd)
         for Md in (16, 128, 1024):
             a3, b3 = rnd((Md, Kd), 400 + rank, 1.0), rnd((Nd, Kd), 500 + rank)
-            for variant in (("oneshot", True), ("twoshot", False), ("auto", None)) if world > 1 \
-                    else (("local", None),):
-                if world > 1:
+            for variant in (("oneshot", True), ("twoshot", False), ("split", "split"),
+                            ("auto", None)) if world > 1 else (("local", None),):
+                if world > 1 and variant[0] == "split":
+                    ours = lambda: ar(a3, b3, mode="split")
+                elif world > 1:
                     ours = lambda v=variant[1]: ar(a3, b3, oneshot=v)
                     theirs = lambda: base.gemm_ar(a3, b3)
                 else:

@@ -365,7 +365,14 @@ class GemmRs(_FusedBase):
 
 
 class GemmAr(_FusedBase):
-    """``out[M, N] = all_reduce(A[M, K_local] @ B[N, K_local].T)`` in one kernel."""
+    """``out[M, N] = all_reduce(A[M, K_local] @ B[N, K_local].T)``.
+
+    ``mode="fused"``: one kernel (two-shot or one-shot epilogue).  ``mode="split"``: this
+    package's GEMM into a symmetric buffer followed by its in-place all-reduce - two launches, no
+    library kernel.  ``mode=None`` picks: measured on B200, the fused kernel wins on 8 ranks
+    (1.1-1.5x cuBLAS + NCCL at M = 16 ... 1024) but on 2 and 4 ranks its three NVLink hops are
+    not hidden behind so little math (0.55-0.98x), while the two tuned launches are ahead of
+    the library pair there; so up to ``gemm_ar_split_max_world`` ranks "auto" means split."""
 
     def __init__(self, ctx, max_m: int, max_n: int):
         super().__init__(ctx)
@@ -378,7 +385,25 @@ class GemmAr(_FusedBase):
         self.flags = _Sym(ctx, self.lib.cb_gemm_ar_flag_words() * 4, zero=True)
         self.trace = None
         self.poll_ns = get_config().fused_poll_ns
+        self._split_calls = 0
         self._sync_init()
+
+    def _split(self, a, b, out, alpha, stream):
+        """GEMM into one of the two symmetric result buffers, all-reduce in place."""
+        from . import collectives as coll
+        from .gemm import gemm
+
+        M, Nn = a.shape[0], b.shape[0]
+        buf = self.result[self._split_calls & 1].tensors[0]
+        view = buf[: M * Nn * 2].view(torch.bfloat16).view(M, Nn)
+        self._split_calls += 1
+        gemm(a, b, out=view, alpha=alpha, stream=stream)
+        coll.all_reduce(self.ctx, view, stream=stream)
+        if out is None:
+            return view
+        with torch.cuda.stream(stream) if stream is not None else _nullctx():
+            out.copy_(view)
+        return out
 
     def _desc(self, r, a, b, out, M, Nn, K, alpha, bn, fp8, oneshot) -> _ArDesc:
         d = _ArDesc()
@@ -417,7 +442,7 @@ class GemmAr(_FusedBase):
 
     @traced("cb200.gemm_ar")
     def __call__(self, a, b, out=None, alpha: float = 1.0, bn: int | None = None,
-                 oneshot: bool | None = None, stream=None):
+                 oneshot: bool | None = None, stream=None, mode: str | None = None):
         a0, b0 = (a[0], b[0]) if self.emu else (a, b)
         M, K = a0.shape
         Nn = b0.shape[0]
@@ -425,6 +450,15 @@ class GemmAr(_FusedBase):
             raise CommError(f"GemmAr built for M<={self.max_m}, N<={self.max_n}")
         fp8 = a0.dtype == torch.float8_e4m3fn
         cfg = get_config()
+        if mode is None:
+            mode = "split" if (not self.emu and oneshot is None and bn is None and
+                               1 < self.world <= cfg.gemm_ar_split_max_world) else "fused"
+        if mode == "split":
+            if self.emu:
+                raise CommError("GemmAr mode='split' runs on real ranks")
+            return self._split(a, b, out, alpha, stream)
+        if mode != "fused":
+            raise CommError(f"unknown GemmAr mode {mode!r}")
         if oneshot is None:
             # One-shot sends every partial tile to every rank (W times the traffic) and has one
             # polling CTA per tile.  Measured on 8 GPUs it loses at every M (116 us against 39 us

@@ -208,6 +208,13 @@ def main():
                     o = op(a, b, oneshot=oneshot)
                     ctx.check_status()
                     report(f"gemm_ar/M{M}/oneshot{int(oneshot)}/{it}", close(o, part))
+            for it in range(3):             # GEMM + in-place all-reduce as two launches
+                o = op(a, b, mode="split")
+                ctx.check_status()
+                report(f"gemm_ar/M{M}/split/{it}", close(o, part))
+            keep = op(a, b).clone()         # "auto": whichever the world size selects
+            ctx.check_status()
+            report(f"gemm_ar/M{M}/auto", close(keep, part))
 
     @guarded("moe")
     def t_moe():

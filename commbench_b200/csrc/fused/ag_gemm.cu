@@ -88,7 +88,9 @@ struct AgPolicy {
   }
   // Processing order: this rank's own row blocks first (all column blocks), then, for
   // rb = 0, 1, ..., row block rb of every peer (the order the pushes arrive in).  The
-  // remote part is rasterised in panels of W-1 row blocks, i.e. one arrival wave each.
+  // remote part is rasterised in panels of W-1 row blocks, i.e. one arrival wave each - but
+  // never fewer than four: every panel streams all of B once, and with two ranks a one-block
+  // panel re-read a 235 MB B sixteen times per call.
   __device__ static void tile_coord(const AgRt& r, int tile, int* m, int* n) {
     const AgGemmParams& p = *r.p;
     const int bpr = p.blocks_per_rank;
@@ -99,7 +101,8 @@ struct AgPolicy {
       raster_tile(tile, bpr, p.g.num_n_blocks, p.src_ready != nullptr ? p.gate_group : bpr, &i, n);
       *m = p.rank * bpr + i;
     } else {
-      raster_tile(tile - local_tiles, (p.world - 1) * bpr, p.g.num_n_blocks, p.world - 1, &i, n);
+      raster_tile(tile - local_tiles, (p.world - 1) * bpr, p.g.num_n_blocks,
+                  p.world - 1 < 4 ? 4 : p.world - 1, &i, n);
       const int rb = i / (p.world - 1);
       const int peer = (p.rank + 1 + i % (p.world - 1)) % p.world;
       *m = peer * bpr + rb;

@@ -13,6 +13,7 @@
 //   datasets/example072_GPU_barrier_within_CTA/nv/empty_gpu_barrier_within_cta.cu:44-84
 //   datasets/example094_TMA_bulk_copy_gmem_to_smem/nv/empty_tma_bulk_copy.cu:28-97
 //   datasets/example010_list_gpu_attributes/nv/empty_list_gpu_attributes.cpp:17-52
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -185,6 +186,44 @@ __global__ void tma_stream_kernel(const uint8_t* __restrict__ src, size_t src_by
 
 using namespace cb;
 
+// mean(|x|) of a bf16 tensor in one pass (the metric the flagship step reads back): 16-byte
+// loads, fp32 partial sums per thread, warp shuffles, one atomicAdd per block; the last block
+// to finish writes sum / n and re-arms the two scratch words for the next call.
+__global__ void __launch_bounds__(256)
+    abs_mean_bf16_kernel(const uint4* __restrict__ x, long long nvec, long long n, float* out,
+                         float* scratch_sum, unsigned int* scratch_count) {
+  float acc = 0.f;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < nvec; i += 256ll * gridDim.x) {
+    const uint4 v = x[i];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h[k]);
+      acc += fabsf(f.x) + fabsf(f.y);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  __shared__ float warp_sum[8];
+  __shared__ bool last;
+  if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float b = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) b += warp_sum[w];
+    atomicAdd(scratch_sum, b);
+    __threadfence();
+    last = atomicAdd(scratch_count, 1u) == gridDim.x - 1;
+    if (last) {
+      __threadfence();
+      const float total = atomicExch(scratch_sum, 0.f);
+      *out = total / static_cast<float>(n);
+      *scratch_count = 0u;
+    }
+  }
+}
+
 extern "C" {
 
 // width in {4, 8, 16} bytes.  dst may be local, peer-mapped or mapped host memory.
@@ -287,6 +326,29 @@ int cb_probe_attributes_json(int device, char* buf, int buflen) {
       p.unifiedAddressing, p.canMapHostMemory, p.ECCEnabled, p.pciDomainID, p.pciBusID,
       p.pciDeviceID);
   return n < buflen ? n : -1;
+}
+
+
+// out[0] = mean(|x[0..n)|) for bf16 x (16-byte aligned, n % 8 == 0).  `scratch` = two zeroed
+// 4-byte words that the kernel leaves zeroed.  One launch.
+int cb_abs_mean_bf16(const void* x, long long n, float* out, void* scratch, void* stream) {
+  if (n <= 0 || (n % 8) != 0 || (reinterpret_cast<uintptr_t>(x) & 15u) != 0 || out == nullptr ||
+      scratch == nullptr) {
+    set_last_error("cb_abs_mean_bf16: n > 0, n % 8 == 0, 16-byte aligned input, out and scratch");
+    return -1;
+  }
+  const long long nvec = n / 8;
+  long long blocks = (nvec + 255) / 256;
+  if (blocks > 592) blocks = 592;
+  abs_mean_bf16_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), nvec, n, out, static_cast<float*>(scratch),
+      static_cast<unsigned int*>(scratch) + 1);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_last_error(std::string("abs_mean launch: ") + cudaGetErrorString(e));
+    return -1;
+  }
+  return 0;
 }
 
 }  // extern "C"

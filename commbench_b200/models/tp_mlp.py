@@ -22,6 +22,7 @@ import torch
 
 from ..ops.gemm import gemm
 from ..ops.tp import AgGemm, GemmRs, stream_write_u32
+from ..ops.util import abs_mean
 
 
 class TPMLP:
@@ -229,8 +230,8 @@ class TPMLP:
             xd = self._x_dev[:n]
             xd.copy_(x_host_pinned, non_blocking=True)
             y = self.forward(xd) if fused else self.forward_unfused(xd)
-        m = y.float().abs().mean()
-        self._metric_host.copy_(m.reshape(1), non_blocking=True)
+        m = abs_mean(y)                 # one pass over y, one launch
+        self._metric_host.copy_(m, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return float(self._metric_host[0])
 

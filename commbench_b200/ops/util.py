@@ -143,6 +143,32 @@ class ShmBroadcast:
 
 
 # ------------------------------------------------------------------------ probes
+_ABS_MEAN_SCRATCH: dict = {}
+
+
+def abs_mean(x: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """``mean(|x|)`` of a bf16 CUDA tensor as a one-element fp32 tensor, in ONE pass over ``x``
+    (``x.float().abs().mean()`` writes and re-reads two fp32 copies).  Falls back to that
+    expression for other dtypes, unaligned or non-contiguous inputs."""
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and
+            x.numel() % 8 == 0 and x.data_ptr() % 16 == 0 and x.numel() > 0):
+        r = x.float().abs().mean().reshape(1)
+        return r if out is None else out.copy_(r)
+    lib = N.load()
+    key = (x.device.index, (stream or torch.cuda.current_stream()).cuda_stream)
+    scratch = _ABS_MEAN_SCRATCH.get(key)
+    if scratch is None:
+        scratch = _ABS_MEAN_SCRATCH[key] = torch.zeros(2, dtype=torch.int32, device=x.device)
+    if out is None:
+        out = torch.empty(1, dtype=torch.float32, device=x.device)
+    rc = lib.cb_abs_mean_bf16(C.c_void_p(x.data_ptr()), C.c_longlong(x.numel()),
+                              C.c_void_p(out.data_ptr()), C.c_void_p(scratch.data_ptr()),
+                              N.stream_ptr(stream))
+    if rc != 0:
+        raise UtilError(f"abs_mean failed: {N.last_error()}")
+    return out
+
+
 def device_attributes(device: int = 0) -> dict:
     lib = N.load()
     buf = C.create_string_buffer(4096)

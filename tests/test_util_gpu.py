@@ -109,3 +109,21 @@ def test_ipc_weight_hand_off_between_two_processes(native_lib):
     p.join(60)
     assert p.exitcode == 0 and shape == (1024, 1024) and mapped == 1
     assert total == expect
+
+
+@pytest.mark.parametrize("shape", [(8,), (1000, 8), (4096, 8192), (3, 5)])
+def test_abs_mean_one_pass_matches_torch(native_lib, shape):
+    """The step metric: one launch, one pass; repeated calls re-arm the scratch words; shapes the
+    kernel does not take (not a multiple of 8 elements) fall back to the PyTorch expression."""
+    from commbench_b200.ops.util import abs_mean
+
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(shape, device="cuda", generator=g).bfloat16()
+    want = x.float().abs().mean().item()
+    for _ in range(3):
+        got = abs_mean(x)
+        assert got.shape == (1,) and got.dtype == torch.float32
+        assert abs(got.item() - want) <= 1e-4 * max(abs(want), 1e-6)
+    out = torch.empty(1, device="cuda")
+    assert abs_mean(x, out=out).data_ptr() == out.data_ptr()
+    assert abs(out.item() - want) <= 1e-4 * max(abs(want), 1e-6)

@@ -61,6 +61,7 @@ struct AgGemmParams {
   int block_rows;  // rows of one row block (the tile height)
   int gate_group;  // row blocks per raster panel of the local tiles while gated
   unsigned int gate_poll_ns;
+  unsigned int row_poll_ns;  // > 0: pause between polls of a remote row block's counter
 };
 
 // Waits until every row of local row block `rb` has landed (bounded).  Polls are 20 us apart:
@@ -131,8 +132,13 @@ struct AgPolicy {
       return true;
     }
     const uint32_t* f = p.flags_local + r.parity * kAgMaxRowBlocks + m_blk;
-    if (!wait_flag_ge_sys(f, static_cast<uint32_t>(p.parts), p.timeout_ns, p.status, PH_AG_ROWS,
-                          m_blk)) {
+    const bool arrived =
+        p.row_poll_ns > 0u
+            ? wait_flag_ge_sys_paced(f, static_cast<uint32_t>(p.parts), p.timeout_ns, p.status,
+                                     PH_AG_ROWS, m_blk, p.row_poll_ns)
+            : wait_flag_ge_sys(f, static_cast<uint32_t>(p.parts), p.timeout_ns, p.status,
+                               PH_AG_ROWS, m_blk);
+    if (!arrived) {
       *abort_flag = 1;
       return false;
     }
@@ -343,6 +349,7 @@ struct CbAgGemmDesc {
 };
 
 static unsigned int g_gate_poll_ns = 20000u;
+static unsigned int g_row_poll_ns = 0u;
 
 static int build_ag_params(const CbAgGemmDesc& d, AgGemmParams* p) {
   const int esz = d.fp8 ? 1 : 2;
@@ -432,6 +439,7 @@ static int build_ag_params(const CbAgGemmDesc& d, AgGemmParams* p) {
     p->gate_group = gg;
   }
   p->gate_poll_ns = g_gate_poll_ns;
+  p->row_poll_ns = g_row_poll_ns;
   p->src_ready = static_cast<const uint32_t*>(d.src_ready);
   p->src_ready_target = d.src_ready_target;
   p->src_ready_rows = d.src_ready_rows > 0 ? d.src_ready_rows : bm;
@@ -456,6 +464,10 @@ static int build_ag_params(const CbAgGemmDesc& d, AgGemmParams* p) {
   }
   return 0;
 }
+
+// Nanoseconds between polls of a remote row block's arrival counter (tuning; 0 = a few
+// back-to-back polls, then 128 ns / 512 ns / 1 us apart).
+void cb_ag_gemm_set_row_poll_ns(unsigned int ns) { g_row_poll_ns = ns; }
 
 // Nanoseconds between polls of the local-rows gate (tuning; default 20000).
 void cb_ag_gemm_set_gate_poll_ns(unsigned int ns) { g_gate_poll_ns = ns; }

@@ -46,6 +46,7 @@ struct GemmRsParams {
   FusedSeq seq;
   uint32_t* status;
   unsigned long long timeout_ns;
+  unsigned int poll_ns;  // pause between polls of a tile's arrival counter
 };
 
 struct RsRt {
@@ -92,7 +93,7 @@ struct RsPolicy {
     const int lm = m_blk - p.rank * p.blocks_per_rank;
     const uint32_t* f = p.flags_local + r.parity * kRsMaxTiles + flag_index(p, lm, n_blk, sub);
     return wait_flag_ge_sys_paced(f, static_cast<uint32_t>(p.world - 1), p.timeout_ns, p.status,
-                                  PH_RS_TILE, lm * p.g.num_n_blocks + n_blk, kPacedPollNs);
+                                  PH_RS_TILE, lm * p.g.num_n_blocks + n_blk, p.poll_ns);
   }
   __device__ static void local_reduce(const RsRt& r, int m_blk, int n_blk, LocalReduce* t) {
     const GemmRsParams& p = *r.p;
@@ -201,6 +202,14 @@ using namespace cb;
 
 extern "C" {
 
+// Polls of a local tile's arrival counter are 3 us apart.  Measured on 4 GPUs at the bench
+// shape, two sweeps: at 300 ns the CTAs that reach their own tiles early delay the peers'
+// partial tiles on their way in (fp8 0.69 / 0.85 ms, bf16 0.67 / 1.04 ms); 1 us: 0.49 / 0.85
+// and 0.67 / 0.88; 3 us: 0.376 / 0.374 and 0.65 / 0.68; 10 us: 0.44 / 0.41 and 0.69 / 0.65 (the
+// waits themselves start to cost).  Run-to-run spread from the power state is of the same
+// size as the smaller differences; the 300 ns -> 3 us step is not.
+static unsigned int g_rs_poll_ns = 3000u;
+
 struct CbGemmRsDesc {
   int rank, world;
   int M, N, K;            // K = local K shard
@@ -281,8 +290,12 @@ static int build_rs_params(const CbGemmRsDesc& d, GemmRsParams* p) {
   p->seq.done_ctas = static_cast<uint32_t*>(d.seq) + 1;
   p->status = static_cast<uint32_t*>(d.status);
   p->timeout_ns = d.timeout_ns;
+  p->poll_ns = g_rs_poll_ns;
   return 0;
 }
+
+// Nanoseconds between polls of a local tile's arrival counter (tuning).
+void cb_gemm_rs_set_poll_ns(unsigned int ns) { g_rs_poll_ns = ns; }
 
 int cb_sizeof_gemm_rs_params() { return static_cast<int>(sizeof(GemmRsParams)); }
 

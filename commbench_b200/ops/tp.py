@@ -184,13 +184,29 @@ class AgGemm(_FusedBase):
                 _fill_p8(d.a_sf_full_peer[par], self.sf_full[par].ptrs)
         return d
 
+    def pick_tiles(self, M: int, Nn: int) -> int:
+        """Tile form of an all-gather GEMM on real ranks.  CTA pairs (256 x 256) are the faster
+        main loop, but their row block - the unit a tile waits for - is 256 rows.  When a
+        rank's OWN rows give less than one wave of pair tiles, the first remote row blocks
+        are needed almost at once and the finer 128-row blocks of one-CTA tiles overlap
+        better: measured on 8 GPUs (8192 x 3584 x 8192 per rank) 0.409 ms against 0.452 ms;
+        on 4 GPUs (8192 x 7168) pairs win, 0.68-0.73 against 0.86 ms."""
+        bn = self._pick_bn(M, Nn)
+        if bn == 512 and self.world > 1 and not self.emu:
+            local_tiles = (M // self.world // 256) * ((Nn + 255) // 256)
+            if local_tiles < self._ctas() // 2:
+                return 256
+        return bn
+
     @staticmethod
-    def pick_comm_ctas(M: int, Nn: int, bn: int, ctas: int, at_least: int) -> int:
-        """Communication CTAs for a launch of ``ctas`` CTAs: the LARGEST even count between
-        ``at_least`` and 24 that does not add a wave of tiles to the compute CTAs.  (8192 x 3584
-        in 256 x 256 pair tiles = 448 tiles: 70 pairs and 64 pairs both need 7 waves, so 20 CTAs
-        can push rows instead of 8 at no cost; 8192 x 14336 = 1792 tiles: 72 pairs need 25
-        waves, 70 need 26, so only 4 are taken.)"""
+    def pick_comm_ctas(M: int, Nn: int, bn: int, ctas: int, at_least: int, cap: int = 24) -> int:
+        """Communication CTAs for a launch of ``ctas`` CTAs: the LARGEST even count up to
+        ``cap`` that does not add a wave of tiles to the compute CTAs (8192 x 14336 in pair
+        tiles = 1792 tiles: 72 pairs need 25 waves, 70 need 26, so 4 are taken; 8192 x 7168:
+        10).  Multicast pushes do not get faster with more CTAs - on 8 GPUs 4 communication
+        CTAs gave 0.409-0.452 ms and 20 gave 0.48-0.51 - so the caller caps the count at 4
+        from 8 ranks up."""
+        at_least = min(at_least, cap)
         pair = 2 if bn in (512, 192) else 1
         tile_m = 128 * pair
         tile_n = {512: 256, 192: 192}.get(bn, bn)
@@ -200,10 +216,10 @@ class AgGemm(_FusedBase):
             workers = (ctas - c) // pair
             return -(-tiles // workers) if workers > 0 else 1 << 30
         best, best_w = None, None
-        for c in range(2, 26, 2):
+        for c in range(2, cap + 2, 2):
             w = waves(c)
             if best is None or w < best_w or (w == best_w and c >= best):
-                if w < (best_w or 1 << 30) or c <= 24:
+                if w < (best_w or 1 << 30) or c <= cap:
                     best, best_w = c, w
         # never below the floor unless that saves a whole wave
         if best < at_least and waves(at_least) == best_w:
@@ -248,9 +264,10 @@ class AgGemm(_FusedBase):
                                 "scale tensors, and shard whole 256-row blocks")
             bn = 192
         elif bn is None:
-            bn = self._pick_bn(M, Nn)
+            bn = self.pick_tiles(M, Nn)
         if auto_comm and not self.emu and self.world > 1:
-            comm_ctas = self.pick_comm_ctas(M, Nn, bn, self._ctas(), comm_ctas)
+            comm_ctas = self.pick_comm_ctas(M, Nn, bn, self._ctas(), comm_ctas,
+                                            cap=4 if self.world >= 8 else 24)
             if parts is None or parts < 1:
                 parts = comm_ctas
         if self.emu:

@@ -54,3 +54,13 @@ def test_expert_placement_is_balanced_and_deterministic():
     # every rank keeps exactly E / W slots
     assert all(len(new[r * 2:(r + 1) * 2]) == 2 for r in range(4))
     assert imbalance([0] * 8, start, 4) == 1.0
+
+
+def test_ag_gemm_comm_cta_rule():
+    from commbench_b200.ops.tp import AgGemm
+
+    # largest count that keeps the compute CTAs' tile waves, within the cap
+    assert AgGemm.pick_comm_ctas(8192, 14336, 512, 148, 8) == 4      # 72 pairs: 25 waves, 70: 26
+    assert AgGemm.pick_comm_ctas(8192, 7168, 512, 148, 8) == 10
+    assert AgGemm.pick_comm_ctas(8192, 3584, 256, 148, 8, cap=4) == 4
+    assert AgGemm.pick_comm_ctas(8192, 3584, 512, 148, 8, cap=4) % 2 == 0

@@ -67,3 +67,14 @@ def test_plan_all_reduce_falls_back_without_multicast(tmp_path, monkeypatch):
     assert coll.plan_all_reduce(Ctx, (64 << 20) + 8, True)["algo"] != "nvls"   # not 16-byte sized
     monkeypatch.delenv("CB200_TUNE_TABLE")
     tuning.reload()
+
+
+def test_tuner_grid_candidates_are_bounded():
+    from commbench_b200.ops.tune import _grid_candidates
+
+    assert _grid_candidates(8192) == [1]                      # never less than 8 KB per CTA
+    assert max(_grid_candidates(1 << 30)) == 128              # never all 148 SMs
+    assert min(_grid_candidates(128 << 20)) >= 64             # never more than 2 MB per CTA
+    for share in (65536, 1 << 20, 32 << 20):
+        g = _grid_candidates(share)
+        assert g == sorted(g) and len(set(g)) == len(g)

@@ -168,6 +168,10 @@ EXAMPLE_TASK: dict = {
     "example057": "ring_attention_kernel", "example069": "ring_attention_kernel",
     "example070": "ulysses_attention_kernel",
     "example031": "twoshot_allreduce_tuned", "example097": "twoshot_allreduce_tuned",
+    "example004": "rdma_device_query", "example029": "rdma_device_query",
+    "example007": "rdma_uc_write", "example028": "rdma_nic_clock",
+    "example092": "transport_put_signal_allreduce",
+    "example033": "put_signal_virtual_ranks", "example040": "put_signal_virtual_ranks",
 }
 EXAMPLE_API: dict = {
     "example004": "ops.transport.Context.device_info", "example029": "ops.transport.Context.device_info",

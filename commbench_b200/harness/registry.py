@@ -172,6 +172,10 @@ EXAMPLE_TASK: dict = {
     "example007": "rdma_uc_write", "example028": "rdma_nic_clock",
     "example092": "transport_put_signal_allreduce",
     "example033": "put_signal_virtual_ranks", "example040": "put_signal_virtual_ranks",
+    "example003": "fifo_device_host", "example005": "fifo_device_host",
+    "example010": "gpu_attributes_probe", "example035": "tile_produce_consume",
+    "example073": "p2p_pingpong", "example088": "ipc_weight_handoff",
+    "example101": "tp_qknorm_virtual_ranks", "example102": "tp_qknorm_virtual_ranks",
 }
 EXAMPLE_API: dict = {
     "example004": "ops.transport.Context.device_info", "example029": "ops.transport.Context.device_info",

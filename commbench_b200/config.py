@@ -28,7 +28,10 @@ class Config:
     ag_gemm_comm_ctas: int = 8                  # CTAs reserved for pushing the local A shard
     gemm_ar_oneshot_max_m: int = 0              # rows at or below use the one-shot epilogue (0: never)
     gemm_ar_split_max_world: int = 4            # up to this many ranks "auto" runs GEMM + all-reduce as two launches
-    fused_poll_ns: int = 300                    # pause between polls of a peer-written flag
+    fused_poll_ns: int = 300                    # GEMM->AR: pause between polls of a peer-written flag
+    gemm_rs_poll_ns: int = 3000                 # GEMM->RS: pause between polls of a tile's arrival counter
+    ag_gemm_row_poll_ns: int = 0                # AG->GEMM: pause between polls of a remote row block (0: back-off)
+    ag_gemm_gate_poll_ns: int = 20000           # AG->GEMM: pause between polls of the host-copy gate
     # --- attention -------------------------------------------------------
     attn_impl: int = 4                          # flash-attention kernel: 4 (P kept in TMEM) or 1
     cp_comm_ctas: int = 4                       # ring attention: CTAs that pull the K/V shards

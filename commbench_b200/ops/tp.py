@@ -156,6 +156,9 @@ class AgGemm(_FusedBase):
         self.a_full = [_Sym(ctx, nbytes), _Sym(ctx, nbytes)]
         self.flags = _Sym(ctx, 2 * 1024 * 4, zero=True)
         # fp8 with hardware block scales: the gathered rows' packed scale words, per parity
+        cfg = get_config()
+        self.lib.cb_ag_gemm_set_row_poll_ns(C.c_uint(cfg.ag_gemm_row_poll_ns))
+        self.lib.cb_ag_gemm_set_gate_poll_ns(C.c_uint(cfg.ag_gemm_gate_poll_ns))
         self.sf_full = None
         if dtype == torch.float8_e4m3fn and k % 128 == 0:
             sf_bytes = ((k // 128 + 3) // 4) * max_m * 4
@@ -318,6 +321,7 @@ class GemmRs(_FusedBase):
     def __init__(self, ctx, max_m: int, max_n: int):
         super().__init__(ctx)
         self.max_m, self.max_n = max_m, max_n
+        self.lib.cb_gemm_rs_set_poll_ns(C.c_uint(get_config().gemm_rs_poll_ns))
         nbytes = max_m * max_n * 2  # W sources x M/W rows x N bf16
         self.stage = [_Sym(ctx, nbytes), _Sym(ctx, nbytes)]
         self.flags = _Sym(ctx, 2 * 8192 * 4, zero=True)

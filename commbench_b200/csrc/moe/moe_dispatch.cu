@@ -109,17 +109,22 @@ struct MoeRecvArgs {
   const float* recv_scale;    // [max_rows, H/128]
   int2* recv_meta;            // [max_rows]
   __nv_bfloat16* a_out;       // bf16 [max_rows, H]  (grouped-GEMM input)
-  const uint32_t* arrived;    // [El]
+  uint32_t* arrived;          // [El]
   const int* recv_expected;   // [El]
   const int* recv_base;       // [El+1]
   int H, max_rows;
   unsigned long long timeout_ns;
   uint32_t* status;
+  uint32_t* ctas_done;        // [El] zero-initialised words of this rank, or null (see the kernel)
 };
 
 // grid (El, slices).  Waits until the expert's rows are all in, then
 // dequantises them to bf16; padding rows (up to the next multiple of 128) are
 // zeroed and marked with source rank -1 so later stages skip them.
+// With `ctas_done` set, the last CTA of an expert to finish clears that expert's arrival
+// counter, so no separate fill launch is needed between two calls.  This is early enough: a peer
+// cannot send rows of its NEXT call before it has this rank's combine rows of the current one,
+// and those leave after this kernel in stream order.
 __global__ void __launch_bounds__(256)
     moe_recv_dequant_kernel(const __grid_constant__ MoeRecvArgs a) {
   pdl_wait();                // chained with programmatic dependent launch: see prim/pdl.cuh
@@ -132,12 +137,12 @@ __global__ void __launch_bounds__(256)
   if (threadIdx.x == 0 && expect > 0)
     ok = wait_flag_ge_sys(a.arrived + j, static_cast<uint32_t>(expect), a.timeout_ns, a.status,
                           PH_MOE_ARRIVE2, j);
-  if (__syncthreads_and(ok ? 1 : 0) == 0) return;
+  const bool all_ok = __syncthreads_and(ok ? 1 : 0) != 0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;
   const int nvec = a.H / 8;
   const int groups = a.H / 128;
-  for (int r = blockIdx.y * warps + warp; r < padded; r += gridDim.y * warps) {
+  for (int r = blockIdx.y * warps + warp; all_ok && r < padded; r += gridDim.y * warps) {
     const long long row = static_cast<long long>(base) + r;
     if (row >= a.max_rows) continue;
     uint4* __restrict__ out = reinterpret_cast<uint4*>(a.a_out + row * a.H);
@@ -162,6 +167,16 @@ __global__ void __launch_bounds__(256)
         ob[i] = __floats2bfloat162_rn(f.x * s, f.y * s);
       }
       out[v] = o;
+    }
+  }
+  if (a.ctas_done != nullptr) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      if (atomicAdd(a.ctas_done + j, 1u) == gridDim.y - 1) {
+        a.arrived[j] = 0u;
+        a.ctas_done[j] = 0u;
+      }
     }
   }
 }

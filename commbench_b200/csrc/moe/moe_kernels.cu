@@ -177,15 +177,13 @@ __global__ void __launch_bounds__(kSlotWarps * 32)
 //   mblk_expert[...]    local expert of each 128-row block of my receive buffer
 //   n_mblocks[1]
 // One CTA; E <= 1024.
-__global__ void moe_plan_kernel(const int* __restrict__ counts_all, int W, int E, int rank,
-                                int* send_row_base, int* src_pair_base, int* recv_expected,
-                                int* recv_base, int* mblk_expert, int* n_mblocks,
-                                int max_recv_rows, uint32_t* status) {
-  pdl_wait();                // chained with programmatic dependent launch: see prim/pdl.cuh
-  pdl_launch_dependents();
+// The plan itself, run by one whole CTA; rows_sh / base_sh: 1024 ints of shared memory each.
+__device__ __forceinline__ void moe_plan_body(const int* __restrict__ counts_all, int W, int E,
+                                              int rank, int* send_row_base, int* src_pair_base,
+                                              int* recv_expected, int* recv_base,
+                                              int* mblk_expert, int* n_mblocks, int max_recv_rows,
+                                              uint32_t* status, int* rows_sh, int* base_sh) {
   const int El = E / W;
-  __shared__ int rows_sh[1024];   // rows(d,j) for every global expert
-  __shared__ int base_sh[1024];   // base(d,j)
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int r = 0;
     for (int s = 0; s < W; ++s) r += counts_all[s * E + e];
@@ -229,6 +227,65 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts_all, int W, int E
     for (int b = 0; b < nb; ++b)
       if ((b0 + b) * 128 < max_recv_rows) mblk_expert[b0 + b] = j;
   }
+}
+
+__global__ void moe_plan_kernel(const int* __restrict__ counts_all, int W, int E, int rank,
+                                int* send_row_base, int* src_pair_base, int* recv_expected,
+                                int* recv_base, int* mblk_expert, int* n_mblocks,
+                                int max_recv_rows, uint32_t* status) {
+  pdl_wait();                // chained with programmatic dependent launch: see prim/pdl.cuh
+  pdl_launch_dependents();
+  __shared__ int rows_sh[1024];   // rows(d,j) for every global expert
+  __shared__ int base_sh[1024];   // base(d,j)
+  moe_plan_body(counts_all, W, E, rank, send_row_base, src_pair_base, recv_expected, recv_base,
+                mblk_expert, n_mblocks, max_recv_rows, status, rows_sh, base_sh);
+}
+
+// Plan and pair sort in one launch.  The sort needs only this rank's own row of the count
+// matrix (src_pair_base = exclusive prefix of it), so every CTA rebuilds that prefix in shared
+// memory - E <= 1024 words - and places its 256 pairs; CTA 0 also runs the plan.
+__global__ void __launch_bounds__(256)
+    moe_plan_sort_kernel(const int* __restrict__ counts_all, int W, int E, int rank,
+                         const int* __restrict__ topk_idx, const int* __restrict__ slot,
+                         int n_pairs, int* __restrict__ sorted_pair, int* send_row_base,
+                         int* src_pair_base, int* recv_expected, int* recv_base,
+                         int* mblk_expert, int* n_mblocks, int max_recv_rows, uint32_t* status) {
+  pdl_wait();                // chained with programmatic dependent launch: see prim/pdl.cuh
+  pdl_launch_dependents();
+  __shared__ int pre_sh[1024];    // exclusive prefix of my counts
+  __shared__ int rows_sh[1024];
+  __shared__ int base_sh[1024];
+  const int* __restrict__ mine = counts_all + static_cast<size_t>(rank) * E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) pre_sh[e] = mine[e];
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    const int per = (E + 31) / 32;
+    const int b = min(lane * per, E), en = min(b + per, E);
+    int sum = 0;
+    for (int e = b; e < en; ++e) sum += pre_sh[e];
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    int acc = incl - sum;
+    for (int e = b; e < en; ++e) {
+      const int c = pre_sh[e];
+      pre_sh[e] = acc;
+      acc += c;
+    }
+  }
+  __syncthreads();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_pairs) {
+    const int e = topk_idx[i];
+    if (e >= 0 && e < E) sorted_pair[pre_sh[e] + slot[i]] = i;
+  }
+  if (blockIdx.x == 0)
+    moe_plan_body(counts_all, W, E, rank, send_row_base, src_pair_base, recv_expected, recv_base,
+                  mblk_expert, n_mblocks, max_recv_rows, status, rows_sh, base_sh);
 }
 
 // Inverse of the slot map: sorted_pair[src_pair_base[e] + slot[i]] = i.
@@ -297,6 +354,27 @@ int cb_moe_plan(const void* counts_all, int W, int E, int rank, void* send_row_b
                     static_cast<int*>(send_row_base), static_cast<int*>(src_pair_base),
                     static_cast<int*>(recv_expected), static_cast<int*>(recv_base),
                     static_cast<int*>(mblk_expert), static_cast<int*>(n_mblocks), max_recv_rows,
+                    static_cast<uint32_t*>(status)) == cudaSuccess
+             ? 0
+             : -1;
+}
+
+// cb_moe_plan and cb_moe_sort_pairs as one launch.
+int cb_moe_plan_sort(const void* counts_all, int W, int E, int rank, const void* topk_idx,
+                     const void* slot, int n_pairs, void* sorted_pair, void* send_row_base,
+                     void* src_pair_base, void* recv_expected, void* recv_base, void* mblk_expert,
+                     void* n_mblocks, int max_recv_rows, void* status, void* stream) {
+  if (E > 1024 || E % W != 0 || n_pairs < 1) {
+    set_last_error("plan: E <= 1024 and divisible by the world size, at least one pair required");
+    return -1;
+  }
+  return launch_pdl(moe_plan_sort_kernel, dim3((n_pairs + 255) / 256), dim3(256), 0,
+                    static_cast<cudaStream_t>(stream), static_cast<const int*>(counts_all), W, E,
+                    rank, static_cast<const int*>(topk_idx), static_cast<const int*>(slot),
+                    n_pairs, static_cast<int*>(sorted_pair), static_cast<int*>(send_row_base),
+                    static_cast<int*>(src_pair_base), static_cast<int*>(recv_expected),
+                    static_cast<int*>(recv_base), static_cast<int*>(mblk_expert),
+                    static_cast<int*>(n_mblocks), max_recv_rows,
                     static_cast<uint32_t*>(status)) == cudaSuccess
              ? 0
              : -1;

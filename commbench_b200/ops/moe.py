@@ -51,7 +51,7 @@ class _RecvArgs(C.Structure):
         ("recv_x", C.c_void_p), ("recv_scale", C.c_void_p), ("recv_meta", C.c_void_p),
         ("a_out", C.c_void_p), ("arrived", C.c_void_p), ("recv_expected", C.c_void_p),
         ("recv_base", C.c_void_p), ("H", C.c_int), ("max_rows", C.c_int),
-        ("timeout_ns", C.c_ulonglong), ("status", C.c_void_p),
+        ("timeout_ns", C.c_ulonglong), ("status", C.c_void_p), ("ctas_done", C.c_void_p),
     ]
 
 
@@ -129,6 +129,7 @@ class _RankState:
             torch.empty(L.max_rows, 2 * L.I, dtype=torch.bfloat16, device=dev)
         self.s = torch.empty(L.max_rows, L.I, dtype=torch.bfloat16, device=dev)
         self.done_ctas = torch.zeros(4, **i32)
+        self.recv_ctas = torch.zeros(L.El, **i32)      # CTAs of the receive kernel done, per expert
         self.y = torch.empty(L.T, L.H, dtype=torch.bfloat16, device=dev)
         g = torch.Generator(device=dev).manual_seed(L.seed * 977 + r)
         # bf16 expert weights N(0, 0.02): gate|up stacked [El, 2I, H] and down [El, H, I]
@@ -232,16 +233,14 @@ class MoELayer:
         else:
             counts_all = [coll.all_gather(self.ctx, self.states[0].counts.view(1, E)).contiguous()]
         self._mark("slots+count_gather")
-        # 3. plan + sorted pairs
+        # 3. plan + sorted pairs (one launch)
         for st, idx, ca in zip(self.states, topk_idx, counts_all):
-            N.check(lib.cb_moe_plan(N.ptr(ca), W, E, st.r, N.ptr(st.send_row_base),
-                                    N.ptr(st.src_pair_base), N.ptr(st.recv_expected),
-                                    N.ptr(st.recv_base), N.ptr(st.mblk_expert),
-                                    N.ptr(st.n_mblocks), self.max_rows,
-                                    C.c_void_p(self._status(st)), sp), "cb_moe_plan")
-            N.check(lib.cb_moe_sort_pairs(N.ptr(idx), N.ptr(st.slot), N.ptr(st.src_pair_base),
-                                          n_pairs, E, N.ptr(st.sorted_pair), sp),
-                    "cb_moe_sort_pairs")
+            N.check(lib.cb_moe_plan_sort(N.ptr(ca), W, E, st.r, N.ptr(idx), N.ptr(st.slot), n_pairs,
+                                         N.ptr(st.sorted_pair), N.ptr(st.send_row_base),
+                                         N.ptr(st.src_pair_base), N.ptr(st.recv_expected),
+                                         N.ptr(st.recv_base), N.ptr(st.mblk_expert),
+                                         N.ptr(st.n_mblocks), self.max_rows,
+                                         C.c_void_p(self._status(st)), sp), "cb_moe_plan_sort")
         self._mark("plan+sort")
         # 4. dispatch push (quantise + send + per-expert arrival counters)
         for st, x, idx, w in zip(self.states, xs, topk_idx, topk_w):
@@ -270,11 +269,10 @@ class MoELayer:
             ra.recv_expected, ra.recv_base = st.recv_expected.data_ptr(), st.recv_base.data_ptr()
             ra.H, ra.max_rows = H, self.max_rows
             ra.timeout_ns, ra.status = self.ctx.timeout_ns, self._status(st)
+            ra.ctas_done = st.recv_ctas.data_ptr()    # the kernel re-arms the arrival counters
             # about two CTAs per SM: the kernel streams max_rows * H bytes in and twice that out
             slices = max(4, -(-2 * self.sms // self.El))
             N.check(lib.cb_moe_recv_dequant(C.byref(ra), self.El, slices, sp), "cb_moe_recv_dequant")
-            self._local(self.arrived, st)[:self.El * 4].zero_()   # counters ready for the next call
-            st.n_rows.copy_(st.n_mblocks * 128)
         self._mark("recv_dequant")
         # 6. grouped GEMMs; the second one sends rows home
         for st in self.states:
@@ -290,6 +288,7 @@ class MoELayer:
             N.check(lib.cb_moe_grouped_gemm(C.byref(d), sp), "grouped gemm (up)")
             self._mark("gemm_up")
             if not self.fused_swiglu:
+                torch.mul(st.n_mblocks, 128, out=st.n_rows)
                 N.check(lib.cb_moe_swiglu(N.ptr(st.h1), N.ptr(st.s), N.ptr(st.n_rows), I, sp),
                         "swiglu")
                 self._mark("swiglu")
@@ -321,7 +320,9 @@ class MoELayer:
 
     @property
     def launches_per_call(self) -> int:
-        return 10 if self.fused_swiglu else 11
+        # slots, count all-gather, plan+sort, dispatch, receive, two grouped GEMMs, combine
+        # reduction; the unfused form adds the row count and the SwiGLU kernel
+        return 8 if self.fused_swiglu else 10
 
 
 def expert_sort(topk_idx: torch.Tensor, num_experts: int):

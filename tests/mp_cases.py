@@ -1,7 +1,9 @@
 """Multi-process checks run under torch.distributed.run (one rank per GPU).
 
 Prints one JSON line per check from rank 0 ("check", "ok", "detail") and exits non-zero
-if any check failed on any rank.  Usage: torchrun ... tests/mp_cases.py [--quick]
+if any check failed on any rank.  Usage: torchrun ... tests/mp_cases.py [group ...]
+with groups out of moe, attention, p2p, parallel, all_reduce, all_gather, reduce_scatter,
+all_to_all, broadcast, ag_gemm, gemm_rs, gemm_ar (none named: all of them).
 """
 import json
 import os
@@ -389,9 +391,18 @@ def main():
         ctx.check_status()
         report("tp_mlp/forward_host_gated", all(abs(g - want) <= 2e-3 * abs(want) for g in got_g), got_g)
 
-    t_moe(); t_attention(); t_p2p(); t_parallel()
-    t_all_reduce(); t_all_gather(); t_reduce_scatter(); t_all_to_all(); t_broadcast()
-    t_ag_gemm(); t_gemm_rs(); t_gemm_ar()
+    groups = {"moe": t_moe, "attention": t_attention, "p2p": t_p2p, "parallel": t_parallel,
+              "all_reduce": t_all_reduce, "all_gather": t_all_gather,
+              "reduce_scatter": t_reduce_scatter, "all_to_all": t_all_to_all,
+              "broadcast": t_broadcast, "ag_gemm": t_ag_gemm, "gemm_rs": t_gemm_rs,
+              "gemm_ar": t_gemm_ar}
+    wanted = [a for a in sys.argv[1:] if not a.startswith("-")]
+    unknown = [a for a in wanted if a not in groups]
+    if unknown:
+        raise SystemExit(f"unknown group(s) {unknown}; choose from {sorted(groups)}")
+    for name, fn in groups.items():
+        if not wanted or name in wanted:
+            fn()
     torch.cuda.synchronize()
     dist.barrier()
     ctx.close()

@@ -30,11 +30,23 @@ struct MoeSendArgs {
   uint32_t* arrived[CB_MAX_RANKS];    // [E/W] rows arrived per local expert
   int rank, world, T, K, H, E, max_rows;
   uint32_t* status;
+  int per_token;              // 1: one copy of a token per destination RANK (see the kernel)
 };
 
 // grid (E, slices).  Warp per row: load the token's bf16 row, per-128-channel
 // absmax -> scale, quantise to e4m3, write 8 bytes per lane to the destination
 // row; the CTA then releases once and bumps the expert's arrival counter.
+//
+// per_token = 0 (expanded layout): every (token, expert) selection carries its own copy of the
+// token, written at its final row of the destination's per-expert receive buffer.
+// per_token = 1: a token crosses NVLink once per destination RANK, however many of that rank's
+// experts it selected (the non-expanded mode of the reference's dispatch,
+// datasets/example081_deepep_jit_dispatch_copy_epilogue/nv/
+// empty_deepep_jit_dispatch_copy_epilogue.cu:11,49-58: `kDoExpand`).  The copy goes to row
+// rank * T + token of the destination's buffer - a position both sides can compute, so no
+// second count exchange is needed - sent by the first of the token's selections that lives on
+// that rank; every selection still writes its {source rank, pair} word at its final row, and the
+// receive kernel expands from there.
 __global__ void __launch_bounds__(256)
     moe_dispatch_send_kernel(const __grid_constant__ MoeSendArgs a) {
   pdl_wait();                // chained with programmatic dependent launch: see prim/pdl.cuh
@@ -53,14 +65,25 @@ __global__ void __launch_bounds__(256)
     const int token = pair / a.K;
     const long long row = static_cast<long long>(a.send_row_base[e]) + r;
     if (row >= a.max_rows) continue;  // plan kernel already reported the overflow
+    long long drow = row;
+    bool send = true;                 // the same for every lane: `pair` belongs to the warp
+    if (a.per_token) {
+      const int k = pair - token * a.K;
+      const int lo = dst * El, hi = lo + El;
+      for (int kk = 0; kk < k; ++kk) {
+        const int ee = a.topk_idx[token * a.K + kk];
+        if (ee >= lo && ee < hi) send = false;     // an earlier selection already sends the token
+      }
+      drow = static_cast<long long>(a.rank) * a.T + token;
+    }
     const uint4* __restrict__ src =
         reinterpret_cast<const uint4*>(a.x + static_cast<size_t>(token) * a.H);
-    uint2* __restrict__ dq = reinterpret_cast<uint2*>(a.recv_x[dst] + row * a.H);
-    float* __restrict__ ds = a.recv_scale[dst] + row * groups;
+    uint2* __restrict__ dq = reinterpret_cast<uint2*>(a.recv_x[dst] + drow * a.H);
+    float* __restrict__ ds = a.recv_scale[dst] + drow * groups;
     // H is a multiple of 256, so every lane makes the same number of trips (the shuffles below
     // need the whole warp); four rows of loads in flight per lane.
 #pragma unroll 4
-    for (int v = lane; v < nvec; v += 32) {
+    for (int v = lane; send && v < nvec; v += 32) {
       const uint4 raw = src[v];
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
       float f[8];
@@ -116,6 +139,9 @@ struct MoeRecvArgs {
   unsigned long long timeout_ns;
   uint32_t* status;
   uint32_t* ctas_done;        // [El] zero-initialised words of this rank, or null (see the kernel)
+  int per_token;              // 1: rows were sent once per token and rank; expand them here
+  int T, K;                   // tokens per rank and selections per token (per_token only)
+  int stage_rows;             // rows of recv_x / recv_scale (per_token only: world * T)
 };
 
 // grid (El, slices).  Waits until the expert's rows are all in, then
@@ -134,9 +160,25 @@ __global__ void __launch_bounds__(256)
   const int base = a.recv_base[j];
   const int padded = a.recv_base[j + 1] - base;
   bool ok = true;
-  if (threadIdx.x == 0 && expect > 0)
+  if (a.per_token) {
+    // A row of this expert may have been sent on behalf of another expert of this rank (the
+    // token's first selection here), so every counter of the rank has to be complete.  One
+    // thread polls them one after the other (starting at its own): all must be complete
+    // anyway, and few pollers leave the memory system to the rows still arriving.
+    if (threadIdx.x == 0) {
+      const int n = static_cast<int>(gridDim.x);
+      for (int t = 0; t < n && ok; ++t) {
+        const int i = (j + t) % n;
+        const int ex = a.recv_expected[i];
+        if (ex > 0)
+          ok = wait_flag_ge_sys(a.arrived + i, static_cast<uint32_t>(ex), a.timeout_ns, a.status,
+                                PH_MOE_ARRIVE2, i);
+      }
+    }
+  } else if (threadIdx.x == 0 && expect > 0) {
     ok = wait_flag_ge_sys(a.arrived + j, static_cast<uint32_t>(expect), a.timeout_ns, a.status,
                           PH_MOE_ARRIVE2, j);
+  }
   const bool all_ok = __syncthreads_and(ok ? 1 : 0) != 0;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;
@@ -151,8 +193,17 @@ __global__ void __launch_bounds__(256)
       if (lane == 0) a.recv_meta[row] = make_int2(-1, -1);
       continue;
     }
-    const uint2* __restrict__ q = reinterpret_cast<const uint2*>(a.recv_x + row * a.H);
-    const float* __restrict__ sc = a.recv_scale + row * groups;
+    long long srow = row;
+    if (a.per_token) {
+      const int2 m = __ldcg(a.recv_meta + row);          // {source rank, source pair}
+      srow = static_cast<long long>(m.x) * a.T + m.y / a.K;
+      if (m.x < 0 || m.y < 0 || srow >= a.stage_rows) {   // never written: leave a zero row
+        for (int v = lane; v < nvec; v += 32) out[v] = make_uint4(0, 0, 0, 0);
+        continue;
+      }
+    }
+    const uint2* __restrict__ q = reinterpret_cast<const uint2*>(a.recv_x + srow * a.H);
+    const float* __restrict__ sc = a.recv_scale + srow * groups;
 #pragma unroll 4
     for (int v = lane; v < nvec; v += 32) {
       const uint2 raw = __ldcg(q + v);
@@ -173,7 +224,12 @@ __global__ void __launch_bounds__(256)
     __syncthreads();
     if (threadIdx.x == 0) {
       __threadfence();
-      if (atomicAdd(a.ctas_done + j, 1u) == gridDim.y - 1) {
+      if (a.per_token) {       // every CTA polls every counter: only the last CTA of the grid may clear
+        if (atomicAdd(a.ctas_done, 1u) == gridDim.x * gridDim.y - 1) {
+          for (unsigned i = 0; i < gridDim.x; ++i) a.arrived[i] = 0u;
+          a.ctas_done[0] = 0u;
+        }
+      } else if (atomicAdd(a.ctas_done + j, 1u) == gridDim.y - 1) {
         a.arrived[j] = 0u;
         a.ctas_done[j] = 0u;
       }
@@ -298,6 +354,10 @@ int cb_moe_dispatch_send(const MoeSendArgs* a, int slices, void* stream) {
 }
 
 int cb_moe_recv_dequant(const MoeRecvArgs* a, int n_local_experts, int slices, void* stream) {
+  if (a->per_token && (a->T < 1 || a->K < 1 || a->stage_rows < 1)) {
+    set_last_error("receive: the per-token form needs T, K and stage_rows");
+    return -1;
+  }
   dim3 grid(n_local_experts, slices < 1 ? 1 : slices);
   return launch_pdl(moe_recv_dequant_kernel, grid, dim3(256), 0,
                     static_cast<cudaStream_t>(stream), *a) == cudaSuccess

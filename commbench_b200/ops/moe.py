@@ -42,7 +42,7 @@ class _SendArgs(C.Structure):
         ("send_row_base", C.c_void_p),
         ("recv_x", _P8), ("recv_scale", _P8), ("recv_meta", _P8), ("arrived", _P8),
         ("rank", C.c_int), ("world", C.c_int), ("T", C.c_int), ("K", C.c_int), ("H", C.c_int),
-        ("E", C.c_int), ("max_rows", C.c_int), ("status", C.c_void_p),
+        ("E", C.c_int), ("max_rows", C.c_int), ("status", C.c_void_p), ("per_token", C.c_int),
     ]
 
 
@@ -52,6 +52,7 @@ class _RecvArgs(C.Structure):
         ("a_out", C.c_void_p), ("arrived", C.c_void_p), ("recv_expected", C.c_void_p),
         ("recv_base", C.c_void_p), ("H", C.c_int), ("max_rows", C.c_int),
         ("timeout_ns", C.c_ulonglong), ("status", C.c_void_p), ("ctas_done", C.c_void_p),
+        ("per_token", C.c_int), ("T", C.c_int), ("K", C.c_int), ("stage_rows", C.c_int),
     ]
 
 
@@ -144,9 +145,22 @@ class MoELayer:
 
     def __init__(self, ctx, tokens: int, hidden: int, intermediate: int, num_experts: int,
                  topk: int, capacity_factor: float = 2.0, seed: int = 0,
-                 fused_swiglu: bool | None = None):
+                 fused_swiglu: bool | None = None, dispatch: str = "per_pair"):
+        """``dispatch``: ``"per_pair"`` sends every (token, expert) selection as its own fp8 row,
+        straight to its final position in the destination's per-expert buffer; ``"per_token"``
+        sends a token once per destination RANK and lets the receive kernel expand it to the
+        rows of that rank's experts (fewer NVLink bytes when a token selects several experts of
+        one rank: about a third at top-8 over 8 ranks; the receive then waits for all of a
+        rank's rows instead of expert by expert)."""
         self.ctx, self.lib = ctx, ctx.lib
         from ..config import get_config
+
+        if dispatch not in ("per_pair", "per_token"):
+            raise CommError("dispatch must be 'per_pair' or 'per_token'")
+        self.per_token = dispatch == "per_token"
+        if (self.lib.cb_sizeof_moe_send_args() != C.sizeof(_SendArgs)
+                or self.lib.cb_sizeof_moe_recv_args() != C.sizeof(_RecvArgs)):
+            raise CommError("MoE argument structs differ between the library and its Python mirror")
 
         self.fused_swiglu = get_config().moe_fused_swiglu if fused_swiglu is None else fused_swiglu
         self.emu = isinstance(ctx, EmuContext)
@@ -161,8 +175,10 @@ class MoELayer:
         dev = ctx.device
         from .tp import _Sym
 
-        self.recv_x = _Sym(ctx, self.max_rows * hidden)
-        self.recv_scale = _Sym(ctx, self.max_rows * (hidden // 128) * 4)
+        # rows of the fp8 receive buffer: the grouped layout, or one slot per (source rank, token)
+        self.stage_rows = self.W * tokens if self.per_token else self.max_rows
+        self.recv_x = _Sym(ctx, self.stage_rows * hidden)
+        self.recv_scale = _Sym(ctx, self.stage_rows * (hidden // 128) * 4)
         self.recv_meta = _Sym(ctx, self.max_rows * 8)
         self.arrived = _Sym(ctx, max(self.El * 4, 64), zero=True)
         self.combine = _Sym(ctx, tokens * topk * hidden * 2)
@@ -255,7 +271,7 @@ class MoELayer:
                 a.recv_meta[r] = self.recv_meta.ptrs[r] if ok else 0
                 a.arrived[r] = self.arrived.ptrs[r] if ok else 0
             a.rank, a.world, a.T, a.K, a.H, a.E, a.max_rows = st.r, W, T, K, H, E, self.max_rows
-            a.status = self._status(st)
+            a.status, a.per_token = self._status(st), int(self.per_token)
             N.check(lib.cb_moe_dispatch_send(C.byref(a), 4, sp), "cb_moe_dispatch_send")
         self._mark("dispatch_send")
         # 5. receive: wait per expert, dequantise to bf16, mark padding rows
@@ -270,6 +286,7 @@ class MoELayer:
             ra.H, ra.max_rows = H, self.max_rows
             ra.timeout_ns, ra.status = self.ctx.timeout_ns, self._status(st)
             ra.ctas_done = st.recv_ctas.data_ptr()    # the kernel re-arms the arrival counters
+            ra.per_token, ra.T, ra.K, ra.stage_rows = int(self.per_token), T, K, self.stage_rows
             # about two CTAs per SM: the kernel streams max_rows * H bytes in and twice that out
             slices = max(4, -(-2 * self.sms // self.El))
             N.check(lib.cb_moe_recv_dequant(C.byref(ra), self.El, slices, sp), "cb_moe_recv_dequant")
@@ -323,6 +340,20 @@ class MoELayer:
         # slots, count all-gather, plan+sort, dispatch, receive, two grouped GEMMs, combine
         # reduction; the unfused form adds the row count and the SwiGLU kernel
         return 8 if self.fused_swiglu else 10
+
+
+def dispatch_rows(topk_idx: torch.Tensor, num_experts: int, world: int, per_token: bool) -> list[int]:
+    """Token rows one rank sends to each destination rank for ``topk_idx`` [T, K] (negative =
+    masked): one per selection (``per_token=False``) or one per distinct (token, rank) couple.
+    Works on any device; the layer's NVLink payload is this times ``H + 4 * H / 128`` bytes."""
+    per = num_experts // world
+    idx = topk_idx.long()
+    dst = torch.where(idx >= 0, idx // per, torch.full_like(idx, -1))          # [T, K]
+    out = []
+    for r in range(world):
+        hit = dst == r
+        out.append(int(hit.any(dim=1).sum()) if per_token else int(hit.sum()))
+    return out
 
 
 def expert_sort(topk_idx: torch.Tensor, num_experts: int):

@@ -63,9 +63,10 @@ class ExpertParallelMoE(MoELayer):
     the output of a shared expert, a residual stream - instead of by separate kernels."""
 
     def __init__(self, ctx, tokens: int, hidden: int, intermediate: int, num_experts: int,
-                 topk: int, capacity_factor: float = 2.0, seed: int = 0, router_weight=None):
+                 topk: int, capacity_factor: float = 2.0, seed: int = 0, router_weight=None,
+                 dispatch: str = "per_pair"):
         super().__init__(ctx, tokens, hidden, intermediate, num_experts, topk,
-                         capacity_factor=capacity_factor, seed=seed)
+                         capacity_factor=capacity_factor, seed=seed, dispatch=dispatch)
         if self.emu:
             raise CommError("ExpertParallelMoE runs on real ranks; use MoELayer for emulation")
         dev = ctx.device

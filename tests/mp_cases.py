@@ -3,7 +3,8 @@
 Prints one JSON line per check from rank 0 ("check", "ok", "detail") and exits non-zero
 if any check failed on any rank.  Usage: torchrun ... tests/mp_cases.py [group ...]
 with groups out of moe, attention, p2p, parallel, all_reduce, all_gather, reduce_scatter,
-all_to_all, broadcast, ag_gemm, gemm_rs, gemm_ar (none named: all of them).
+all_to_all, broadcast, ag_gemm, gemm_rs, gemm_ar (none named: all of them) and, only when
+named, moe_per_token (the layer with one dispatch row per token and rank).
 """
 import json
 import os
@@ -252,6 +253,26 @@ def main():
         report("ep/rebalance_keeps_output", err < 1e-2 and info["moved"] > 0 and
                info["imbalance_after"] < info["imbalance_before"], [err, info])
 
+    @guarded("moe_per_token")
+    def t_moe_per_token():
+        # a token crosses NVLink once per destination rank; the receive kernel expands it
+        from commbench_b200.ops.moe import MoELayer, reference_moe, router_topk
+
+        T, H, I, E, K = 256, 1024, 512, 8 * world, 4
+        layer = MoELayer(ctx, T, H, I, E, K, capacity_factor=4.0, seed=3, dispatch="per_token")
+        g = torch.Generator(device="cuda").manual_seed(500 + rank)
+        x = torch.randn(T, H, device="cuda", generator=g).bfloat16()
+        idx, w = router_topk(torch.randn(T, E, device="cuda", generator=g), K)
+        w1, w2 = layer.weights()
+        w1_all = torch.cat(gather_all(w1.contiguous()))
+        w2_all = torch.cat(gather_all(w2.contiguous()))
+        ref = reference_moe(x, idx, w, w1_all, w2_all, I)
+        for it in range(3):
+            y = layer.forward(x, idx, w)
+            ctx.check_status()
+            err = ((y.float() - ref).abs().max() / (ref.abs().max() + 1e-6)).item()
+            report(f"moe_per_token/{it}", err < 3e-2, err)
+
     @guarded("attention")
     def t_attention():
         from commbench_b200.ops.cp import (RingAttention, reference_attention, ulysses_attention,
@@ -396,7 +417,9 @@ def main():
               "reduce_scatter": t_reduce_scatter, "all_to_all": t_all_to_all,
               "broadcast": t_broadcast, "ag_gemm": t_ag_gemm, "gemm_rs": t_gemm_rs,
               "gemm_ar": t_gemm_ar}
+    on_request = {"moe_per_token": t_moe_per_token}
     wanted = [a for a in sys.argv[1:] if not a.startswith("-")]
+    groups.update({k: v for k, v in on_request.items() if k in wanted})
     unknown = [a for a in wanted if a not in groups]
     if unknown:
         raise SystemExit(f"unknown group(s) {unknown}; choose from {sorted(groups)}")

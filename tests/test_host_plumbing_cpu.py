@@ -220,3 +220,34 @@ def test_gate_up_interleave_puts_both_halves_of_an_output_block_in_one_tile():
     assert torch.allclose((torch.nn.functional.silu(hg[:, :, 0]) * hg[:, :, 1]).reshape(5, I), ref)
     with pytest.raises(Exception):
         interleave_gate_up(torch.zeros(1, 2 * 96, 8))
+
+
+def test_dispatch_rows_per_pair_and_per_token():
+    """Rows a rank sends to each destination: one per selection, or one per (token, rank) couple;
+    and the rule that picks the sender in the per-token form (the first selection of the token
+    that lives on the rank) names exactly one selection of every couple."""
+    from commbench_b200.ops.moe import dispatch_rows
+
+    E, W, K = 16, 4, 4
+    per = E // W
+    idx = torch.tensor([[0, 1, 2, 3],          # all four on rank 0
+                        [0, 4, 8, 12],         # one on each rank
+                        [5, 6, 13, -1],        # two on rank 1, one on rank 3, one masked
+                        [15, 14, 13, 12]])     # all four on rank 3
+    assert dispatch_rows(idx, E, W, per_token=False) == [5, 3, 1, 6]
+    assert dispatch_rows(idx, E, W, per_token=True) == [2, 2, 1, 3]
+    owners = [0] * W
+    for t in range(idx.shape[0]):
+        for k in range(K):
+            e = int(idx[t, k])
+            if e < 0:
+                continue
+            d = e // per
+            if not any(0 <= int(idx[t, kk]) and int(idx[t, kk]) // per == d for kk in range(k)):
+                owners[d] += 1
+    assert owners == dispatch_rows(idx, E, W, per_token=True)
+    g = torch.Generator().manual_seed(0)
+    big = torch.stack([torch.randperm(256, generator=g)[:8] for _ in range(512)])
+    pair, tok = dispatch_rows(big, 256, 8, False), dispatch_rows(big, 256, 8, True)
+    assert sum(pair) == 512 * 8 and all(t <= p for t, p in zip(tok, pair))
+    assert 0.55 < sum(tok) / sum(pair) < 0.75        # 8 * (1 - (7/8)^8) / 8 = 0.66 expected

@@ -42,16 +42,17 @@ def test_dispatch_layout_matches_cpu_reference(native_lib, T, K, R):
     assert torch.equal(per_r.cpu(), ref_in.sum(0).int())
 
 
+@pytest.mark.parametrize("dispatch", ["per_pair", "per_token"])
 @pytest.mark.parametrize("fused_swiglu", [True, False])
 @pytest.mark.parametrize("world", [1, 2, 4])
-def test_moe_layer_virtual_ranks(native_lib, world, fused_swiglu):
+def test_moe_layer_virtual_ranks(native_lib, world, fused_swiglu, dispatch):
     from commbench_b200.ops.moe import MoELayer, reference_moe, router_topk
     from commbench_b200.runtime.context import EmuContext
 
     T, H, I, E, K = 96, 512, 256, 8, 2
     ctx = EmuContext(world)
     layer = MoELayer(ctx, T, H, I, E, K, capacity_factor=float(world) * 2,
-                     fused_swiglu=fused_swiglu)
+                     fused_swiglu=fused_swiglu, dispatch=dispatch)
     assert layer.launches_per_call == (8 if fused_swiglu else 10)
     xs, idxs, ws = [], [], []
     for r in range(world):

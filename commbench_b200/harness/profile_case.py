@@ -4,7 +4,7 @@
     python -m commbench_b200.harness.profile_case gemm_fp8
     python -m commbench_b200.harness.profile_case attn   [--seq 8192 --heads 16]
     python -m commbench_b200.harness.profile_case quant
-    python -m commbench_b200.harness.profile_case moe    [--tokens 4096]   # per-stage event times
+    python -m commbench_b200.harness.profile_case moe    [--tokens 4096] [--dispatch both]   # per-stage event times
     python -m commbench_b200.harness.profile_case ag_gemm | gemm_rs | gemm_ar  [--world 2]
                                   # the fused kernels, virtual ranks inside ONE cooperative launch
 
@@ -48,6 +48,8 @@ def main(argv=None) -> int:
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--launches", type=int, default=3)
+    ap.add_argument("--dispatch", choices=["per_pair", "per_token", "both"], default="per_pair",
+                    help="moe: dispatch form(s) to time (per_token = one row per token and rank)")
     ap.add_argument("--bn", type=int, default=0,
                     help="gemm tile selector (0 = chosen from the shape; 512 = CTA pair, 256x256); "
                          "the fused cases take it too (256 = one CTA per 128x256 tile: the form "
@@ -121,9 +123,15 @@ def main(argv=None) -> int:
         from ..runtime.context import EmuContext
 
         T, H, I, E, K = a.tokens, 7168, 2048, 32, 8
-        for fused in (False, True):
+        runs = []
+        if a.dispatch in ("per_pair", "both"):
+            runs += [("separate_swiglu", False, "per_pair"), ("fused_swiglu", True, "per_pair")]
+        if a.dispatch in ("per_token", "both"):
+            runs += [("fused_swiglu_per_token", True, "per_token")]
+        for label, fused, dispatch in runs:
             ctx = EmuContext(1)
-            layer = MoELayer(ctx, T, H, I, E, K, capacity_factor=1.5, fused_swiglu=fused)
+            layer = MoELayer(ctx, T, H, I, E, K, capacity_factor=1.5, fused_swiglu=fused,
+                             dispatch=dispatch)
             gg = torch.Generator(device=dev).manual_seed(7)
             x = torch.randn(T, H, device=dev, generator=gg).bfloat16()
             idx, w = router_topk(torch.randn(T, E, device=dev, generator=gg), K)
@@ -135,7 +143,8 @@ def main(argv=None) -> int:
             n = a.launches + 2
             stages = {k: round(v / n, 3) for k, v in layer.stage_ms().items()}
             ctx.check_status()
-            out["fused_swiglu" if fused else "separate_swiglu"] = {"ms": round(ms, 3), "stages_ms": stages}
+            out[label] = {"ms": round(ms, 3), "stages_ms": stages,
+                          "launches_per_call": layer.launches_per_call}
             del layer, ctx
             torch.cuda.empty_cache()
     print(json.dumps(out))

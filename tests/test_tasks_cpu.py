@@ -68,13 +68,21 @@ def test_skeleton_and_reference_build(task, tmp_path):
 @pytest.mark.timeout(600)
 @pytest.mark.parametrize("task", CPU)
 def test_cpu_task_reference_passes_and_skeleton_does_not(task, tmp_path):
+    """Reference and skeleton are launched side by side (separate work folders and rendezvous
+    ports): most of a run is interpreter start-up of the ranks."""
+    from concurrent.futures import ThreadPoolExecutor
+
     folder = os.path.join(TASKS, task)
-    r = CR.compile_and_run(folder, CR.find_ref_file(folder), work_dir=str(tmp_path))
+    with ThreadPoolExecutor(2) as pool:
+        f_ref = pool.submit(CR.compile_and_run, folder, CR.find_ref_file(folder),
+                            work_dir=str(tmp_path / "ref"))
+        f_skel = pool.submit(CR.compile_and_run, folder, CR.find_empty_file(folder),
+                             work_dir=str(tmp_path / "skel"))
+        r, skel = f_ref.result(), f_skel.result()
     assert CR.analyze_result(r) == (True, "program reported PASS"), r.output[-2000:]
     rows = (r.result_json or {}).get("metrics")
     spec = CR.load_task(folder)
     assert rows and all(spec["primary_metric"] in row for row in rows)
-    skel = CR.compile_and_run(folder, CR.find_empty_file(folder), work_dir=str(tmp_path))
     assert not CR.analyze_result(skel)[0]
     shutil.rmtree(os.path.join(folder, "__pycache__"), ignore_errors=True)
 
